@@ -1,0 +1,127 @@
+/*
+ * qgemm.h -- C-ABI of the B200 (sm_100a) quantized-GEMM library (libqgemm.so).
+ *
+ * This is the drop-in boundary under the C++ API of include/gemm.h: plain pointers and sizes, no
+ * C++ or framework types. Every pointer is a DEVICE pointer owned by the caller, exactly as in the
+ * reference harness (tests/includes/test_config.h:245-262). All entry points return a
+ * qgemm_status_t and are asynchronous with respect to the host unless stated otherwise; work is
+ * enqueued on `stream` (0 = the default stream, which is what the reference always uses, e.g.
+ * src/gemm/sm80_gemm_kernel_v4.cu:344-349).
+ *
+ * There is no CPU fallback: on a machine without an sm_100 GPU the compute entry points fail with
+ * QGEMM_ERR_CUDA / QGEMM_ERR_UNSUPPORTED.
+ */
+#ifndef QGEMM_H_
+#define QGEMM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    QGEMM_OK = 0,
+    QGEMM_ERR_INVALID_ARG = 1,    /* null pointer, ld smaller than the row length, bad enum */
+    QGEMM_ERR_UNSUPPORTED = 2,    /* dtype combination or device not supported */
+    QGEMM_ERR_ALIGNMENT = 3,      /* operand base not 16-byte aligned or ld*sizeof(T) not a multiple of 16 */
+    QGEMM_ERR_CUDA = 4,           /* a CUDA runtime/driver call failed */
+    QGEMM_ERR_WORKSPACE = 5,      /* scratch memory could not be provided */
+    QGEMM_ERR_DEVICE_TIMEOUT = 6  /* a kernel abandoned a bounded wait; see qgemm_device_status */
+} qgemm_status_t;
+
+typedef enum {
+    QGEMM_DTYPE_BF16 = 0,
+    QGEMM_DTYPE_FP16 = 1,
+    QGEMM_DTYPE_INT8 = 2,
+    QGEMM_DTYPE_FP8_E4M3 = 3, /* OCP e4m3 (max 448), the CUDA-side FP8 type of include/gpu_type.h:7 */
+    QGEMM_DTYPE_FP32 = 4,
+    QGEMM_DTYPE_INT32 = 5
+} qgemm_dtype_t;
+
+/* How the K x N operand B is laid out in memory. */
+typedef enum {
+    QGEMM_B_ROW_MAJOR = 0, /* B[k*ldb + n]: the layout of GEMM_kernel_v1..v5 (src/include/gemm_utils.cuh:108) */
+    QGEMM_B_K_MAJOR = 1    /* B[n*ldb + k]: "col-major [K,N]", the operand form of GEMM_kernel_v3_1 / v4_1
+                              (src/include/gemm_utils.cuh:263-273) and of fp8_mm
+                              (src/mix_gemm/hip_mix_gemm_kernel.cpp:425-439, 508-516) */
+} qgemm_b_layout_t;
+
+typedef struct CUstream_st* qgemm_stream_t; /* == cudaStream_t */
+
+/* Optional tuning overrides; zero in a field means "library heuristic". */
+typedef struct {
+    int tile_n;  /* 128 or 256 */
+    int split_k; /* number of K splits (>= 1) */
+    int group_m; /* tile rows per scheduling group */
+    int max_ctas; /* cap on the persistent grid (testing) */
+} qgemm_tuning_t;
+
+/*
+ * C = A x B.  Replaces GEMM_kernel_v1..v5<typeIn,typeOut> (include/gemm.h:25-66; specialisations
+ * e.g. src/gemm/sm80_gemm_kernel_v4.cu:366-378) and, with QGEMM_B_K_MAJOR, the operand form of
+ * GEMM_kernel_v3_1 / v4_1.
+ *   A: [M,K] row-major, leading dimension lda (elements).   B: see qgemm_b_layout_t, ldb.
+ *   C: [M,N] row-major, ldc.   in_dtype x out_dtype: {BF16,FP16} -> {FP32,BF16,FP16} (fp32
+ *   accumulate), INT8 -> INT32 (exact).
+ * A, and B when K-major, need a 16-byte aligned base and ld*sizeof(T) % 16 == 0 (the reference
+ * needs the same for its float4 / cp.async loads). Row-major B of any alignment is relaid out
+ * into library scratch first.
+ */
+int qgemm_gemm(int in_dtype, int out_dtype, int b_layout, const void* A, size_t lda, const void* B, size_t ldb,
+               void* C, size_t ldc, size_t M, size_t N, size_t K, qgemm_stream_t stream);
+
+/*
+ * Mixed-precision GEMM C = (A o Q_A) x (B o Q_B) (README.md:5-7) with per-matrix scalar
+ * coefficients: out = cast(scale_a * scale_b * acc). Argument order follows the reference's
+ * (a, b, as, bs, c) (src/mix_gemm/hip_mix_gemm_kernel.cpp:508-516; src/gemm/sm80_gemm_kernel.cu:4-22).
+ *   in_dtype: INT8 (int32 accumulate, exact) or FP8_E4M3 (fp32 accumulate); BF16/FP16 also accepted.
+ *   out_dtype: BF16, FP16 or FP32.   scale_a / scale_b: DEVICE pointers to one float each, or NULL (= 1).
+ */
+int qgemm_mix_gemm(int in_dtype, int out_dtype, int b_layout, const void* A, size_t lda, const void* B, size_t ldb,
+                   const float* scale_a, const float* scale_b, void* C, size_t ldc, size_t M, size_t N, size_t K,
+                   qgemm_stream_t stream);
+
+/* Both of the above with explicit tuning (tuning may be NULL). scale_a/scale_b may be NULL. */
+int qgemm_gemm_ex(int in_dtype, int out_dtype, int b_layout, const void* A, size_t lda, const void* B, size_t ldb,
+                  const float* scale_a, const float* scale_b, void* C, size_t ldc, size_t M, size_t N, size_t K,
+                  const qgemm_tuning_t* tuning, qgemm_stream_t stream);
+
+/*
+ * out[c*ld_out + r] = in[r*ld_in + c] for 1- or 2-byte elements. Replaces matrix_transpose<T>
+ * (src/include/matrix_transpose.h:3-4; src/transpose/transpose.cu:60-77). Any rows, cols >= 0;
+ * ld_in >= cols, ld_out >= rows (elements). in and out must not overlap.
+ */
+int qgemm_transpose(const void* in, void* out, size_t rows, size_t cols, size_t ld_in, size_t ld_out,
+                    size_t elem_bytes, qgemm_stream_t stream);
+
+/*
+ * Library-owned scratch of the current device (relaid-out B, split-K partial sums). It grows on
+ * demand (a growth step synchronises the device and allocates); reserve it up front to keep
+ * allocation out of timed or captured regions. The reference API has no workspace argument
+ * (include/gemm.h:25-66), hence the internal buffer.
+ */
+int qgemm_workspace_reserve(size_t bytes);
+size_t qgemm_workspace_bytes(void);
+
+/* Bytes of scratch a call with these arguments would use (0 if none). */
+size_t qgemm_workspace_query(int in_dtype, int b_layout, size_t M, size_t N, size_t K, const qgemm_tuning_t* tuning);
+
+/*
+ * Synchronises the current device and copies its four status words to out4:
+ * [0] error code (0 = none, 1 = a bounded wait ran out), [1] CTA, [2] role (1 producer, 2 MMA,
+ * 3 epilogue), [3] position. Returns QGEMM_ERR_DEVICE_TIMEOUT if [0] != 0. Clears the words.
+ */
+int qgemm_device_status(int* out4);
+
+/* Frees the scratch and cached descriptors of every device (blas::blas_destroy() calls this). */
+int qgemm_shutdown(void);
+
+const char* qgemm_status_string(int status);
+int qgemm_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QGEMM_H_ */

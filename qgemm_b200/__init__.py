@@ -1,0 +1,203 @@
+"""qgemm_b200 -- Python host side of the B200 (sm_100a) quantized-GEMM library.
+
+The product is ``libqgemm.so`` (hand-written CUDA behind the C-ABI of ``include/qgemm.h``). This
+package loads it with ctypes and mirrors the torch-level entry points the reference sketches
+(``bf16_mm`` / ``int8_mm`` / ``fp8_mm`` taking ``(a, b, as, bs, c)``,
+src/gemm/sm80_gemm_kernel.cu:4-22 and src/mix_gemm/hip_mix_gemm_kernel.cpp:508-516). PyTorch is
+used only for device memory and streams; there is no CPU or eager fallback -- if the shared
+library is missing, importing :func:`lib` raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libqgemm.so")
+
+# qgemm_status_t
+OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_CUDA, ERR_WORKSPACE, ERR_DEVICE_TIMEOUT = range(7)
+# qgemm_dtype_t
+BF16, FP16, INT8, FP8_E4M3, FP32, INT32 = range(6)
+# qgemm_b_layout_t
+B_ROW_MAJOR, B_K_MAJOR = 0, 1
+
+#: every symbol include/qgemm.h declares
+C_ABI_SYMBOLS = (
+    "qgemm_gemm", "qgemm_mix_gemm", "qgemm_gemm_ex", "qgemm_transpose", "qgemm_workspace_reserve",
+    "qgemm_workspace_bytes", "qgemm_workspace_query", "qgemm_device_status", "qgemm_shutdown",
+    "qgemm_status_string", "qgemm_version",
+)
+
+
+class Tuning(C.Structure):
+    """qgemm_tuning_t: zero fields mean "library heuristic"."""
+    _fields_ = [("tile_n", C.c_int), ("split_k", C.c_int), ("group_m", C.c_int), ("max_ctas", C.c_int)]
+
+
+class QgemmError(RuntimeError):
+    def __init__(self, status: int, what: str):
+        self.status = status
+        super().__init__(f"{what}: {status_string(status)} (status {status})")
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """The loaded C-ABI library. Raises if it has not been built (python -m qgemm_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: build it with `python -m qgemm_b200.build`; "
+                              "there is no fallback path")
+        L = C.CDLL(LIB_PATH)
+        sz, vp, fp, i = C.c_size_t, C.c_void_p, C.c_void_p, C.c_int
+        L.qgemm_gemm.argtypes = [i, i, i, vp, sz, vp, sz, vp, sz, sz, sz, sz, vp]
+        L.qgemm_mix_gemm.argtypes = [i, i, i, vp, sz, vp, sz, fp, fp, vp, sz, sz, sz, sz, vp]
+        L.qgemm_gemm_ex.argtypes = [i, i, i, vp, sz, vp, sz, fp, fp, vp, sz, sz, sz, sz, C.POINTER(Tuning), vp]
+        L.qgemm_transpose.argtypes = [vp, vp, sz, sz, sz, sz, sz, vp]
+        L.qgemm_workspace_reserve.argtypes = [sz]
+        L.qgemm_workspace_bytes.restype = sz
+        L.qgemm_workspace_query.argtypes = [i, i, sz, sz, sz, C.POINTER(Tuning)]
+        L.qgemm_workspace_query.restype = sz
+        L.qgemm_device_status.argtypes = [C.POINTER(C.c_int)]
+        L.qgemm_status_string.argtypes = [i]
+        L.qgemm_status_string.restype = C.c_char_p
+        for name in ("qgemm_gemm", "qgemm_mix_gemm", "qgemm_gemm_ex", "qgemm_transpose", "qgemm_workspace_reserve",
+                     "qgemm_device_status", "qgemm_shutdown", "qgemm_version"):
+            getattr(L, name).restype = i
+        _lib = L
+    return _lib
+
+
+def status_string(status: int) -> str:
+    return lib().qgemm_status_string(int(status)).decode()
+
+
+def _check(status: int, what: str) -> None:
+    if status != OK:
+        raise QgemmError(status, what)
+
+
+# ----------------------------------------------------------------------------- torch-level API
+def _torch():
+    import torch
+    return torch
+
+
+def _dtype_code(t) -> int:
+    torch = _torch()
+    table = {torch.bfloat16: BF16, torch.float16: FP16, torch.int8: INT8, torch.float32: FP32, torch.int32: INT32}
+    if hasattr(torch, "float8_e4m3fn"):
+        table[torch.float8_e4m3fn] = FP8_E4M3
+    if t.dtype not in table:
+        raise QgemmError(ERR_UNSUPPORTED, f"dtype {t.dtype}")
+    return table[t.dtype]
+
+
+def _require_cuda_2d(name, t):
+    if not t.is_cuda:
+        raise QgemmError(ERR_INVALID_ARG, f"{name} must be a CUDA tensor (there is no CPU path)")
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise QgemmError(ERR_INVALID_ARG, f"{name} must be 2-D with unit inner stride")
+
+
+def _stream_ptr(t) -> int:
+    return _torch().cuda.current_stream(t.device).cuda_stream
+
+
+def _gemm(a, b, scale_a, scale_b, c, b_kmajor: bool, tuning: Tuning | None, mixed: bool) -> None:
+    torch = _torch()
+    for name, t in (("a", a), ("b", b), ("c", c)):
+        _require_cuda_2d(name, t)
+    if a.dtype != b.dtype:
+        raise QgemmError(ERR_INVALID_ARG, "a and b must have the same dtype")
+    M, K = a.shape
+    if b_kmajor:
+        N, Kb = b.shape
+    else:
+        Kb, N = b.shape
+    if Kb != K or tuple(c.shape) != (M, N):
+        raise QgemmError(ERR_INVALID_ARG, f"shape mismatch a{tuple(a.shape)} b{tuple(b.shape)} c{tuple(c.shape)}")
+    for name, s in (("scale_a", scale_a), ("scale_b", scale_b)):
+        if s is not None and (not s.is_cuda or s.dtype != torch.float32 or s.numel() != 1):
+            raise QgemmError(ERR_INVALID_ARG, f"{name} must be a 1-element float32 CUDA tensor")
+    sa = scale_a.data_ptr() if scale_a is not None else None
+    sb = scale_b.data_ptr() if scale_b is not None else None
+    with torch.cuda.device(a.device):
+        rc = lib().qgemm_gemm_ex(
+            _dtype_code(a), _dtype_code(c), B_K_MAJOR if b_kmajor else B_ROW_MAJOR,
+            a.data_ptr(), max(a.stride(0), K), b.data_ptr(), max(b.stride(0), b.shape[1]),
+            sa, sb, c.data_ptr(), max(c.stride(0), N), M, N, K,
+            C.byref(tuning) if tuning is not None else None, _stream_ptr(a))
+    _check(rc, "qgemm_gemm_ex" if not mixed else "qgemm_mix_gemm")
+
+
+def gemm(a, b, c, b_kmajor: bool = False, tuning: Tuning | None = None) -> None:
+    """c[M,N] = a[M,K] x B, B = b[K,N] (row-major) or, with ``b_kmajor``, b[N,K].
+
+    bf16/fp16 inputs give fp32/bf16/fp16 output with fp32 accumulation; int8 inputs give the exact
+    int32 accumulator. Mirrors GEMM_kernel_vN<typeIn,typeOut> of the reference's include/gemm.h:25-66.
+    """
+    _gemm(a, b, None, None, c, b_kmajor, tuning, mixed=False)
+
+
+def mix_gemm(a, b, scale_a, scale_b, c, b_kmajor: bool = True, tuning: Tuning | None = None) -> None:
+    """c = cast(scale_a * scale_b * (a x B)) for int8 (int32 accumulate) or fp8-e4m3 (fp32 accumulate)."""
+    _gemm(a, b, scale_a, scale_b, c, b_kmajor, tuning, mixed=True)
+
+
+def bf16_mm(a, b, a_scale, b_scale, c) -> None:
+    """(a, b, as, bs, c) with a [m,k], b [n,k] as the reference's torch entry points take them
+    (n = b.size(0), src/gemm/sm80_gemm_kernel.cu:4-12). Scales may be None."""
+    _gemm(a, b, a_scale, b_scale, c, True, None, mixed=True)
+
+
+def int8_mm(a, b, a_scale, b_scale, c) -> None:
+    """int8 a [m,k], b [n,k], per-matrix float32 scales -> c [m,n] (src/gemm/sm80_gemm_kernel.cu:14-22)."""
+    _gemm(a, b, a_scale, b_scale, c, True, None, mixed=True)
+
+
+def fp8_mm(a, b, a_scale, b_scale, c) -> None:
+    """fp8-e4m3 a [m,k], b [n,k], per-matrix float32 scales -> c [m,n]
+    (src/mix_gemm/hip_mix_gemm_kernel.cpp:508-516; per-matrix instead of block scales)."""
+    _gemm(a, b, a_scale, b_scale, c, True, None, mixed=True)
+
+
+def transpose(x, out=None):
+    """out[c, r] = x[r, c] for 1- or 2-byte element tensors (matrix_transpose<T>,
+    src/include/matrix_transpose.h:3-4)."""
+    torch = _torch()
+    _require_cuda_2d("x", x)
+    rows, cols = x.shape
+    if out is None:
+        out = torch.empty((cols, rows), dtype=x.dtype, device=x.device)
+    _require_cuda_2d("out", out)
+    if tuple(out.shape) != (cols, rows) or out.dtype != x.dtype:
+        raise QgemmError(ERR_INVALID_ARG, "out must be [cols, rows] of the same dtype")
+    with torch.cuda.device(x.device):
+        rc = lib().qgemm_transpose(x.data_ptr(), out.data_ptr(), rows, cols, max(x.stride(0), cols),
+                                   max(out.stride(0), rows),
+                                   x.element_size(), _stream_ptr(x))
+    _check(rc, "qgemm_transpose")
+    return out
+
+
+def workspace_reserve(nbytes: int) -> None:
+    _check(lib().qgemm_workspace_reserve(int(nbytes)), "qgemm_workspace_reserve")
+
+
+def workspace_query(in_dtype: int, b_layout: int, M: int, N: int, K: int, tuning: Tuning | None = None) -> int:
+    return int(lib().qgemm_workspace_query(in_dtype, b_layout, M, N, K, C.byref(tuning) if tuning else None))
+
+
+def device_status():
+    """Synchronise and return (status, [code, cta, role, position])."""
+    buf = (C.c_int * 4)()
+    rc = lib().qgemm_device_status(buf)
+    return rc, list(buf)
+
+
+def shutdown() -> None:
+    _check(lib().qgemm_shutdown(), "qgemm_shutdown")

@@ -1,0 +1,486 @@
+// Host side of libqgemm.so: argument validation, per-device scratch, TMA tensor maps, tile /
+// split-K selection, kernel launches, and the extern "C" entry points declared in include/qgemm.h.
+//
+// Takes over the role of the reference's launch_bf16_kernel_v{1..5} host templates (grid / block /
+// shared-memory arithmetic and the launch, e.g. src/gemm/sm80_gemm_kernel_v4.cu:333-355) and of its
+// divisibility-based tile dispatch (src/mix_gemm/hip_mix_gemm_kernel.cpp:442-505), with shape
+// heuristics at run time instead of compile-time constexpr configs (src/include/gemm_config.h:30-36).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+
+#include "gemm_launch.cuh"
+#include "qgemm_internal.h"
+
+namespace qgemm {
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceState {
+    bool init = false;
+    int sm_count = 0;
+    int cc_major = 0;
+    void* ws = nullptr;
+    size_t ws_bytes = 0;
+    int* status = nullptr;
+};
+
+std::mutex g_mutex;
+DeviceState g_dev[kMaxDevices];
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+int get_state(DeviceState** out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return QGEMM_ERR_CUDA;
+    if (dev < 0 || dev >= kMaxDevices) return QGEMM_ERR_UNSUPPORTED;
+    DeviceState& s = g_dev[dev];
+    if (!s.init) {
+        if (cudaDeviceGetAttribute(&s.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            return QGEMM_ERR_CUDA;
+        if (cudaDeviceGetAttribute(&s.cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
+            return QGEMM_ERR_CUDA;
+        if (s.cc_major != 10) return QGEMM_ERR_UNSUPPORTED;  // tcgen05 / tensor memory are sm_100 features
+        if (cudaMalloc(&s.status, 64) != cudaSuccess) return QGEMM_ERR_CUDA;
+        if (cudaMemset(s.status, 0, 64) != cudaSuccess) return QGEMM_ERR_CUDA;
+        s.init = true;
+    }
+    if (g_encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess || fn == nullptr)
+            return QGEMM_ERR_CUDA;
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    *out = &s;
+    return QGEMM_OK;
+}
+
+int ensure_workspace(DeviceState& s, size_t bytes) {
+    if (bytes <= s.ws_bytes) return QGEMM_OK;
+    // Growing: earlier launches may still be using the old buffer.
+    if (cudaDeviceSynchronize() != cudaSuccess) return QGEMM_ERR_CUDA;
+    if (s.ws != nullptr) cudaFree(s.ws);
+    s.ws = nullptr;
+    s.ws_bytes = 0;
+    const size_t rounded = (bytes + ((size_t)1 << 20) - 1) & ~(((size_t)1 << 20) - 1);
+    if (cudaMalloc(&s.ws, rounded) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return QGEMM_ERR_WORKSPACE;
+    }
+    s.ws_bytes = rounded;
+    return QGEMM_OK;
+}
+
+// ---------------------------------------------------------------- tensor maps
+struct MapKey {
+    const void* ptr;
+    uint64_t rows, cols, ld;
+    uint32_t box_rows, dtype;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows &&
+               dtype == o.dtype;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        uint64_t h = reinterpret_cast<uint64_t>(k.ptr);
+        auto mix = [&h](uint64_t v) { h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2); };
+        mix(k.rows);
+        mix(k.cols);
+        mix(k.ld);
+        mix(k.box_rows);
+        mix(k.dtype);
+        return static_cast<size_t>(h);
+    }
+};
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+// K-major operand [rows, cols=K] with leading dimension ld (elements); box = 128 bytes of K x box_rows,
+// 128-byte swizzle, zero fill outside the tensor.
+int make_operand_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, int in_dtype, uint32_t box_rows,
+                     CUtensorMap* out) {
+    const MapKey key{ptr, rows, cols, ld, box_rows, static_cast<uint32_t>(in_dtype)};
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) {
+        *out = it->second;
+        return QGEMM_OK;
+    }
+    CUtensorMapDataType dt;
+    uint32_t es;
+    switch (in_dtype) {
+        case QGEMM_DTYPE_BF16: dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; es = 2; break;
+        case QGEMM_DTYPE_FP16: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; es = 2; break;
+        default: dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; es = 1; break;
+    }
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {ld * es};
+    const cuuint32_t box[2] = {128u / es, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    const CUresult r = g_encode(&m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return QGEMM_ERR_CUDA;
+    if (g_maps.size() > 4096) g_maps.clear();
+    g_maps.emplace(key, m);
+    *out = m;
+    return QGEMM_OK;
+}
+
+// ---------------------------------------------------------------- configuration
+struct Config {
+    int bn, splits, kb_per_split, group_m;
+};
+
+int env_int(const char* name) {
+    const char* v = std::getenv(name);
+    return v ? std::atoi(v) : 0;
+}
+
+// Estimated duration in units of "one 128-byte K block of a 128x256 tile" (about 0.27 us at peak).
+double estimate(int bn, int splits, size_t M, size_t N, int kb_total, int sms, int* kbps_out) {
+    const int mt = static_cast<int>((M + kBM - 1) / kBM);
+    const int nt = static_cast<int>((N + bn - 1) / bn);
+    const int kbps = (kb_total + splits - 1) / splits;
+    const int real_splits = (kb_total + kbps - 1) / kbps;
+    const long long units = static_cast<long long>(mt) * nt * real_splits;
+    const long long waves = (units + sms - 1) / sms;
+    const double t_kb = (bn == 256) ? 1.0 : 0.56;  // narrower tiles re-read A relatively more often
+    const double fill = (bn == 256) ? 6.0 : 4.5;   // pipeline fill + epilogue drain per work unit
+    double t = static_cast<double>(waves) * (kbps * t_kb + fill);
+    if (real_splits > 1) {
+        // partial slabs are written once and read once by the second pass (~1.75 MB per unit of time)
+        const double slab_bytes = static_cast<double>(real_splits) * M * N * 4.0;
+        t += 12.0 + 2.0 * slab_bytes / 1.75e6;
+    }
+    *kbps_out = kbps;
+    return t;
+}
+
+Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuning_t* tuning) {
+    int want_bn = tuning ? tuning->tile_n : 0;
+    int want_split = tuning ? tuning->split_k : 0;
+    int want_group = tuning ? tuning->group_m : 0;
+    if (!want_bn) want_bn = env_int("QGEMM_TILE_N");
+    if (!want_split) want_split = env_int("QGEMM_SPLIT_K");
+    if (!want_group) want_group = env_int("QGEMM_GROUP_M");
+
+    Config best{256, 1, kb_total, 16};
+    double best_t = 1e300;
+    for (int bn : {256, 128}) {
+        if (want_bn && bn != want_bn) continue;
+        const int max_split = want_split ? want_split : std::min(kb_total, 16);
+        for (int s = want_split ? want_split : 1; s <= max_split; ++s) {
+            if (s > kb_total) break;
+            int kbps = 0;
+            const double t = estimate(bn, s, M, N, kb_total, sms, &kbps);
+            if (!want_split && s > 1 && kbps < 2) continue;
+            if (t < best_t) {
+                best_t = t;
+                best.bn = bn;
+                best.kb_per_split = kbps;
+                best.splits = (kb_total + kbps - 1) / kbps;
+            }
+        }
+    }
+    if (best_t == 1e300) {  // an override asked for something infeasible (e.g. split_k > K blocks)
+        best.bn = (want_bn == 128) ? 128 : 256;
+        best.splits = 1;
+        best.kb_per_split = kb_total;
+    }
+    best.group_m = want_group > 0 ? want_group : (best.bn == 256 ? 16 : 8);
+    return best;
+}
+
+struct TypeInfo {
+    int kind;       // ptx::KIND_*
+    int elem_bytes;
+    uint32_t fmt;   // tcgen05 operand format code
+    uint32_t cfmt;  // accumulator format code
+    bool acc_int;
+};
+
+bool type_info(int in_dtype, TypeInfo* t) {
+    switch (in_dtype) {
+        case QGEMM_DTYPE_BF16: *t = {ptx::KIND_F16, 2, 1u, 1u, false}; return true;
+        case QGEMM_DTYPE_FP16: *t = {ptx::KIND_F16, 2, 0u, 1u, false}; return true;
+        case QGEMM_DTYPE_INT8: *t = {ptx::KIND_I8, 1, 1u, 2u, true}; return true;
+        case QGEMM_DTYPE_FP8_E4M3: *t = {ptx::KIND_F8, 1, 0u, 1u, false}; return true;
+        default: return false;
+    }
+}
+
+int out_kind_of(int out_dtype) {
+    switch (out_dtype) {
+        case QGEMM_DTYPE_FP32: return OUT_F32;
+        case QGEMM_DTYPE_BF16: return OUT_BF16;
+        case QGEMM_DTYPE_FP16: return OUT_F16;
+        case QGEMM_DTYPE_INT32: return OUT_RAW32;
+        default: return -1;
+    }
+}
+
+size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct Plan {
+    TypeInfo ti;
+    int out_kind;
+    int kb_total;
+    Config cfg;
+    size_t ld_relayout;     // elements; leading dimension of the relaid-out B
+    size_t relayout_bytes;  // 0 when B is already K-major
+    size_t ldw;             // leading dimension of split-K partial slabs (elements)
+    size_t partial_bytes;   // 0 when splits == 1
+};
+
+int make_plan(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, size_t K, int sms,
+              const qgemm_tuning_t* tuning, Plan* p) {
+    if (!type_info(in_dtype, &p->ti)) return QGEMM_ERR_UNSUPPORTED;
+    p->out_kind = out_kind_of(out_dtype);
+    if (p->out_kind < 0) return QGEMM_ERR_UNSUPPORTED;
+    if (p->out_kind == OUT_RAW32 && in_dtype != QGEMM_DTYPE_INT8) return QGEMM_ERR_UNSUPPORTED;
+    if (b_layout != QGEMM_B_ROW_MAJOR && b_layout != QGEMM_B_K_MAJOR) return QGEMM_ERR_INVALID_ARG;
+    if (M > 0x7fffff00ull || N > 0x7fffff00ull || K > 0x7fffff00ull) return QGEMM_ERR_INVALID_ARG;
+    const size_t kblk = 128 / p->ti.elem_bytes;
+    p->kb_total = static_cast<int>((K + kblk - 1) / kblk);
+    p->cfg = choose_config(M, N, std::max(p->kb_total, 1), sms, tuning);
+    p->ld_relayout = round_up(K, 16 / p->ti.elem_bytes);
+    p->relayout_bytes = (b_layout == QGEMM_B_ROW_MAJOR) ? round_up(N * p->ld_relayout * p->ti.elem_bytes, 256) : 0;
+    p->ldw = round_up(N, 4);
+    p->partial_bytes = p->cfg.splits > 1 ? static_cast<size_t>(p->cfg.splits) * M * p->ldw * 4 : 0;
+    return QGEMM_OK;
+}
+
+int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size_t lda, const void* B, size_t ldb,
+                  const float* scale_a, const float* scale_b, void* C, size_t ldc, size_t M, size_t N, size_t K,
+                  const qgemm_tuning_t* tuning, cudaStream_t stream) {
+    if (M == 0 || N == 0) return QGEMM_OK;
+    if (C == nullptr || ldc < N) return QGEMM_ERR_INVALID_ARG;
+    if (K > 0 && (A == nullptr || B == nullptr || lda < K)) return QGEMM_ERR_INVALID_ARG;
+    if (K > 0 && ldb < (b_layout == QGEMM_B_K_MAJOR ? K : N)) return QGEMM_ERR_INVALID_ARG;
+
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState* st = nullptr;
+    int rc = get_state(&st);
+    if (rc != QGEMM_OK) return rc;
+
+    Plan plan;
+    rc = make_plan(in_dtype, out_dtype, b_layout, M, N, K, st->sm_count, tuning, &plan);
+    if (rc != QGEMM_OK) return rc;
+    if (plan.out_kind == OUT_RAW32 && (scale_a != nullptr || scale_b != nullptr)) return QGEMM_ERR_INVALID_ARG;
+    const int out_bytes = (plan.out_kind == OUT_BF16 || plan.out_kind == OUT_F16) ? 2 : 4;
+
+    if (K == 0) {  // empty sum: C = 0
+        return cudaMemset2DAsync(C, ldc * out_bytes, 0, N * out_bytes, M, stream) == cudaSuccess ? QGEMM_OK
+                                                                                                  : QGEMM_ERR_CUDA;
+    }
+
+    const int es = plan.ti.elem_bytes;
+    if (reinterpret_cast<uintptr_t>(A) % 16 != 0 || (lda * es) % 16 != 0) return QGEMM_ERR_ALIGNMENT;
+    if (b_layout == QGEMM_B_K_MAJOR && (reinterpret_cast<uintptr_t>(B) % 16 != 0 || (ldb * es) % 16 != 0))
+        return QGEMM_ERR_ALIGNMENT;
+
+    rc = ensure_workspace(*st, plan.relayout_bytes + plan.partial_bytes);
+    if (rc != QGEMM_OK) return rc;
+
+    const void* b_kmajor = B;
+    size_t ldb_k = ldb;
+    if (b_layout == QGEMM_B_ROW_MAJOR) {
+        // B arrives N-major: relayout to K-major [N, K] in scratch (rows = K, cols = N on the way in).
+        rc = transpose_launch(B, st->ws, K, N, ldb, plan.ld_relayout, es, stream);
+        if (rc != QGEMM_OK) return rc;
+        b_kmajor = st->ws;
+        ldb_k = plan.ld_relayout;
+    }
+
+    const Config& cfg = plan.cfg;
+    CUtensorMap ta, tb;
+    rc = make_operand_map(A, M, K, lda, in_dtype, kBM, &ta);
+    if (rc != QGEMM_OK) return rc;
+    rc = make_operand_map(b_kmajor, N, K, ldb_k, in_dtype, static_cast<uint32_t>(cfg.bn), &tb);
+    if (rc != QGEMM_OK) return rc;
+
+    GemmParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.M = static_cast<int>(M);
+    p.N = static_cast<int>(N);
+    p.K = static_cast<int>(K);
+    p.m_tiles = static_cast<int>((M + kBM - 1) / kBM);
+    p.n_tiles = static_cast<int>((N + cfg.bn - 1) / cfg.bn);
+    p.splits = cfg.splits;
+    p.kb_total = plan.kb_total;
+    p.kb_per_split = cfg.kb_per_split;
+    p.group_m = cfg.group_m;
+    p.idesc = ptx::make_idesc(plan.ti.cfmt, plan.ti.fmt, plan.ti.fmt, kBM, static_cast<uint32_t>(cfg.bn));
+    p.status = st->status;
+
+    int launch_out = plan.out_kind;
+    uint8_t* partials = static_cast<uint8_t*>(st->ws) + plan.relayout_bytes;
+    if (cfg.splits > 1) {
+        p.C = partials;
+        p.ldc = static_cast<long long>(plan.ldw);
+        p.split_stride = static_cast<long long>(M) * static_cast<long long>(plan.ldw);
+        p.c_vec_ok = 1;
+        launch_out = OUT_RAW32;
+    } else {
+        p.C = C;
+        p.ldc = static_cast<long long>(ldc);
+        p.split_stride = 0;
+        p.scale_a = scale_a;
+        p.scale_b = scale_b;
+        p.c_vec_ok = (reinterpret_cast<uintptr_t>(C) % 16 == 0) && ((ldc * out_bytes) % 16 == 0);
+    }
+
+    const long long work = static_cast<long long>(p.m_tiles) * p.n_tiles * p.splits;
+    if (work > 0x7fffffffLL) return QGEMM_ERR_UNSUPPORTED;
+    int grid = static_cast<int>(std::min<long long>(work, st->sm_count));
+    int cap = tuning ? tuning->max_ctas : 0;
+    if (!cap) cap = env_int("QGEMM_MAX_CTAS");
+    if (cap > 0) grid = std::min(grid, cap);
+
+    cudaError_t e;
+    switch (plan.ti.kind) {
+        case ptx::KIND_F16: e = launch_gemm_f16(cfg.bn, launch_out, ta, tb, p, grid, stream); break;
+        case ptx::KIND_I8: e = launch_gemm_i8(cfg.bn, launch_out, ta, tb, p, grid, stream); break;
+        default: e = launch_gemm_f8(cfg.bn, launch_out, ta, tb, p, grid, stream); break;
+    }
+    if (e != cudaSuccess) return QGEMM_ERR_CUDA;
+
+    if (cfg.splits > 1) {
+        rc = splitk_reduce_launch(partials, p.split_stride, p.ldc, cfg.splits, plan.ti.acc_int, C,
+                                  static_cast<long long>(ldc), p.M, p.N, plan.out_kind, scale_a, scale_b, stream);
+        if (rc != QGEMM_OK) return rc;
+    }
+    return QGEMM_OK;
+}
+
+}  // namespace
+
+}  // namespace qgemm
+
+// ------------------------------------------------------------------------------------ C-ABI
+using namespace qgemm;
+
+extern "C" {
+
+int qgemm_gemm_ex(int in_dtype, int out_dtype, int b_layout, const void* A, size_t lda, const void* B, size_t ldb,
+                  const float* scale_a, const float* scale_b, void* C, size_t ldc, size_t M, size_t N, size_t K,
+                  const qgemm_tuning_t* tuning, qgemm_stream_t stream) {
+    return gemm_dispatch(in_dtype, out_dtype, b_layout, A, lda, B, ldb, scale_a, scale_b, C, ldc, M, N, K, tuning,
+                         reinterpret_cast<cudaStream_t>(stream));
+}
+
+int qgemm_gemm(int in_dtype, int out_dtype, int b_layout, const void* A, size_t lda, const void* B, size_t ldb,
+               void* C, size_t ldc, size_t M, size_t N, size_t K, qgemm_stream_t stream) {
+    const bool ok = ((in_dtype == QGEMM_DTYPE_BF16 || in_dtype == QGEMM_DTYPE_FP16) &&
+                     (out_dtype == QGEMM_DTYPE_FP32 || out_dtype == QGEMM_DTYPE_BF16 || out_dtype == QGEMM_DTYPE_FP16)) ||
+                    (in_dtype == QGEMM_DTYPE_INT8 && out_dtype == QGEMM_DTYPE_INT32);
+    if (!ok) return QGEMM_ERR_UNSUPPORTED;
+    return gemm_dispatch(in_dtype, out_dtype, b_layout, A, lda, B, ldb, nullptr, nullptr, C, ldc, M, N, K, nullptr,
+                         reinterpret_cast<cudaStream_t>(stream));
+}
+
+int qgemm_mix_gemm(int in_dtype, int out_dtype, int b_layout, const void* A, size_t lda, const void* B, size_t ldb,
+                   const float* scale_a, const float* scale_b, void* C, size_t ldc, size_t M, size_t N, size_t K,
+                   qgemm_stream_t stream) {
+    if (out_dtype != QGEMM_DTYPE_FP32 && out_dtype != QGEMM_DTYPE_BF16 && out_dtype != QGEMM_DTYPE_FP16)
+        return QGEMM_ERR_UNSUPPORTED;
+    return gemm_dispatch(in_dtype, out_dtype, b_layout, A, lda, B, ldb, scale_a, scale_b, C, ldc, M, N, K, nullptr,
+                         reinterpret_cast<cudaStream_t>(stream));
+}
+
+int qgemm_transpose(const void* in, void* out, size_t rows, size_t cols, size_t ld_in, size_t ld_out,
+                    size_t elem_bytes, qgemm_stream_t stream) {
+    return transpose_launch(in, out, rows, cols, ld_in, ld_out, elem_bytes, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int qgemm_workspace_reserve(size_t bytes) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState* st = nullptr;
+    int rc = get_state(&st);
+    if (rc != QGEMM_OK) return rc;
+    return ensure_workspace(*st, bytes);
+}
+
+size_t qgemm_workspace_bytes(void) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+    return g_dev[dev].ws_bytes;
+}
+
+size_t qgemm_workspace_query(int in_dtype, int b_layout, size_t M, size_t N, size_t K, const qgemm_tuning_t* tuning) {
+    if (M == 0 || N == 0 || K == 0) return 0;
+    int sms = 148;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_dev[dev].init)
+            sms = g_dev[dev].sm_count;
+    }
+    Plan plan;
+    const int out = (in_dtype == QGEMM_DTYPE_INT8) ? QGEMM_DTYPE_INT32 : QGEMM_DTYPE_FP32;
+    if (make_plan(in_dtype, out, b_layout, M, N, K, sms, tuning, &plan) != QGEMM_OK) return 0;
+    return plan.relayout_bytes + plan.partial_bytes;
+}
+
+int qgemm_device_status(int* out4) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState* st = nullptr;
+    int rc = get_state(&st);
+    if (rc != QGEMM_OK) return rc;
+    if (cudaDeviceSynchronize() != cudaSuccess) return QGEMM_ERR_CUDA;
+    int host[4] = {0, 0, 0, 0};
+    if (cudaMemcpy(host, st->status, sizeof(host), cudaMemcpyDeviceToHost) != cudaSuccess) return QGEMM_ERR_CUDA;
+    if (host[0] != 0 && cudaMemset(st->status, 0, 64) != cudaSuccess) return QGEMM_ERR_CUDA;
+    if (out4 != nullptr) std::memcpy(out4, host, sizeof(host));
+    return host[0] != 0 ? QGEMM_ERR_DEVICE_TIMEOUT : QGEMM_OK;
+}
+
+int qgemm_shutdown(void) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int cur = 0;
+    if (cudaGetDevice(&cur) != cudaSuccess) return QGEMM_ERR_CUDA;
+    for (int d = 0; d < kMaxDevices; ++d) {
+        DeviceState& s = g_dev[d];
+        if (!s.init) continue;
+        cudaSetDevice(d);
+        cudaDeviceSynchronize();
+        if (s.ws) cudaFree(s.ws);
+        if (s.status) cudaFree(s.status);
+        s = DeviceState();
+    }
+    cudaSetDevice(cur);
+    g_maps.clear();
+    return QGEMM_OK;
+}
+
+const char* qgemm_status_string(int status) {
+    switch (status) {
+        case QGEMM_OK: return "ok";
+        case QGEMM_ERR_INVALID_ARG: return "invalid argument";
+        case QGEMM_ERR_UNSUPPORTED: return "unsupported dtype combination or device";
+        case QGEMM_ERR_ALIGNMENT: return "operand not 16-byte aligned (base or leading dimension)";
+        case QGEMM_ERR_CUDA: return "CUDA call failed";
+        case QGEMM_ERR_WORKSPACE: return "scratch memory unavailable";
+        case QGEMM_ERR_DEVICE_TIMEOUT: return "a kernel abandoned a bounded wait";
+        default: return "unknown status";
+    }
+}
+
+int qgemm_version(void) { return 100; }
+
+}  // extern "C"

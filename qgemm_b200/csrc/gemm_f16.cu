@@ -1,0 +1,9 @@
+// tcgen05 kind::f16 instantiations of the persistent GEMM kernel.
+#include "gemm_launch.cuh"
+
+namespace qgemm {
+cudaError_t launch_gemm_f16(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                           int grid, cudaStream_t stream) {
+    return launch_kind<ptx::KIND_F16>(bn, out, ta, tb, p, grid, stream);
+}
+}  // namespace qgemm

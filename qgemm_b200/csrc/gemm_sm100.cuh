@@ -1,0 +1,353 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a.
+//
+//   C[M,N] = A[M,K] x B^T   with A K-major ([M,K] row-major) and B K-major ([N,K] row-major).
+//
+// One CTA per SM loops over output tiles (128 x BN) in a grouped order that keeps the set of
+// concurrently processed tiles compact in (m, n) so their A/B panels are shared through L2. Inside
+// the CTA three roles run concurrently:
+//   warp 0 (one elected lane)  TMA producer: fills a STAGES-deep ring of 128-byte-swizzled
+//                              shared-memory tiles, signalling `full[stage]` by transaction bytes;
+//   warp 1 (one elected lane)  MMA issuer: tcgen05.mma from shared-memory descriptors into one of
+//                              two tensor-memory accumulators, releasing ring slots with
+//                              tcgen05.commit -> `empty[stage]` and publishing a finished tile
+//                              with tcgen05.commit -> `tmem_full[acc]`;
+//   warps 2..5                 epilogue: tcgen05.ld of their 32-lane quadrant, scale + down-cast,
+//                              global stores, then `tmem_empty[acc]` so that the mainloop of the
+//                              next tile overlaps the epilogue of this one.
+//
+// This replaces the reference's thread-block-per-tile WMMA / mma.sync kernels
+// (src/gemm/sm80_gemm_kernel_v1.cu:73-173 ... src/gemm/sm89_gemm_kernel_v5.cu:133-270) and its
+// gmem->smem loaders (src/include/gemm_utils.cuh:61-274). Unlike those it honours lda/ldb/ldc and
+// takes any M, N, K >= 1: out-of-range parts of a tile are zero-filled by TMA on the way in and
+// masked on the way out.
+//
+// Every mbarrier wait is bounded: when a wait runs out the CTA records where in `status`, raises a
+// shared abort flag that makes every role leave its loop, lets copies in flight land, frees its
+// tensor memory and returns, so the context stays usable.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "ptx.cuh"
+
+namespace qgemm {
+
+enum : int { OUT_F32 = 0, OUT_BF16 = 1, OUT_F16 = 2, OUT_RAW32 = 3 };
+
+struct GemmParams {
+    void* C;                 // output matrix, or the split-K partial workspace
+    long long ldc;           // leading dimension of C in elements
+    long long split_stride;  // elements between consecutive split-K slabs (unused when splits == 1)
+    int M, N, K;
+    int m_tiles, n_tiles, splits;
+    int kb_total;      // number of 128-byte K blocks covering K
+    int kb_per_split;  // K blocks per split (every split is non-empty)
+    int group_m;       // tile rows per scheduling group
+    uint32_t idesc;    // tcgen05 instruction descriptor
+    const float* scale_a;  // device scalars (may be null = 1.0)
+    const float* scale_b;
+    int* status;   // device status words: [0] code, [1] cta, [2] role, [3] stage/tile
+    int c_vec_ok;  // C base and ldc allow 16-byte vector stores
+};
+
+constexpr int kBM = 128;
+constexpr int kGemmThreads = 192;
+constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
+
+enum : int { ROLE_PRODUCER = 1, ROLE_MMA = 2, ROLE_EPILOGUE = 3 };
+enum : int { DEV_ERR_WAIT_TIMEOUT = 1 };
+
+__device__ __forceinline__ void record_error(int* status, int code, int role, int where) {
+    if (status != nullptr && atomicCAS(&status[0], 0, code) == 0) {
+        status[1] = static_cast<int>(blockIdx.x);
+        status[2] = role;
+        status[3] = where;
+    }
+}
+
+// Returns false when the wait was abandoned (its own limit, or another role's abort).
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                             int role, int where) {
+#pragma unroll 1
+    for (int i = 0; i < 128; ++i)
+        if (ptx::mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t it = 0;
+#pragma unroll 1
+    while (!ptx::mbar_try_wait(bar, parity)) {
+        if ((++it & 0xffu) == 0) {
+            if (*abort_flag != 0) return false;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                *abort_flag = 1;
+                record_error(status, DEV_ERR_WAIT_TIMEOUT, role, where);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+struct TileCoord {
+    int m_blk, n_blk, split;
+};
+
+// Work item -> tile. Splits of one tile are adjacent; tiles are grouped `group_m` tile-rows at a
+// time and walked column by column inside the group (the reference's GROUP_SIZE_M idea,
+// src/gemm/sm80_gemm_kernel_v3.cu:170-184, counted here in tile rows, not elements).
+__device__ __forceinline__ TileCoord decode_tile(int w, const GemmParams& p) {
+    TileCoord t;
+    int tile = w / p.splits;
+    t.split = w - tile * p.splits;
+    int group_sz = p.group_m * p.n_tiles;
+    int g = tile / group_sz;
+    int first_m = g * p.group_m;
+    int gm = min(p.m_tiles - first_m, p.group_m);
+    int r = tile - g * group_sz;
+    t.n_blk = r / gm;
+    t.m_blk = first_m + (r - t.n_blk * gm);
+    return t;
+}
+
+template <int OUT>
+struct OutBytes {
+    static constexpr int value = (OUT == OUT_BF16 || OUT == OUT_F16) ? 2 : 4;
+};
+
+// Writes 32 consecutive columns of one output row: scale, convert, store (16-byte vectors when the
+// whole chunk is in range and aligned, predicated scalars otherwise).
+template <int KIND, int OUT>
+__device__ __forceinline__ void store_chunk(uint8_t* c_base, long long ldc, long long row, int n0, int n_valid,
+                                            bool vec_ok, const uint32_t (&v)[32], float alpha) {
+    if constexpr (OUT == OUT_RAW32) {
+        uint32_t* dst = reinterpret_cast<uint32_t*>(c_base) + row * ldc + n0;
+        if (vec_ok && n_valid == 32) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < n_valid) dst[j] = v[j];
+        }
+    } else {
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            float a = (KIND == ptx::KIND_I8) ? static_cast<float>(static_cast<int>(v[j])) : __uint_as_float(v[j]);
+            f[j] = a * alpha;
+        }
+        if constexpr (OUT == OUT_F32) {
+            float* dst = reinterpret_cast<float*>(c_base) + row * ldc + n0;
+            if (vec_ok && n_valid == 32) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    reinterpret_cast<float4*>(dst)[j] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (j < n_valid) dst[j] = f[j];
+            }
+        } else {
+            uint32_t pk[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                if constexpr (OUT == OUT_BF16) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+                    pk[j] = *reinterpret_cast<uint32_t*>(&h);
+                } else {
+                    __half2 h = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+                    pk[j] = *reinterpret_cast<uint32_t*>(&h);
+                }
+            }
+            uint16_t* dst = reinterpret_cast<uint16_t*>(c_base) + row * ldc + n0;
+            if (vec_ok && n_valid == 32) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    reinterpret_cast<uint4*>(dst)[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (j < n_valid) dst[j] = static_cast<uint16_t>((j & 1) ? (pk[j >> 1] >> 16) : (pk[j >> 1] & 0xffffu));
+            }
+        }
+    }
+}
+
+template <int BN, int STAGES>
+struct GemmSmem {
+    static constexpr int kAStage = kBM * 128;
+    static constexpr int kBStage = BN * 128;
+    static constexpr int kTiles = STAGES * (kAStage + kBStage);
+    static constexpr int kBarOffset = kTiles;                    // full[STAGES], empty[STAGES], tfull[2], tempty[2]
+    static constexpr int kMiscOffset = kBarOffset + (2 * STAGES + 4) * 8;  // tmem base, abort flag
+    static constexpr int kTotal = kMiscOffset + 16;
+    static constexpr int kDynamicBytes = kTotal + 1024;          // slack for the 1024-byte alignment
+};
+
+template <int KIND, int BN, int STAGES, int OUT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const GemmParams p) {
+    using L = GemmSmem<BN, STAGES>;
+    constexpr int ELT = (KIND == ptx::KIND_F16) ? 2 : 1;
+    constexpr int BK = 128 / ELT;  // elements per 128-byte K block
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+    static_assert(TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns");
+    static_assert(BN % 32 == 0 && BN <= 256, "tile N");
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
+    uint8_t* smem = smem_raw + pad;
+    const uint32_t smem_base = raw_addr + pad;
+    const uint32_t smem_a = smem_base;
+    const uint32_t smem_b = smem_base + STAGES * L::kAStage;
+    const uint32_t bar_full = smem_base + L::kBarOffset;
+    const uint32_t bar_empty = bar_full + STAGES * 8;
+    const uint32_t bar_tfull = bar_empty + STAGES * 8;
+    const uint32_t bar_tempty = bar_tfull + 2 * 8;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kMiscOffset);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 4);
+
+    const int warp = static_cast<int>(threadIdx.x) >> 5;
+    const int lane = static_cast<int>(threadIdx.x) & 31;
+    const int total_work = p.m_tiles * p.n_tiles * p.splits;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(bar_full + s * 8, 1);
+            ptx::mbar_init(bar_empty + s * 8, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(bar_tfull + a * 8, 1);
+            ptx::mbar_init(bar_tempty + a * 8, 4);
+        }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+    }
+    if (warp == 0 && lane == 0) {
+        ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (ptx::elect_one()) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+                const TileCoord t = decode_tile(w, p);
+                const int kb0 = t.split * p.kb_per_split;
+                const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, p.status, ROLE_PRODUCER, kb)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t full = bar_full + stage * 8;
+                    ptx::mbar_arrive_expect_tx(full, L::kAStage + L::kBStage);
+                    ptx::tma_load_2d(smem_a + stage * L::kAStage, &tmap_a, full, kb * BK, t.m_blk * kBM);
+                    ptx::tma_load_2d(smem_b + stage * L::kBStage, &tmap_b, full, kb * BK, t.n_blk * BN);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (ptx::elect_one()) {
+            uint32_t stage = 0, phase = 0;
+            uint32_t it = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x, ++it) {
+                const TileCoord t = decode_tile(w, p);
+                const int kb0 = t.split * p.kb_per_split;
+                const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                const uint32_t acc = it & 1u;
+                const uint32_t acc_phase = (it >> 1) & 1u;
+                if (!wait_bounded(bar_tempty + acc * 8, acc_phase ^ 1u, abort_flag, p.status, ROLE_MMA, -1)) break;
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status, ROLE_MMA, kb)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint64_t a_desc = ptx::make_kmajor_sw128_desc(smem_a + stage * L::kAStage);
+                    const uint64_t b_desc = ptx::make_kmajor_sw128_desc(smem_b + stage * L::kBStage);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per 128-byte block
+                        ptx::umma_ss<KIND>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc,
+                                           (kb > kb0 || k > 0) ? 1u : 0u);
+                    }
+                    ptx::tc_commit(bar_empty + stage * 8);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) ptx::tc_commit(bar_tfull + acc * 8);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const int quad = warp & 3;  // tensor-memory lane quadrant this warp may read
+        float alpha = 1.0f;
+        if constexpr (OUT != OUT_RAW32) {
+            if (p.scale_a != nullptr) alpha *= __ldg(p.scale_a);
+            if (p.scale_b != nullptr) alpha *= __ldg(p.scale_b);
+        }
+        uint32_t it = 0;
+        for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++it) {
+            const TileCoord t = decode_tile(w, p);
+            const uint32_t acc = it & 1u;
+            const uint32_t acc_phase = (it >> 1) & 1u;
+            if (!wait_bounded(bar_tfull + acc * 8, acc_phase, abort_flag, p.status, ROLE_EPILOGUE, w)) break;
+            ptx::tc_fence_after();
+            const long long row = static_cast<long long>(t.m_blk) * kBM + quad * 32 + lane;
+            uint8_t* c_base = reinterpret_cast<uint8_t*>(p.C) +
+                              static_cast<long long>(t.split) * p.split_stride * OutBytes<OUT>::value;
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int n0 = t.n_blk * BN + c * 32;
+                if (n0 >= p.N) break;  // warp-uniform
+                uint32_t v[32];
+                ptx::tmem_ld_32x32b_x32(t_addr + c * 32, v);
+                ptx::tmem_ld_wait();
+                if (row < p.M)
+                    store_chunk<KIND, OUT>(c_base, p.ldc, row, n0, min(32, p.N - n0), p.c_vec_ok != 0, v, alpha);
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar_tempty + acc * 8);
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (*abort_flag != 0) {
+        // Let TMA copies and MMAs that were already issued finish before the memory they touch
+        // is released.
+        for (int i = 0; i < 64; ++i) __nanosleep(20000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace qgemm

@@ -1,0 +1,21 @@
+// Declarations shared by the translation units of libqgemm.so (not installed).
+#pragma once
+#include <cuda_runtime.h>
+#include <cstddef>
+#include <cstdint>
+
+#include "../../include/qgemm.h"
+
+namespace qgemm {
+
+int transpose_launch(const void* in, void* out, size_t rows, size_t cols, size_t ld_in, size_t ld_out,
+                     size_t elem_bytes, cudaStream_t stream);
+
+// Sums `splits` slabs of 32-bit partial accumulators (fp32, or int32 when acc_is_int) laid out as
+// [split][M][ldw] and writes cast(scale_a*scale_b*sum) (out_kind: OUT_F32/BF16/F16) or the raw sum
+// (OUT_RAW32) to C[M,N].
+int splitk_reduce_launch(const void* partials, long long split_stride, long long ldw, int splits, bool acc_is_int,
+                         void* C, long long ldc, int M, int N, int out_kind, const float* scale_a,
+                         const float* scale_b, cudaStream_t stream);
+
+}  // namespace qgemm

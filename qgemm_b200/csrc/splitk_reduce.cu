@@ -1,0 +1,126 @@
+// Second pass of split-K: a deterministic, fixed-order sum of the per-split partial accumulators
+// followed by the same scale + down-cast the fused epilogue applies. The reference only sketches
+// split-K (an unused `split_k` constant, src/gemm/sm89_gemm_kernel_v5.cu:319); int8 partials are
+// kept as int32 so the split path stays bit-exact.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "gemm_sm100.cuh"
+#include "qgemm_internal.h"
+
+namespace qgemm {
+
+namespace {
+
+template <bool ACC_INT>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const uint32_t* __restrict__ partials, long long split_stride, long long ldw, int splits,
+                     void* __restrict__ C, long long ldc, int M, int N, int out_kind,
+                     const float* __restrict__ scale_a, const float* __restrict__ scale_b, int c_vec_ok) {
+    const long long quads_per_row = ldw >> 2;
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= quads_per_row * M) return;
+    const long long row = idx / quads_per_row;
+    const int col = static_cast<int>(idx - row * quads_per_row) * 4;
+    if (col >= N) return;
+
+    const uint32_t* src = partials + row * ldw + col;
+    uint32_t raw[4];
+    float f[4];
+    if constexpr (ACC_INT) {
+        int s[4] = {0, 0, 0, 0};
+        for (int k = 0; k < splits; ++k) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(src + k * split_stride));
+            s[0] += static_cast<int>(v.x);
+            s[1] += static_cast<int>(v.y);
+            s[2] += static_cast<int>(v.z);
+            s[3] += static_cast<int>(v.w);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            raw[j] = static_cast<uint32_t>(s[j]);
+            f[j] = static_cast<float>(s[j]);
+        }
+    } else {
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int k = 0; k < splits; ++k) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(src + k * split_stride));
+            s[0] += __uint_as_float(v.x);
+            s[1] += __uint_as_float(v.y);
+            s[2] += __uint_as_float(v.z);
+            s[3] += __uint_as_float(v.w);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            raw[j] = __float_as_uint(s[j]);
+            f[j] = s[j];
+        }
+    }
+
+    const int n_valid = min(4, N - col);
+    if (out_kind == OUT_RAW32) {
+        uint32_t* dst = reinterpret_cast<uint32_t*>(C) + row * ldc + col;
+        if (c_vec_ok && n_valid == 4) {
+            *reinterpret_cast<uint4*>(dst) = make_uint4(raw[0], raw[1], raw[2], raw[3]);
+        } else {
+            for (int j = 0; j < n_valid; ++j) dst[j] = raw[j];
+        }
+        return;
+    }
+    float alpha = 1.0f;
+    if (scale_a != nullptr) alpha *= __ldg(scale_a);
+    if (scale_b != nullptr) alpha *= __ldg(scale_b);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) f[j] *= alpha;
+    if (out_kind == OUT_F32) {
+        float* dst = reinterpret_cast<float*>(C) + row * ldc + col;
+        if (c_vec_ok && n_valid == 4) {
+            *reinterpret_cast<float4*>(dst) = make_float4(f[0], f[1], f[2], f[3]);
+        } else {
+            for (int j = 0; j < n_valid; ++j) dst[j] = f[j];
+        }
+    } else {
+        uint16_t h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (out_kind == OUT_BF16) {
+                __nv_bfloat16 b = __float2bfloat16_rn(f[j]);
+                h[j] = *reinterpret_cast<uint16_t*>(&b);
+            } else {
+                __half b = __float2half_rn(f[j]);
+                h[j] = *reinterpret_cast<uint16_t*>(&b);
+            }
+        }
+        uint16_t* dst = reinterpret_cast<uint16_t*>(C) + row * ldc + col;
+        if (c_vec_ok && n_valid == 4) {
+            *reinterpret_cast<uint2*>(dst) =
+                make_uint2(h[0] | (static_cast<uint32_t>(h[1]) << 16), h[2] | (static_cast<uint32_t>(h[3]) << 16));
+        } else {
+            for (int j = 0; j < n_valid; ++j) dst[j] = h[j];
+        }
+    }
+}
+
+}  // namespace
+
+int splitk_reduce_launch(const void* partials, long long split_stride, long long ldw, int splits, bool acc_is_int,
+                         void* C, long long ldc, int M, int N, int out_kind, const float* scale_a,
+                         const float* scale_b, cudaStream_t stream) {
+    const int out_bytes = (out_kind == OUT_BF16 || out_kind == OUT_F16) ? 2 : 4;
+    const int c_vec_ok = (reinterpret_cast<uintptr_t>(C) % 16 == 0) && ((ldc * out_bytes) % 16 == 0);
+    const long long total = (ldw >> 2) * M;
+    const int threads = 256;
+    const long long blocks = (total + threads - 1) / threads;
+    if (blocks <= 0) return QGEMM_OK;
+    if (blocks > 0x7fffffffLL) return QGEMM_ERR_UNSUPPORTED;
+    const uint32_t* p = reinterpret_cast<const uint32_t*>(partials);
+    if (acc_is_int)
+        splitk_reduce_kernel<true><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
+            p, split_stride, ldw, splits, C, ldc, M, N, out_kind, scale_a, scale_b, c_vec_ok);
+    else
+        splitk_reduce_kernel<false><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
+            p, split_stride, ldw, splits, C, ldc, M, N, out_kind, scale_a, scale_b, c_vec_ok);
+    return cudaGetLastError() == cudaSuccess ? QGEMM_OK : QGEMM_ERR_CUDA;
+}
+
+}  // namespace qgemm
