@@ -1,0 +1,86 @@
+"""Host-side checks that need no GPU: the C-ABI library loads, exports every symbol the public
+header declares, and its argument validation / planning logic behaves. No compute is launched."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "qgemm.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(qgemm_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(qlib):
+    declared = _declared_symbols()
+    assert set(declared) == set(qlib.C_ABI_SYMBOLS)
+    L = C.CDLL(qlib.LIB_PATH)
+    for sym in declared:
+        assert hasattr(L, sym), sym
+
+
+def test_version_and_status_strings(qlib):
+    L = qlib.lib()
+    assert L.qgemm_version() >= 100
+    seen = set()
+    for code in range(7):
+        s = qlib.status_string(code)
+        assert s and s != "unknown status"
+        seen.add(s)
+    assert len(seen) == 7
+    assert qlib.status_string(12345) == "unknown status"
+
+
+def test_empty_problem_is_ok_without_touching_the_device(qlib):
+    L = qlib.lib()
+    assert L.qgemm_gemm(qlib.BF16, qlib.FP32, qlib.B_K_MAJOR, None, 0, None, 0, None, 0, 0, 128, 64, None) == qlib.OK
+    assert L.qgemm_gemm(qlib.BF16, qlib.FP32, qlib.B_K_MAJOR, None, 0, None, 0, None, 0, 128, 0, 64, None) == qlib.OK
+    assert L.qgemm_transpose(None, None, 0, 0, 0, 0, 2, None) == qlib.OK
+
+
+def test_argument_validation_precedes_any_launch(qlib):
+    L = qlib.lib()
+    # null output / ld too small
+    assert L.qgemm_gemm(qlib.BF16, qlib.FP32, qlib.B_K_MAJOR, 16, 64, 16, 64, None, 128, 128, 128, 64, None) \
+        == qlib.ERR_INVALID_ARG
+    assert L.qgemm_gemm(qlib.BF16, qlib.FP32, qlib.B_K_MAJOR, 16, 64, 16, 64, 16, 64, 128, 128, 64, None) \
+        == qlib.ERR_INVALID_ARG
+    assert L.qgemm_gemm(qlib.BF16, qlib.FP32, qlib.B_K_MAJOR, 16, 32, 16, 64, 16, 128, 128, 128, 64, None) \
+        == qlib.ERR_INVALID_ARG
+    # dtype pairs the plain entry point does not take
+    assert L.qgemm_gemm(qlib.FP8_E4M3, qlib.BF16, qlib.B_K_MAJOR, 16, 64, 16, 64, 16, 128, 128, 128, 64, None) \
+        == qlib.ERR_UNSUPPORTED
+    assert L.qgemm_mix_gemm(qlib.INT8, qlib.INT32, qlib.B_K_MAJOR, 16, 64, 16, 64, None, None, 16, 128, 128, 128, 64,
+                            None) == qlib.ERR_UNSUPPORTED
+    assert L.qgemm_transpose(16, 32, 8, 8, 8, 8, 4, None) == qlib.ERR_UNSUPPORTED
+    assert L.qgemm_transpose(16, 32, 8, 8, 4, 8, 2, None) == qlib.ERR_INVALID_ARG
+
+
+def test_compute_without_a_gpu_fails_loudly(qlib):
+    """There is no CPU fallback: on a machine without CUDA a real call returns an error code."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("this check is for machines without a GPU")
+    L = qlib.lib()
+    rc = L.qgemm_gemm(qlib.BF16, qlib.FP32, qlib.B_K_MAJOR, 1024, 64, 2048, 64, 4096, 128, 128, 128, 64, None)
+    assert rc in (qlib.ERR_CUDA, qlib.ERR_UNSUPPORTED)
+    with pytest.raises(qlib.QgemmError):
+        qlib.gemm(torch.zeros(8, 8, dtype=torch.bfloat16), torch.zeros(8, 8, dtype=torch.bfloat16),
+                  torch.zeros(8, 8))
+
+
+def test_workspace_planning(qlib):
+    # row-major B needs a relaid-out copy: N * round_up(K, 8) * 2 bytes for bf16
+    assert qlib.workspace_query(qlib.BF16, qlib.B_ROW_MAJOR, 8192, 8192, 8192) == 8192 * 8192 * 2
+    assert qlib.workspace_query(qlib.BF16, qlib.B_K_MAJOR, 8192, 8192, 8192) == 0
+    # an explicit split-K adds splits * M * round_up(N, 4) * 4 bytes of partial sums
+    t = qlib.Tuning(128, 4, 0, 0)
+    assert qlib.workspace_query(qlib.INT8, qlib.B_K_MAJOR, 100, 518, 2048, t) == 4 * 100 * 520 * 4
+    # more splits than 128-byte K blocks cannot be honoured: the plan falls back to what exists
+    t = qlib.Tuning(128, 64, 0, 0)
+    assert qlib.workspace_query(qlib.INT8, qlib.B_K_MAJOR, 128, 128, 256, t) <= 2 * 128 * 128 * 4
+    assert qlib.workspace_query(qlib.BF16, qlib.B_K_MAJOR, 0, 8, 8) == 0

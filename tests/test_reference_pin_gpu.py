@@ -1,0 +1,59 @@
+"""Live three-way check on the GPU: the reference project's own kernels (oracle/_ref, built from the
+reference sources by oracle/build_ref.sh) vs the CPU oracle vs this library, on the same inputs."""
+import numpy as np
+import pytest
+import torch
+
+from qgemm_b200 import datagen
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ref_gpu():
+    from oracle import ref_gpu as r
+    if not r.available():
+        pytest.skip("oracle/_ref/libqgemm_ref.so not built (needs the reference sources at build time)")
+    return r
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 128, 192), (1024, 1024, 1024), (512, 2048, 4096)])
+@pytest.mark.parametrize("version", ["v1", "v3", "v4"])
+def test_reference_kernels_agree_with_oracle_and_library(qlib, oracle, ref_gpu, dev, M, N, K, version):
+    a32 = datagen.normal((M, K), seed=K, stream=0)
+    b32 = datagen.normal((K, N), seed=K, stream=1)
+    a = torch.from_numpy(a32).to(dev).to(torch.bfloat16)
+    b = torch.from_numpy(b32).to(dev).to(torch.bfloat16)
+    c_ref = torch.zeros((M, N), dtype=torch.float32, device=dev)
+    ref_gpu.gemm(version, a, b, c_ref)
+    c_ours = torch.zeros((M, N), dtype=torch.float32, device=dev)
+    qlib.gemm(a, b, c_ours, b_kmajor=False)
+    torch.cuda.synchronize()
+    ref = c_ref.cpu().numpy()
+    ours = c_ours.cpu().numpy()
+    assert oracle.rel_l2(ours, ref) <= 1e-5
+    if M * N * K <= 2 ** 30:
+        _, a_val = oracle.round_bf16(a32)
+        _, b_val = oracle.round_bf16(b32)
+        cpu = oracle.gemm_f32(a_val, b_val, False)
+        assert oracle.rel_l2(cpu, ref) <= 1e-5
+        assert oracle.rel_l2(ours, cpu) <= 1e-5
+
+
+def test_reference_kmajor_kernel(qlib, oracle, ref_gpu, dev):
+    """GEMM_kernel_v3_1 consumes B as [N,K]; it matches GEMM_kernel_kmajor semantics here."""
+    M, N, K = 512, 256, 320
+    a = torch.from_numpy(datagen.normal((M, K), seed=1, stream=0)).to(dev).to(torch.bfloat16)
+    bk = torch.from_numpy(datagen.normal((N, K), seed=1, stream=1)).to(dev).to(torch.bfloat16)
+    c_ref = torch.zeros((M, N), dtype=torch.float32, device=dev)
+    ref_gpu.gemm("v3_1", a, bk, c_ref)
+    c_ours = torch.zeros((M, N), dtype=torch.float32, device=dev)
+    qlib.gemm(a, bk, c_ours, b_kmajor=True)
+    assert oracle.rel_l2(c_ours.cpu().numpy(), c_ref.cpu().numpy()) <= 1e-5
+
+
+def test_reference_transpose_kernel(qlib, ref_gpu, dev):
+    x = torch.randn((1024, 2048), device=dev).to(torch.bfloat16)
+    y_ref = torch.zeros((2048, 1024), dtype=torch.bfloat16, device=dev)
+    ref_gpu.transpose(x, y_ref)
+    assert torch.equal(qlib.transpose(x), y_ref)
