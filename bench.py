@@ -1,0 +1,474 @@
+#!/usr/bin/env python
+"""Benchmark of the GEMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Default workload (N = 1): the BF16 configuration -- M = N = K = 8192, A and B both row-major (so B
+goes through the relayout kernel), fp32 accumulate, bf16 output, seeded normal(0,1) inputs. One
+"step" is one pass of the hot path (relayout + GEMM) over that problem. With N > 1 (launched by
+torch.distributed.run, one rank per GPU) every rank runs its own column block of the same width:
+the global problem is M x (N*8192) x K column-sharded over the ranks, with no data-path
+collective, i.e. weak scaling. `value` is whole-job TFLOPS = ranks * 2*M*N*K / max-over-ranks time.
+
+Prints ONE JSON line on rank 0 with the throughput of device-resident operands (`value`), the same
+metric through the host-buffer call with both copies inside the timed region (`e2e`), the live
+roofline of the dominant kernel, SM clocks sampled during the timed regions, and -- at N = 1 -- the
+CPU baseline (the CPU restatement of the reference semantics; the reference ships no CPU GEMM).
+
+`--impl reference` times that CPU restatement alone (rank 0 only), on a bounded row band per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# DRAM traffic per launch of the dominant kernel, from the ncu capture summarised under profiles/
+# (bytes; None until measured). Keyed by workload.
+NCU_TRAFFIC_BYTES = {}
+
+NOMINAL_PEAK_TFLOPS = {"bf16": 2250.0, "fp16": 2250.0, "int8": 4500.0, "fp8": 4500.0}
+
+WORKLOADS = {
+    # name: (in, out, M, N, K, b_kmajor, description)
+    "c2_bf16_8192": ("bf16", "bf16", 8192, 8192, 8192, False,
+                     "BF16 GEMM M=N=K=8192, A,B row-major (B relaid out to K-major), fp32 acc, bf16 out"),
+    "c1_fp16_1024": ("fp16", "fp32", 1024, 1024, 1024, True,
+                     "FP16 GEMM M=N=K=1024, B col-major [K,N], uniform[-1,1) seed 0, fp32 out"),
+    "c3_int8_8192": ("int8", "bf16", 8192, 8192, 8192, True,
+                     "int8 mixed GEMM M=N=K=8192, per-matrix scales, int32 acc, bf16 out"),
+    "c4_fp8_16": ("fp8", "bf16", 16, 7168, 2048, True, "FP8 e4m3 M=16 N=7168 K=2048, per-matrix scales, bf16 out"),
+    "c4_fp8_64": ("fp8", "bf16", 64, 7168, 2048, True, "FP8 e4m3 M=64 N=7168 K=2048"),
+    "c4_fp8_256": ("fp8", "bf16", 256, 7168, 2048, True, "FP8 e4m3 M=256 N=7168 K=2048"),
+    "c4_fp8_1024": ("fp8", "bf16", 1024, 7168, 2048, True, "FP8 e4m3 M=1024 N=7168 K=2048"),
+    "c4_fp8_6144": ("fp8", "bf16", 6144, 7168, 2048, True, "FP8 e4m3 M=6144 N=7168 K=2048"),
+    "c5_int8_sharded": ("int8", "bf16", 32768, 32768, 8192, True,
+                        "int8 mixed GEMM 32768x32768x8192, B/C column-sharded over the ranks (strong scaling)"),
+}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2_bf16_8192", choices=sorted(WORKLOADS))
+    ap.add_argument("--seed", type=int, default=2)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", action="store_true", help="c5: also time the all-gather of the C slices")
+    ap.add_argument("--tile-n", type=int, default=0)
+    ap.add_argument("--split-k", type=int, default=0)
+    ap.add_argument("--group-m", type=int, default=0)
+    return ap.parse_args()
+
+
+# ------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) while active."""
+
+    def __init__(self, torch_device_index: int):
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._active = threading.Event()
+        self._thread = None
+        self._h = None
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(torch_device_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            try:
+                self._h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self._h = pynvml.nvmlDeviceGetHandleByIndex(torch_device_index)
+            self._nv = pynvml
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._h = None
+
+    _REASONS = {
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+        0x80: "hw_power_brake_slowdown",
+    }
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            if self._active.is_set():
+                try:
+                    self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)) if hasattr(
+                        nv, "nvmlDeviceGetCurrentClocksEventReasons") else int(
+                        nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+                    for bit, name in self._REASONS.items():
+                        if mask & bit:
+                            self.reasons.add(name)
+                except Exception:
+                    pass
+            time.sleep(0.004)
+
+    def start(self):
+        if self._h is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def region(self, on: bool):
+        (self._active.set if on else self._active.clear)()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=1.0)
+
+    def summary(self):
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+# ------------------------------------------------------------------------------------ CPU arm
+class CpuArm:
+    """The CPU restatement of the reference semantics (the reference ships no CPU GEMM) on this
+    workload's operands: prepared once, then timed on row bands."""
+
+    def __init__(self, workload: str, seed: int):
+        from oracle import oracle as o
+        from qgemm_b200 import datagen
+        in_name, _, M, N, K, _, _ = WORKLOADS[workload]
+        self.N = min(N, 8192)  # one rank's column block of the sharded workload, at most this wide
+        self.K = K
+        rows = min(M, 8192)
+        self.threads = o.num_threads()
+        if in_name == "int8":
+            self.bt = datagen.int8_uniform((self.N, K), seed, 1)
+            self.a = datagen.int8_uniform((rows, K), seed, 0)
+            self.fn = o.gemm_i8_blocked
+        else:
+            bt = datagen.normal((self.N, K), seed, 1)
+            a = datagen.normal((rows, K), seed, 0)
+            rnd = {"bf16": lambda x: o.round_bf16(x)[1], "fp16": lambda x: o.round_f16(x)[1],
+                   "fp8": lambda x: o.quantize_e4m3(x)[1]}[in_name]
+            self.bt, self.a = rnd(bt), rnd(a)
+            self.fn = o.gemm_f32_blocked
+
+    def run(self, rows: int):
+        """Returns (seconds, flop) for rows [0, rows)."""
+        rows = min(rows, self.a.shape[0])
+        t0 = time.perf_counter()
+        self.fn(self.a[:rows], self.bt)
+        return time.perf_counter() - t0, 2.0 * rows * self.N * self.K
+
+    def calibrate(self, target_seconds: float) -> int:
+        probe = min(96, self.a.shape[0])
+        dt, _ = self.run(probe)
+        rows = int(probe * target_seconds / max(dt, 1e-6))
+        rows = max(48, rows // 48 * 48)
+        return min(rows, self.a.shape[0])
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    in_name, out_name, M, N, K, b_kmajor, desc = WORKLOADS[args.workload]
+    arm = CpuArm(args.workload, args.seed)
+    # size the per-step band so that the whole run stays within about a minute of GEMM time
+    rows = arm.calibrate(60.0 / max(1, args.steps + args.warmup))
+    for _ in range(args.warmup):
+        arm.run(rows)
+    t_total, flops = 0.0, 0.0
+    for _ in range(args.steps):
+        dt, fl = arm.run(rows)
+        t_total += dt
+        flops += fl
+    value = flops / t_total / 1e12
+    sample = (f"rows 0..{rows} x {arm.N} columns x K={K} of the workload per step, blocked OpenMP "
+              f"{'int32' if in_name == 'int8' else 'fp32'} GEMM")
+    line = {
+        "impl": "reference", "metric": "gemm_tflops", "value": value, "unit": "TFLOPS", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_total / max(1, args.steps),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32" if in_name != "int8" else "int32", "data": "synthetic",
+        "config": {"workload": args.workload, "description": desc,
+                   "note": "the reference ships no CPU GEMM; this is the CPU restatement of its semantics"},
+        "cpu_baseline": {"value": value, "unit": "TFLOPS", "cores": arm.threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------ GPU arm
+def make_operands(workload, seed, rank, world, torch, dev):
+    """Host (pinned) and device operands of this rank. Returns a dict."""
+    import numpy as np
+    from qgemm_b200 import datagen
+    in_name, out_name, M, N, K, b_kmajor, _ = WORKLOADS[workload]
+    tdt = {"bf16": torch.bfloat16, "fp16": torch.float16, "int8": torch.int8, "fp8": torch.float8_e4m3fn}[in_name]
+    odt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[out_name]
+    if workload == "c5_int8_sharded":
+        n0 = rank * (N // world)
+        N = N // world
+    sa = sb = None
+    b_stream = 1 + 1000 * rank  # each rank owns different columns of B
+    if in_name == "int8":
+        a_h = torch.from_numpy(datagen.int8_uniform((M, K), seed, 0))
+        b_h = torch.from_numpy(datagen.int8_uniform((N, K) if b_kmajor else (K, N), seed, b_stream))
+        s0, s1 = datagen.scale_pair(seed)
+        sa, sb = torch.tensor([s0], device=dev), torch.tensor([s1], device=dev)
+    elif in_name == "fp8":
+        a32 = torch.from_numpy(datagen.normal((M, K), seed, 0))
+        b32 = torch.from_numpy(datagen.normal((N, K) if b_kmajor else (K, N), seed, b_stream))
+        s0 = a32.abs().max() / 448.0
+        s1 = b32.abs().max() / 448.0
+        a_h = (a32 / s0).to(torch.float8_e4m3fn)
+        b_h = (b32 / s1).to(torch.float8_e4m3fn)
+        sa, sb = s0.reshape(1).to(dev), s1.reshape(1).to(dev)
+    else:
+        gen = datagen.uniform if workload == "c1_fp16_1024" else datagen.normal
+        a_h = torch.from_numpy(gen((M, K), seed, 0)).to(tdt)
+        b_h = torch.from_numpy(gen((N, K) if b_kmajor else (K, N), seed, b_stream)).to(tdt)
+    a_h, b_h = a_h.pin_memory(), b_h.pin_memory()
+    c_h = torch.empty((M, N), dtype=odt).pin_memory()
+    return dict(M=M, N=N, K=K, a_h=a_h, b_h=b_h, c_h=c_h, a=a_h.to(dev), b=b_h.to(dev),
+                c=torch.empty((M, N), dtype=odt, device=dev), sa=sa, sb=sb, b_kmajor=b_kmajor, in_dtype=tdt,
+                out_dtype=odt)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import qgemm_b200 as q
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    q.lib()  # fail loudly here if the CUDA library is missing
+
+    in_name, out_name, M0, N0, K0, _, desc = WORKLOADS[args.workload]
+    ops = make_operands(args.workload, args.seed, rank, world, torch, dev)
+    M, N, K = ops["M"], ops["N"], ops["K"]
+    tuning = None
+    if args.tile_n or args.split_k or args.group_m:
+        tuning = q.Tuning(args.tile_n, args.split_k, args.group_m, 0)
+    mixed = ops["sa"] is not None
+
+    def call_device():
+        q._gemm(ops["a"], ops["b"], ops["sa"], ops["sb"], ops["c"], ops["b_kmajor"], tuning, mixed)
+
+    # scratch is reserved before any timed region
+    q.workspace_reserve(q.workspace_query({"bf16": q.BF16, "fp16": q.FP16, "int8": q.INT8, "fp8": q.FP8_E4M3}[in_name],
+                                          q.B_K_MAJOR if ops["b_kmajor"] else q.B_ROW_MAJOR, M, N, K, tuning))
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    # ---------------- value: device-resident operands, the public call
+    for _ in range(max(args.warmup, 3)):
+        call_device()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.region(True)
+    e0.record()
+    for _ in range(args.steps):
+        call_device()
+    e1.record()
+    torch.cuda.synchronize()
+    sampler.region(False)
+    barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    ms_per_step = ms_total / args.steps
+    flop_per_step_rank = 2.0 * M * N * K
+    value = world * flop_per_step_rank / (ms_per_step * 1e-3) / 1e12
+    launches_per_step = 1 + (0 if ops["b_kmajor"] else 1)
+    ws_partials = q.workspace_query({"bf16": q.BF16, "fp16": q.FP16, "int8": q.INT8, "fp8": q.FP8_E4M3}[in_name],
+                                    q.B_K_MAJOR, M, N, K, tuning)
+    if ws_partials > 0:
+        launches_per_step += 1  # split-K second pass
+
+    # ---------------- roofline of the dominant kernel: the GEMM kernel alone (K-major operands), per-launch events
+    if ops["b_kmajor"]:
+        b_k = ops["b"]
+    else:
+        b_k = q.transpose(ops["b"])
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for _ in range(3):
+        q._gemm(ops["a"], b_k, ops["sa"], ops["sb"], ops["c"], True, tuning, mixed)
+    torch.cuda.synchronize()
+    sampler.region(True)
+    for s, e in evs:
+        s.record()
+        q._gemm(ops["a"], b_k, ops["sa"], ops["sb"], ops["c"], True, tuning, mixed)
+        e.record()
+    torch.cuda.synchronize()
+    sampler.region(False)
+    gemm_ms = sum(s.elapsed_time(e) for s, e in evs) / len(evs)
+    achieved_tflops = flop_per_step_rank / (gemm_ms * 1e-3) / 1e12
+    es_in = 2 if in_name in ("bf16", "fp16") else 1
+    es_out = {"bf16": 2, "fp16": 2, "fp32": 4}[out_name]
+    alg_bytes = M * K * es_in + N * K * es_in + M * N * es_out
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    ridge_bound = "tensor"
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    hbm_src = "measured" if "hbm_gbs" in peaks else "fallback"
+    intensity = flop_per_step_rank / alg_bytes
+    if in_name in ("bf16", "fp16"):
+        tensor_peak = float(peaks.get("bf16_tflops", 1590.0))
+        peak_src = "measured cuBLAS bf16 burst" if "bf16_tflops" in peaks else "fallback 1590"
+    else:
+        tensor_peak = NOMINAL_PEAK_TFLOPS[in_name]
+        peak_src = "nominal dense peak (no measured 8-bit figure exists on this pool)"
+    if intensity < tensor_peak * 1e12 / (hbm_peak * 1e9):
+        ridge_bound = "hbm"
+    if ridge_bound == "tensor":
+        roofline = {"bound": "tensor", "achieved": achieved_tflops, "peak": tensor_peak, "unit": "TFLOP/s",
+                    "frac": achieved_tflops / tensor_peak, "peak_source": peak_src,
+                    "frac_of_nominal": achieved_tflops / NOMINAL_PEAK_TFLOPS[in_name]}
+    else:
+        gbs = alg_bytes / (gemm_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
+                    "peak_source": hbm_src + " copy bandwidth"}
+    roofline.update({"kernel": "gemm_tcgen05_kernel", "kernel_ms": gemm_ms, "algorithmic_flop": flop_per_step_rank,
+                     "algorithmic_bytes": alg_bytes, "traffic": NCU_TRAFFIC_BYTES.get(args.workload)})
+
+    # the relayout kernel on its own (HBM-bound), when the workload uses it
+    relayout = None
+    if not ops["b_kmajor"]:
+        bt = torch.empty((N, K), dtype=ops["in_dtype"], device=dev)
+        for _ in range(3):
+            q.transpose(ops["b"], bt)
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(10, args.steps)
+        t0.record()
+        for _ in range(reps):
+            q.transpose(ops["b"], bt)
+        t1.record()
+        torch.cuda.synchronize()
+        tms = t0.elapsed_time(t1) / reps
+        tbytes = 2.0 * N * K * es_in
+        relayout = {"kernel": "transpose_kernel", "kernel_ms": tms, "achieved": tbytes / (tms * 1e-3) / 1e9,
+                    "peak": hbm_peak, "unit": "GB/s", "frac": tbytes / (tms * 1e-3) / 1e9 / hbm_peak,
+                    "peak_source": hbm_src + " copy bandwidth", "algorithmic_bytes": tbytes}
+
+    # ---------------- e2e: host buffers through the host-level call, copies inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        from qgemm_b200.host_api import HostGemm
+        hg = HostGemm(M, N, K, ops["in_dtype"], ops["out_dtype"], ops["b_kmajor"], dev)
+        e2e_steps = max(3, min(args.steps, 20))
+        for _ in range(3):
+            hg(ops["a_h"], ops["b_h"], ops["c_h"], ops["sa"], ops["sb"])
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sampler.region(True)
+        s0.record()
+        for _ in range(e2e_steps):
+            hg(ops["a_h"], ops["b_h"], ops["c_h"], ops["sa"], ops["sb"])
+        s1.record()
+        torch.cuda.synchronize()
+        sampler.region(False)
+        barrier()
+        e2e_ms = max_over_ranks(s0.elapsed_time(s1)) / e2e_steps
+        # the host result of the last step is the device result
+        check = bool(torch.equal(ops["c_h"][:64].to(dev), hg.c[:64]))
+        e2e = {"value": world * flop_per_step_rank / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS",
+               "h2d_bytes_per_step": hg.h2d_bytes, "d2h_bytes_per_step": hg.d2h_bytes, "ms_per_step": e2e_ms,
+               "steps": e2e_steps, "kernel_launches_per_step": hg.kernel_launches_per_call,
+               "result_roundtrip_ok": check}
+
+    # ---------------- c5: optional all-gather of the C slices (timed separately)
+    gather = None
+    if args.gather and world > 1:
+        from qgemm_b200 import sharding
+        for _ in range(2):
+            sharding.all_gather_slabs(ops["c"])
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(5):
+            sharding.all_gather_slabs(ops["c"])
+        g1.record()
+        torch.cuda.synchronize()
+        gms = max_over_ranks(g0.elapsed_time(g1)) / 5
+        gather = {"ms": gms, "bytes_received_per_rank": ops["c"].numel() * ops["c"].element_size() * (world - 1)}
+
+    sampler.stop()
+    rc, st = q.device_status()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        arm = CpuArm(args.workload, args.seed)
+        rows = arm.calibrate(12.0)
+        dt, fl = arm.run(rows)
+        cpu = {"value": fl / dt / 1e12, "unit": "TFLOPS", "cores": arm.threads, "kind": "port",
+               "sample": f"rows 0..{rows} of the workload ({dt:.1f} s), blocked OpenMP GEMM restating the reference "
+                         "semantics (the reference ships no CPU GEMM)"}
+
+    if rank == 0:
+        line = {
+            "metric": "gemm_tflops", "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong" if args.workload == "c5_int8_sharded" else "weak", "vs_baseline": None,
+            "dtype": in_name, "data": "synthetic",
+            "config": {"workload": args.workload, "description": desc, "per_rank_shape": [M, N, K],
+                       "l2": "inputs_larger_than_l2" if alg_bytes > 126e6 else "operands fit in L2 (latency config)",
+                       "seed": args.seed, "sharding": f"columns of B/C over {world} rank(s), no data-path collective"},
+            "per_gpu_tflops": value / world,
+            "frac_of_nominal_dense_peak": value / world / NOMINAL_PEAK_TFLOPS[in_name],
+            "roofline": roofline, "clocks": sampler.summary(), "e2e": e2e,
+            "gpu_launches": launches_per_step * args.steps, "cpu_baseline": cpu, "device_status": st if rc else 0,
+        }
+        if relayout is not None:
+            line["relayout_roofline"] = relayout
+        if gather is not None:
+            line["all_gather"] = gather
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

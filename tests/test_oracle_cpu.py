@@ -161,8 +161,14 @@ def test_oracle_matches_reference_kernels(oracle, golden):
 
 
 def test_reference_variants_agree(golden):
-    assert float(golden["v4_max_abs_diff_v3"]) < 1e-3
+    """v1 (WMMA), v2 (cp.async), v3 (mma.sync) and v3_1 (K-major B) of the reference give the same
+    result on the same inputs, so pinning against v1 and v3 pins against all four. The reference's
+    v4 does not agree with them (its recorded deviation is as large as the outputs): it is a defect
+    of that kernel, recorded in the fixture and not used as a pin."""
+    assert bool(golden["v2_equals_v1"])
     assert float(golden["v3_1_max_abs_diff_v3"]) < 1e-3
+    assert np.array_equal(golden["c_v1"], golden["c_v3"]) or np.max(np.abs(golden["c_v1"] - golden["c_v3"])) < 1e-3
+    assert float(golden["v4_max_abs_diff_v3"]) > 1.0
 
 
 def test_oracle_transpose_matches_reference_kernel(oracle, golden):

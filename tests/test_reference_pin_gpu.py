@@ -8,6 +8,10 @@ from qgemm_b200 import datagen
 
 pytestmark = pytest.mark.gpu
 
+# The reference's sm89 GEMM_kernel_v4 (2-stage pipeline) is left out on purpose: run on the same
+# inputs it disagrees with the reference's own v1/v2/v3/v3_1 (which agree with each other bit for
+# bit) by errors as large as the values themselves -- see v4_max_abs_diff_v3 in the golden fixture.
+
 
 @pytest.fixture(scope="module")
 def ref_gpu():
@@ -18,7 +22,7 @@ def ref_gpu():
 
 
 @pytest.mark.parametrize("M,N,K", [(512, 128, 192), (1024, 1024, 1024), (512, 2048, 4096)])
-@pytest.mark.parametrize("version", ["v1", "v3", "v4"])
+@pytest.mark.parametrize("version", ["v1", "v2", "v3"])
 def test_reference_kernels_agree_with_oracle_and_library(qlib, oracle, ref_gpu, dev, M, N, K, version):
     a32 = datagen.normal((M, K), seed=K, stream=0)
     b32 = datagen.normal((K, N), seed=K, stream=1)
