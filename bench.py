@@ -31,9 +31,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# DRAM traffic per launch of the dominant kernel, from the ncu capture summarised under profiles/
-# (bytes; None until measured). Keyed by workload.
-NCU_TRAFFIC_BYTES = {}
+# DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum), from the
+# ncu capture summarised in profiles/gemm_tcgen05_bf16_8192_cta1.md. Keyed by workload; None where no
+# capture of that workload exists.
+NCU_TRAFFIC_BYTES = {"c2_bf16_8192": 1.017461e9 + 126.353e6}
 
 NOMINAL_PEAK_TFLOPS = {"bf16": 2250.0, "fp16": 2250.0, "int8": 4500.0, "fp8": 4500.0}
 
