@@ -115,6 +115,31 @@ size_t qgemm_workspace_query(int in_dtype, int b_layout, size_t M, size_t N, siz
  */
 int qgemm_device_status(int* out4);
 
+/*
+ * Split-K mixed GEMM that allocates nothing. It has no counterpart in the reference; it exists for
+ * callers that cannot allocate device memory where they need the product -- real-time loops that must not
+ * risk the device-wide synchronisation an allocation can imply, embedders whose memory budget is fixed at
+ * start-up, and processes in which another allocator already owns all of the GPU's memory so that a
+ * cudaMalloc made here would fail. Same result as qgemm_gemm_ex with
+ * tuning {tile_n = 128, split_k}, bit for bit, but the partial sums live in a fixed array inside the
+ * loaded module (QGEMM_STATIC_SCRATCH_BYTES, held by every GPU that loads the library until the process
+ * exits) instead of the library's growable scratch, and no cudaMalloc / cudaFree or other allocating
+ * routine is called.
+ *   A [M,K] and B [N,K] (K-major only), both 16-byte aligned with 16-byte-multiple leading dimensions;
+ *   dtypes as qgemm_mix_gemm, plus INT8 -> INT32 with both scales NULL; 2 <= split_k <= ceil(K*sizeof(T)/128).
+ *   Needs split_k * M * round_up(N,4) * 4 bytes of the fixed array: a larger problem is rejected with
+ *   QGEMM_ERR_WORKSPACE before anything is launched.
+ * The first call on a device resolves the array's device address (cudaGetSymbolAddress) and configures the
+ * kernel; make that first call before starting any stream capture. All calls on a device share the one
+ * array, which keeps the previous call's partial sums (none of them needs clearing: each call overwrites
+ * what it later reads), so calls that overlap on the GPU (for example on different streams with no
+ * ordering between them) race with each other and must be serialised by the caller.
+ */
+#define QGEMM_STATIC_SCRATCH_BYTES (32u << 20)
+int qgemm_mix_gemm_splitk_static(int in_dtype, int out_dtype, const void* A, size_t lda, const void* B, size_t ldb,
+                                 const float* scale_a, const float* scale_b, void* C, size_t ldc, size_t M, size_t N,
+                                 size_t K, int split_k, qgemm_stream_t stream);
+
 /* Frees the scratch and cached descriptors of every device (blas::blas_destroy() calls this). */
 int qgemm_shutdown(void);
 

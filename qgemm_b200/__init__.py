@@ -26,7 +26,7 @@ B_ROW_MAJOR, B_K_MAJOR = 0, 1
 C_ABI_SYMBOLS = (
     "qgemm_gemm", "qgemm_mix_gemm", "qgemm_gemm_ex", "qgemm_transpose", "qgemm_workspace_reserve",
     "qgemm_workspace_bytes", "qgemm_workspace_query", "qgemm_device_status", "qgemm_shutdown",
-    "qgemm_status_string", "qgemm_version",
+    "qgemm_status_string", "qgemm_version", "qgemm_mix_gemm_splitk_static",
 )
 
 
@@ -64,6 +64,8 @@ def lib() -> C.CDLL:
         L.qgemm_device_status.argtypes = [C.POINTER(C.c_int)]
         L.qgemm_status_string.argtypes = [i]
         L.qgemm_status_string.restype = C.c_char_p
+        L.qgemm_mix_gemm_splitk_static.argtypes = [i, i, vp, sz, vp, sz, fp, fp, vp, sz, sz, sz, sz, i, vp]
+        L.qgemm_mix_gemm_splitk_static.restype = i
         for name in ("qgemm_gemm", "qgemm_mix_gemm", "qgemm_gemm_ex", "qgemm_transpose", "qgemm_workspace_reserve",
                      "qgemm_device_status", "qgemm_shutdown", "qgemm_version"):
             getattr(L, name).restype = i
@@ -163,6 +165,32 @@ def fp8_mm(a, b, a_scale, b_scale, c) -> None:
     """fp8-e4m3 a [m,k], b [n,k], per-matrix float32 scales -> c [m,n]
     (src/mix_gemm/hip_mix_gemm_kernel.cpp:508-516; per-matrix instead of block scales)."""
     _gemm(a, b, a_scale, b_scale, c, True, None, mixed=True)
+
+
+STATIC_SCRATCH_BYTES = 32 << 20  # QGEMM_STATIC_SCRATCH_BYTES
+
+
+def mix_gemm_splitk_static(a, b, scale_a, scale_b, c, split_k: int) -> None:
+    """Split-K GEMM through the entry point that never allocates (for callers that cannot call
+    cudaMalloc where they need the product: fixed-budget embedders, loops that must not risk a
+    device-wide synchronisation, processes whose GPU memory is already owned by another allocator).
+    a [M,K], b [N,K] K-major; partial sums live in a fixed ``STATIC_SCRATCH_BYTES`` array inside the
+    library, so ``split_k * M * round_up(N, 4) * 4`` must fit in it and calls that overlap on the GPU
+    must be serialised by the caller. Bit-identical to ``mix_gemm(..., tuning=Tuning(128, split_k, 0, 0))``."""
+    torch = _torch()
+    for name, t in (("a", a), ("b", b), ("c", c)):
+        _require_cuda_2d(name, t)
+    M, K = a.shape
+    N = b.shape[0]
+    if b.shape[1] != K or tuple(c.shape) != (M, N) or a.dtype != b.dtype:
+        raise QgemmError(ERR_INVALID_ARG, "shape or dtype mismatch")
+    sa = scale_a.data_ptr() if scale_a is not None else None
+    sb = scale_b.data_ptr() if scale_b is not None else None
+    with torch.cuda.device(a.device):
+        rc = lib().qgemm_mix_gemm_splitk_static(
+            _dtype_code(a), _dtype_code(c), a.data_ptr(), max(a.stride(0), K), b.data_ptr(), max(b.stride(0), K),
+            sa, sb, c.data_ptr(), max(c.stride(0), N), M, N, K, int(split_k), _stream_ptr(a))
+    _check(rc, "qgemm_mix_gemm_splitk_static")
 
 
 def transpose(x, out=None):
