@@ -56,6 +56,7 @@ typedef struct {
     int split_k; /* number of K splits (>= 1) */
     int group_m; /* tile rows per scheduling group */
     int max_ctas; /* cap on the persistent grid (testing) */
+    int cta_pair; /* 1 = pair two CTAs on 256x256 tiles (tcgen05 cta_group::2), -1 = never, 0 = heuristic */
 } qgemm_tuning_t;
 
 /*

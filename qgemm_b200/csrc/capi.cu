@@ -143,6 +143,7 @@ int make_operand_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
 // ---------------------------------------------------------------- configuration
 struct Config {
     int bn, splits, kb_per_split, group_m;
+    bool pair;  // two CTAs per 256x256 tile (bn is then 256 and tiles are counted in 256-row units)
 };
 
 int env_int(const char* name) {
@@ -178,7 +179,7 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
     if (!want_split) want_split = env_int("QGEMM_SPLIT_K");
     if (!want_group) want_group = env_int("QGEMM_GROUP_M");
 
-    Config best{256, 1, kb_total, 16};
+    Config best{256, 1, kb_total, 16, false};
     double best_t = 1e300;
     for (int bn : {256, 128}) {
         if (want_bn && bn != want_bn) continue;
@@ -201,7 +202,12 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
         best.splits = 1;
         best.kb_per_split = kb_total;
     }
-    best.group_m = want_group > 0 ? want_group : (best.bn == 256 ? 16 : 8);
+    int want_pair = tuning ? tuning->cta_pair : 0;
+    if (!want_pair) want_pair = env_int("QGEMM_CTA_PAIR");
+    // CTA pairs move a third fewer bytes per flop; they pay off once both 128-row halves hold real rows.
+    best.pair = want_pair > 0 || (want_pair == 0 && best.bn == 256 && best.splits == 1 && M > 128);
+    if (best.pair) best.bn = 256;
+    best.group_m = want_group > 0 ? want_group : (best.pair ? 8 : (best.bn == 256 ? 16 : 8));
     return best;
 }
 
@@ -310,7 +316,7 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     CUtensorMap ta, tb;
     rc = make_operand_map(A, M, K, lda, in_dtype, kBM, &ta);
     if (rc != QGEMM_OK) return rc;
-    rc = make_operand_map(b_kmajor, N, K, ldb_k, in_dtype, static_cast<uint32_t>(cfg.bn), &tb);
+    rc = make_operand_map(b_kmajor, N, K, ldb_k, in_dtype, cfg.pair ? 128u : static_cast<uint32_t>(cfg.bn), &tb);
     if (rc != QGEMM_OK) return rc;
 
     GemmParams p;
@@ -318,13 +324,15 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     p.M = static_cast<int>(M);
     p.N = static_cast<int>(N);
     p.K = static_cast<int>(K);
-    p.m_tiles = static_cast<int>((M + kBM - 1) / kBM);
+    const int tile_m = cfg.pair ? kPairTileM : kBM;
+    p.m_tiles = static_cast<int>((M + tile_m - 1) / tile_m);
     p.n_tiles = static_cast<int>((N + cfg.bn - 1) / cfg.bn);
     p.splits = cfg.splits;
     p.kb_total = plan.kb_total;
     p.kb_per_split = cfg.kb_per_split;
     p.group_m = cfg.group_m;
-    p.idesc = ptx::make_idesc(plan.ti.cfmt, plan.ti.fmt, plan.ti.fmt, kBM, static_cast<uint32_t>(cfg.bn));
+    p.idesc = ptx::make_idesc(plan.ti.cfmt, plan.ti.fmt, plan.ti.fmt, static_cast<uint32_t>(tile_m),
+                              static_cast<uint32_t>(cfg.bn));
     p.status = st->status;
 
     int launch_out = plan.out_kind;
@@ -352,10 +360,20 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     if (cap > 0) grid = std::min(grid, cap);
 
     cudaError_t e;
-    switch (plan.ti.kind) {
-        case ptx::KIND_F16: e = launch_gemm_f16(cfg.bn, launch_out, ta, tb, p, grid, stream); break;
-        case ptx::KIND_I8: e = launch_gemm_i8(cfg.bn, launch_out, ta, tb, p, grid, stream); break;
-        default: e = launch_gemm_f8(cfg.bn, launch_out, ta, tb, p, grid, stream); break;
+    if (cfg.pair) {
+        int clusters = static_cast<int>(std::min<long long>(work, st->sm_count / 2));
+        if (cap > 0) clusters = std::min(clusters, std::max(1, cap / 2));
+        switch (plan.ti.kind) {
+            case ptx::KIND_F16: e = launch_gemm_pair_f16(launch_out, ta, tb, p, clusters, stream); break;
+            case ptx::KIND_I8: e = launch_gemm_pair_i8(launch_out, ta, tb, p, clusters, stream); break;
+            default: e = launch_gemm_pair_f8(launch_out, ta, tb, p, clusters, stream); break;
+        }
+    } else {
+        switch (plan.ti.kind) {
+            case ptx::KIND_F16: e = launch_gemm_f16(cfg.bn, launch_out, ta, tb, p, grid, stream); break;
+            case ptx::KIND_I8: e = launch_gemm_i8(cfg.bn, launch_out, ta, tb, p, grid, stream); break;
+            default: e = launch_gemm_f8(cfg.bn, launch_out, ta, tb, p, grid, stream); break;
+        }
     }
     if (e != cudaSuccess) return QGEMM_ERR_CUDA;
 

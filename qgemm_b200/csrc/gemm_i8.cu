@@ -6,4 +6,8 @@ cudaError_t launch_gemm_i8(int bn, int out, const CUtensorMap& ta, const CUtenso
                            int grid, cudaStream_t stream) {
     return launch_kind<ptx::KIND_I8>(bn, out, ta, tb, p, grid, stream);
 }
+cudaError_t launch_gemm_pair_i8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                                 int clusters, cudaStream_t stream) {
+    return launch_pair_kind<ptx::KIND_I8>(out, ta, tb, p, clusters, stream);
+}
 }  // namespace qgemm

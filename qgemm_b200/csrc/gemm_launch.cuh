@@ -1,6 +1,7 @@
 // Host-side launch helper shared by the per-kind instantiation files.
 #pragma once
 #include "gemm_sm100.cuh"
+#include "gemm_sm100_2cta.cuh"
 
 namespace qgemm {
 
@@ -46,6 +47,66 @@ cudaError_t launch_kind(int bn, int out, const CUtensorMap& ta, const CUtensorMa
 #undef QGEMM_CASE
     return cudaErrorInvalidValue;
 }
+
+// CTA-pair kernel (256 x 256 tiles, clusters of two). `max_clusters_out`, when non-null, receives how many
+// clusters the device can keep resident at once (queried once per device).
+template <int KIND, int OUT>
+cudaError_t launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int clusters,
+                            cudaStream_t stream) {
+    auto kernel = gemm_tcgen05_pair_kernel<KIND, OUT>;
+    constexpr int smem = PairSmem::kDynamicBytes;
+    static bool configured[64] = {};
+    static int max_clusters[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!configured[dev]) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * 74);
+        cfg.blockDim = dim3(kGemmThreads);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
+            (void)cudaGetLastError();
+            n = 74;
+        }
+        max_clusters[dev] = n;
+        configured[dev] = true;
+    }
+    if (clusters > max_clusters[dev]) clusters = max_clusters[dev];
+    if (clusters < 1) clusters = 1;
+    kernel<<<2 * clusters, kGemmThreads, smem, stream>>>(ta, tb, p);
+    return cudaGetLastError();
+}
+
+template <int KIND>
+cudaError_t launch_pair_kind(int out, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int clusters,
+                             cudaStream_t stream) {
+    switch (out) {
+        case OUT_F32: return launch_pair_one<KIND, OUT_F32>(ta, tb, p, clusters, stream);
+        case OUT_BF16: return launch_pair_one<KIND, OUT_BF16>(ta, tb, p, clusters, stream);
+        case OUT_F16: return launch_pair_one<KIND, OUT_F16>(ta, tb, p, clusters, stream);
+        case OUT_RAW32: return launch_pair_one<KIND, OUT_RAW32>(ta, tb, p, clusters, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_gemm_pair_f16(int out, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                                 int clusters, cudaStream_t stream);
+cudaError_t launch_gemm_pair_i8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                                int clusters, cudaStream_t stream);
+cudaError_t launch_gemm_pair_f8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                                int clusters, cudaStream_t stream);
 
 // Defined one per translation unit so the kinds compile in parallel.
 cudaError_t launch_gemm_f16(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,

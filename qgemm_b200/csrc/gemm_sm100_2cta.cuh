@@ -1,0 +1,213 @@
+// CTA-pair variant of the persistent tcgen05 GEMM: two CTAs of a 2-CTA cluster share one
+// 256 x 256 output tile through tcgen05.mma.cta_group::2.
+//
+// Each CTA loads 128 rows of A and only its 128-row half of the B tile (32 KB per 128-byte K block
+// instead of the 48 KB a lone 128 x 256 tile needs), so a third fewer bytes cross L2 -> SM and
+// shared memory per flop, and six pipeline stages fit where the lone-CTA kernel has four. The
+// even-ranked ("leader") CTA issues every MMA; the instruction reads both CTAs' shared memory and
+// writes rows 0..127 of the tile into the leader's tensor memory and rows 128..255 into the peer's.
+//
+// Barriers (all mbarriers, every wait bounded as in gemm_sm100.cuh):
+//   full[stage]   leader only; one arrive.expect_tx by the leader's producer for both CTAs' bytes;
+//                 both producers' TMA loads credit it (cta_group::2 loads may signal the peer's barrier);
+//   empty[stage]  one per CTA; the leader's tcgen05.commit arrives on both;
+//   tmem_full[a]  one per CTA; the leader's tcgen05.commit arrives on both;
+//   tmem_empty[a] leader only; the 4 epilogue warps of each CTA arrive on it (count 8).
+// No TMA load is multicast.
+#pragma once
+#include "gemm_sm100.cuh"
+
+namespace qgemm {
+
+constexpr int kPairStages = 6;
+constexpr int kPairTileM = 256;
+constexpr int kPairTileN = 256;
+
+struct PairSmem {
+    static constexpr int kAStage = 128 * 128;
+    static constexpr int kBStage = 128 * 128;
+    static constexpr int kTiles = kPairStages * (kAStage + kBStage);
+    static constexpr int kBarOffset = kTiles;
+    static constexpr int kMiscOffset = kBarOffset + (2 * kPairStages + 4) * 8;
+    static constexpr int kTotal = kMiscOffset + 16;
+    static constexpr int kDynamicBytes = kTotal + 1024;
+};
+
+// p.m_tiles / p.n_tiles count 256 x 256 pair tiles; the grid is 2 * (number of clusters).
+template <int KIND, int OUT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                         const GemmParams p) {
+    using L = PairSmem;
+    constexpr int STAGES = kPairStages;
+    constexpr int ELT = (KIND == ptx::KIND_F16) ? 2 : 1;
+    constexpr int BK = 128 / ELT;
+    constexpr int BN = kPairTileN;
+    constexpr uint32_t TMEM_COLS = 512;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
+    uint8_t* smem = smem_raw + pad;
+    const uint32_t smem_base = raw_addr + pad;
+    const uint32_t smem_a = smem_base;
+    const uint32_t smem_b = smem_base + STAGES * L::kAStage;
+    const uint32_t bar_full = smem_base + L::kBarOffset;
+    const uint32_t bar_empty = bar_full + STAGES * 8;
+    const uint32_t bar_tfull = bar_empty + STAGES * 8;
+    const uint32_t bar_tempty = bar_tfull + 2 * 8;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kMiscOffset);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 4);
+
+    const int warp = static_cast<int>(threadIdx.x) >> 5;
+    const int lane = static_cast<int>(threadIdx.x) & 31;
+    const uint32_t rank = ptx::cluster_ctarank();  // 0 = leader
+    const int cluster_id = static_cast<int>(blockIdx.x) >> 1;
+    const int n_clusters = static_cast<int>(gridDim.x) >> 1;
+    const int total_work = p.m_tiles * p.n_tiles * p.splits;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(bar_full + s * 8, 1);
+            ptx::mbar_init(bar_empty + s * 8, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(bar_tfull + a * 8, 1);
+            ptx::mbar_init(bar_tempty + a * 8, 8);
+        }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+    }
+    if (warp == 0 && lane == 0) {
+        ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    // Both CTAs' barriers must exist before either CTA signals the other's.
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (both CTAs)
+        if (ptx::elect_one()) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int w = cluster_id; ok && w < total_work; w += n_clusters) {
+                const TileCoord t = decode_tile(w, p);
+                const int kb0 = t.split * p.kb_per_split;
+                const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                const int row_a = (t.m_blk * 2 + static_cast<int>(rank)) * 128;
+                const int row_b = t.n_blk * BN + static_cast<int>(rank) * 128;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, p.status, ROLE_PRODUCER, kb)) {
+                        ok = false;
+                        break;
+                    }
+                    if (rank == 0) ptx::mbar_arrive_expect_tx(bar_full + stage * 8, 2 * (L::kAStage + L::kBStage));
+                    const uint32_t leader_full = ptx::mapa_shared(bar_full + stage * 8, 0);
+                    ptx::tma_load_2d_pair(smem_a + stage * L::kAStage, &tmap_a, leader_full, kb * BK, row_a);
+                    ptx::tma_load_2d_pair(smem_b + stage * L::kBStage, &tmap_b, leader_full, kb * BK, row_b);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (rank == 0 && ptx::elect_one()) {
+            uint32_t stage = 0, phase = 0;
+            uint32_t it = 0;
+            bool ok = true;
+            for (int w = cluster_id; ok && w < total_work; w += n_clusters, ++it) {
+                const TileCoord t = decode_tile(w, p);
+                const int kb0 = t.split * p.kb_per_split;
+                const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                const uint32_t acc = it & 1u;
+                const uint32_t acc_phase = (it >> 1) & 1u;
+                if (!wait_bounded(bar_tempty + acc * 8, acc_phase ^ 1u, abort_flag, p.status, ROLE_MMA, -1)) break;
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status, ROLE_MMA, kb)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint64_t a_desc = ptx::make_kmajor_sw128_desc(smem_a + stage * L::kAStage);
+                    const uint64_t b_desc = ptx::make_kmajor_sw128_desc(smem_b + stage * L::kBStage);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        ptx::umma_ss_pair<KIND>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc,
+                                                (kb > kb0 || k > 0) ? 1u : 0u);
+                    }
+                    ptx::tc_commit_pair(bar_empty + stage * 8, 3);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) ptx::tc_commit_pair(bar_tfull + acc * 8, 3);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (both CTAs)
+        const int quad = warp & 3;
+        float alpha = 1.0f;
+        if constexpr (OUT != OUT_RAW32) {
+            if (p.scale_a != nullptr) alpha *= __ldg(p.scale_a);
+            if (p.scale_b != nullptr) alpha *= __ldg(p.scale_b);
+        }
+        uint32_t it = 0;
+        for (int w = cluster_id; w < total_work; w += n_clusters, ++it) {
+            const TileCoord t = decode_tile(w, p);
+            const uint32_t acc = it & 1u;
+            const uint32_t acc_phase = (it >> 1) & 1u;
+            if (!wait_bounded(bar_tfull + acc * 8, acc_phase, abort_flag, p.status, ROLE_EPILOGUE, w)) break;
+            ptx::tc_fence_after();
+            const long long row =
+                (static_cast<long long>(t.m_blk) * 2 + static_cast<long long>(rank)) * 128 + quad * 32 + lane;
+            uint8_t* c_base = reinterpret_cast<uint8_t*>(p.C) +
+                              static_cast<long long>(t.split) * p.split_stride * OutBytes<OUT>::value;
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int n0 = t.n_blk * BN + c * 32;
+                if (n0 >= p.N) break;
+                uint32_t v[32];
+                ptx::tmem_ld_32x32b_x32(t_addr + c * 32, v);
+                ptx::tmem_ld_wait();
+                if (row < p.M)
+                    store_chunk<KIND, OUT>(c_base, p.ldc, row, n0, min(32, p.N - n0), p.c_vec_ok != 0, v, alpha);
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa_shared(bar_tempty + acc * 8, 0));
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    ptx::tc_fence_before();
+    __syncthreads();
+    // Neither CTA may release its shared or tensor memory while the other can still touch it.
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+    if (*abort_flag != 0) {
+        for (int i = 0; i < 64; ++i) __nanosleep(20000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace qgemm
