@@ -32,9 +32,9 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 # DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum), from the
-# ncu capture summarised in profiles/gemm_tcgen05_bf16_8192_cta1.md. Keyed by workload; None where no
+# ncu capture summarised in profiles/gemm_tcgen05_pair_bf16_8192.md. Keyed by workload; None where no
 # capture of that workload exists.
-NCU_TRAFFIC_BYTES = {"c2_bf16_8192": 1.017461e9 + 126.353e6}
+NCU_TRAFFIC_BYTES = {"c2_bf16_8192": 1.082997e9 + 127.506e6}
 
 NOMINAL_PEAK_TFLOPS = {"bf16": 2250.0, "fp16": 2250.0, "int8": 4500.0, "fp8": 4500.0}
 
@@ -66,6 +66,7 @@ def parse_args():
     ap.add_argument("--seed", type=int, default=2)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="never replay the timed loop from a CUDA graph")
     ap.add_argument("--gather", action="store_true", help="c5: also time the all-gather of the C slices")
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--split-k", type=int, default=0)
@@ -155,6 +156,8 @@ class CpuArm:
         self.N = min(N, 8192)  # one rank's column block of the sharded workload, at most this wide
         self.K = K
         rows = min(M, 8192)
+        # torch.distributed.run exports OMP_NUM_THREADS=1; the CPU arm is meant to use every host core
+        o.set_threads(os.cpu_count() or 1)
         self.threads = o.num_threads()
         if in_name == "int8":
             self.bt = datagen.int8_uniform((self.N, K), seed, 1)
@@ -315,20 +318,41 @@ def main():
             return float(t.item())
         return ms
 
+    # Launch-bound workloads (a step of a few microseconds) are replayed from a CUDA graph so that the
+    # device, not the Python caller, sets the pace; large steps are launched directly.
+    use_graph = (nsets > 1) and not args.no_graph
+
+    def run_timed(step_fn, steps):
+        """Time `steps` calls of step_fn on the current stream. Returns milliseconds for all of them."""
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if use_graph:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(steps):
+                    step_fn()
+            for _ in range(3):
+                g.replay()
+            barrier()
+            sampler.region(True)
+            t0.record()
+            g.replay()
+            t1.record()
+        else:
+            barrier()
+            sampler.region(True)
+            t0.record()
+            for _ in range(steps):
+                step_fn()
+            t1.record()
+        torch.cuda.synchronize()
+        sampler.region(False)
+        return t0.elapsed_time(t1)
+
     # ---------------- value: device-resident operands, the public call
     for _ in range(max(args.warmup, 3)):
         call_device()
+    ms_total = max_over_ranks(run_timed(call_device, args.steps))
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler.region(True)
-    e0.record()
-    for _ in range(args.steps):
-        call_device()
-    e1.record()
-    torch.cuda.synchronize()
-    sampler.region(False)
-    barrier()
-    ms_total = max_over_ranks(e0.elapsed_time(e1))
     ms_per_step = ms_total / args.steps
     flop_per_step_rank = 2.0 * M * N * K
     value = world * flop_per_step_rank / (ms_per_step * 1e-3) / 1e12
@@ -340,20 +364,29 @@ def main():
 
     # ---------------- roofline of the dominant kernel: the GEMM kernel alone (K-major operands), per-launch events
     ksets = sets if ops["b_kmajor"] else [(a_, q.transpose(b_), c_) for a_, b_, c_ in sets]
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    for i in range(3):
-        a_, b_, c_ = ksets[i % nsets]
+    kcount = [0]
+
+    def call_kernel():
+        a_, b_, c_ = ksets[kcount[0] % nsets]
+        kcount[0] += 1
         q._gemm(a_, b_, ops["sa"], ops["sb"], c_, True, tuning, mixed)
+
+    for _ in range(3):
+        call_kernel()
     torch.cuda.synchronize()
-    sampler.region(True)
-    for i, (s, e) in enumerate(evs):
-        a_, b_, c_ = ksets[i % nsets]
-        s.record()
-        q._gemm(a_, b_, ops["sa"], ops["sb"], c_, True, tuning, mixed)
-        e.record()
-    torch.cuda.synchronize()
-    sampler.region(False)
-    gemm_ms = sum(s.elapsed_time(e) for s, e in evs) / len(evs)
+    if use_graph:
+        gemm_ms = run_timed(call_kernel, args.steps) / args.steps
+    else:
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+               for _ in range(args.steps)]
+        sampler.region(True)
+        for s, e in evs:
+            s.record()
+            call_kernel()
+            e.record()
+        torch.cuda.synchronize()
+        sampler.region(False)
+        gemm_ms = sum(s.elapsed_time(e) for s, e in evs) / len(evs)
     achieved_tflops = flop_per_step_rank / (gemm_ms * 1e-3) / 1e12
     es_in = 2 if in_name in ("bf16", "fp16") else 1
     es_out = {"bf16": 2, "fp16": 2, "fp32": 4}[out_name]
@@ -383,7 +416,8 @@ def main():
         gbs = alg_bytes / (gemm_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
                     "peak_source": hbm_src + " copy bandwidth"}
-    roofline.update({"kernel": "gemm_tcgen05_kernel", "kernel_ms": gemm_ms, "algorithmic_flop": flop_per_step_rank,
+    roofline.update({"kernel": "gemm_tcgen05_pair_kernel" if M > 128 and not (args.tile_n or args.split_k) else "gemm_tcgen05_kernel",
+                     "kernel_ms": gemm_ms, "algorithmic_flop": flop_per_step_rank,
                      "algorithmic_bytes": alg_bytes, "traffic": NCU_TRAFFIC_BYTES.get(args.workload)})
 
     # the relayout kernel on its own (HBM-bound), when the workload uses it
@@ -468,6 +502,7 @@ def main():
             "config": {"workload": args.workload, "description": desc, "per_rank_shape": [M, N, K],
                        "l2": "inputs_larger_than_l2" if nsets == 1 else
                        f"rotating {nsets} operand sets ({nsets * set_bytes / 1e6:.0f} MB) so no step finds its inputs in L2",
+                       "timed_loop": "CUDA graph replay" if use_graph else "direct launches",
                        "seed": args.seed, "sharding": f"columns of B/C over {world} rank(s), no data-path collective"},
             "per_gpu_tflops": value / world,
             "frac_of_nominal_dense_peak": value / world / NOMINAL_PEAK_TFLOPS[in_name],

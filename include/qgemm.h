@@ -52,7 +52,7 @@ typedef struct CUstream_st* qgemm_stream_t; /* == cudaStream_t */
 
 /* Optional tuning overrides; zero in a field means "library heuristic". */
 typedef struct {
-    int tile_n;  /* 128 or 256 */
+    int tile_n;  /* 64, 128 or 256 */
     int split_k; /* number of K splits (>= 1) */
     int group_m; /* tile rows per scheduling group */
     int max_ctas; /* cap on the persistent grid (testing) */

@@ -27,3 +27,17 @@ SRCS=(
   -I "$REF/include" -I "$REF/src/include" \
   -shared -o "$OUT/libqgemm_ref.so" "${SRCS[@]}" -lcudart
 echo "$OUT/libqgemm_ref.so"
+
+# The reference's own benchmark harness, UNMODIFIED, compiled against this repository's include/
+# (gemm.h, blas.h) and linked with libqgemm.so instead of the reference's gemm_lib: the drop-in
+# check. Needs qgemm_b200/libqgemm.so (python -m qgemm_b200.build).
+REPO="$(cd "$HERE/.." && pwd)"
+if [ -f "$REPO/qgemm_b200/libqgemm.so" ]; then
+  "$NVCC" -ccbin /usr/bin/g++ -std=c++17 -O2 -DUSE_CUDA -w -Wno-deprecated-gpu-targets \
+    -I "$REPO/include" -I "$REF/tests" -I "$REF/tests/includes" \
+    "$REF/tests/cuda_benchmark.cpp" \
+    -L "$REPO/qgemm_b200" -lqgemm -lcublas \
+    -Xlinker -rpath -Xlinker '$ORIGIN/../../qgemm_b200' \
+    -o "$OUT/cuda_benchmark"
+  echo "$OUT/cuda_benchmark"
+fi

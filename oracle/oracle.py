@@ -49,6 +49,10 @@ def _sz(x):
     return C.c_size_t(int(x))
 
 
+def set_threads(n: int) -> None:
+    lib().oracle_set_threads(C.c_int(int(n)))
+
+
 def num_threads() -> int:
     return int(lib().oracle_num_threads())
 

@@ -7,10 +7,15 @@
  *
  * PARITY STATUS: the reference project ships no CPU GEMM, no golden vectors and no known-answer
  * tests for this path (its harness compares each kernel with cuBLAS at run time,
- * tests/includes/test_config.h:29-52,161-169). The arithmetic below therefore restates the
- * reference's *semantics*, each function citing the reference lines it follows. Until it has been
- * checked against outputs of the reference's own GPU kernels (see oracle/build_ref.sh and
- * tests/golden/), parity is "unpinned" for every tier that has no such fixture.
+ * tests/includes/test_config.h:29-52,161-169). The arithmetic below restates the reference's
+ * *semantics*, each function citing the reference lines it follows.
+ *   - bf16 GEMM and transpose: PINNED. The reference's own GPU kernels (GEMM_kernel_v1/v2/v3/v3_1,
+ *     matrix_transpose) were compiled from its sources (oracle/build_ref.sh) and run on a B200;
+ *     their inputs and outputs are tests/golden/reference_bf16_gemm.npz and the CPU tests check
+ *     this file against them.
+ *   - int8 and FP8 mixed GEMM: parity unpinned -- the reference has no implementation of them for
+ *     NVIDIA GPUs (src/mix_gemm/sm80_mix_gemm_kernel.cpp is empty) and none on the CPU. int8 is
+ *     exact integer arithmetic; the FP8 conversions are checked against ml_dtypes and torch.
  *
  * Plain C99 + OpenMP; build with oracle/Makefile.
  */
@@ -351,6 +356,14 @@ void oracle_gemm_i8_blocked(const int8_t* A, size_t lda, const int8_t* Bt, size_
             }
         }
     }
+}
+
+void oracle_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
 }
 
 int oracle_num_threads(void) {

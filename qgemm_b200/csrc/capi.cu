@@ -152,15 +152,22 @@ int env_int(const char* name) {
 }
 
 // Estimated duration in units of "one 128-byte K block of a 128x256 tile" (about 0.27 us at peak).
-double estimate(int bn, int splits, size_t M, size_t N, int kb_total, int sms, int* kbps_out) {
-    const int mt = static_cast<int>((M + kBM - 1) / kBM);
+// `pair` = CTA pairs on 256x256 tiles (half as many schedulable units, a third fewer bytes per flop).
+double estimate(int bn, bool pair, int splits, size_t M, size_t N, int kb_total, int sms, int* kbps_out) {
+    const int tile_m = pair ? kPairTileM : kBM;
+    const int mt = static_cast<int>((M + tile_m - 1) / tile_m);
     const int nt = static_cast<int>((N + bn - 1) / bn);
     const int kbps = (kb_total + splits - 1) / splits;
     const int real_splits = (kb_total + kbps - 1) / kbps;
     const long long units = static_cast<long long>(mt) * nt * real_splits;
-    const long long waves = (units + sms - 1) / sms;
-    const double t_kb = (bn == 256) ? 1.0 : 0.56;  // narrower tiles re-read A relatively more often
-    const double fill = (bn == 256) ? 6.0 : 4.5;   // pipeline fill + epilogue drain per work unit
+    const int slots = pair ? std::max(1, sms / 2) : sms;
+    const long long waves = (units + slots - 1) / slots;
+    // time per K block of one unit, and pipeline fill + epilogue drain per unit
+    double t_kb, fill;
+    if (pair) { t_kb = 0.93; fill = 6.0; }
+    else if (bn == 256) { t_kb = 1.0; fill = 6.0; }
+    else if (bn == 128) { t_kb = 0.56; fill = 4.5; }   // narrower tiles re-read A relatively more often
+    else { t_kb = 0.33; fill = 4.0; }
     double t = static_cast<double>(waves) * (kbps * t_kb + fill);
     if (real_splits > 1) {
         // partial slabs are written once and read once by the second pass (~1.75 MB per unit of time)
@@ -175,38 +182,41 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
     int want_bn = tuning ? tuning->tile_n : 0;
     int want_split = tuning ? tuning->split_k : 0;
     int want_group = tuning ? tuning->group_m : 0;
+    int want_pair = tuning ? tuning->cta_pair : 0;
     if (!want_bn) want_bn = env_int("QGEMM_TILE_N");
     if (!want_split) want_split = env_int("QGEMM_SPLIT_K");
     if (!want_group) want_group = env_int("QGEMM_GROUP_M");
+    if (!want_pair) want_pair = env_int("QGEMM_CTA_PAIR");
 
     Config best{256, 1, kb_total, 16, false};
     double best_t = 1e300;
-    for (int bn : {256, 128}) {
-        if (want_bn && bn != want_bn) continue;
+    struct Cand { int bn; bool pair; };
+    const Cand cands[] = {{256, true}, {256, false}, {128, false}, {64, false}};
+    for (const Cand& c : cands) {
+        if (c.pair && (want_pair < 0 || (want_bn && want_bn != 256))) continue;
+        if (!c.pair && want_pair > 0) continue;
+        if (want_bn && c.bn != want_bn) continue;
         const int max_split = want_split ? want_split : std::min(kb_total, 16);
         for (int s = want_split ? want_split : 1; s <= max_split; ++s) {
             if (s > kb_total) break;
             int kbps = 0;
-            const double t = estimate(bn, s, M, N, kb_total, sms, &kbps);
+            const double t = estimate(c.bn, c.pair, s, M, N, kb_total, sms, &kbps);
             if (!want_split && s > 1 && kbps < 2) continue;
             if (t < best_t) {
                 best_t = t;
-                best.bn = bn;
+                best.bn = c.bn;
+                best.pair = c.pair;
                 best.kb_per_split = kbps;
                 best.splits = (kb_total + kbps - 1) / kbps;
             }
         }
     }
     if (best_t == 1e300) {  // an override asked for something infeasible (e.g. split_k > K blocks)
-        best.bn = (want_bn == 128) ? 128 : 256;
+        best.pair = want_pair > 0;
+        best.bn = best.pair ? 256 : ((want_bn == 128 || want_bn == 64) ? want_bn : 256);
         best.splits = 1;
         best.kb_per_split = kb_total;
     }
-    int want_pair = tuning ? tuning->cta_pair : 0;
-    if (!want_pair) want_pair = env_int("QGEMM_CTA_PAIR");
-    // CTA pairs move a third fewer bytes per flop; they pay off once both 128-row halves hold real rows.
-    best.pair = want_pair > 0 || (want_pair == 0 && best.bn == 256 && best.splits == 1 && M > 128);
-    if (best.pair) best.bn = 256;
     best.group_m = want_group > 0 ? want_group : (best.pair ? 8 : (best.bn == 256 ? 16 : 8));
     return best;
 }

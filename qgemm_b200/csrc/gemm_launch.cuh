@@ -8,7 +8,7 @@ namespace qgemm {
 // Stages per tile width: a stage holds a 128x128-byte A tile and a BNx128-byte B tile.
 template <int BN>
 struct StagesFor {
-    static constexpr int value = (BN == 256) ? 4 : 6;
+    static constexpr int value = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
 };
 
 template <int KIND, int BN, int OUT>
@@ -44,6 +44,10 @@ cudaError_t launch_kind(int bn, int out, const CUtensorMap& ta, const CUtensorMa
     QGEMM_CASE(128, OUT_BF16)
     QGEMM_CASE(128, OUT_F16)
     QGEMM_CASE(128, OUT_RAW32)
+    QGEMM_CASE(64, OUT_F32)
+    QGEMM_CASE(64, OUT_BF16)
+    QGEMM_CASE(64, OUT_F16)
+    QGEMM_CASE(64, OUT_RAW32)
 #undef QGEMM_CASE
     return cudaErrorInvalidValue;
 }
