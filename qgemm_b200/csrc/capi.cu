@@ -140,6 +140,39 @@ int make_operand_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
     return QGEMM_OK;
 }
 
+// Output [splits][M][N] (splits == 1 for the final C) with leading dimension ld and slab stride
+// M*ld, elements of 2 or 4 bytes; box = 128 bytes of N x 32 rows x 1 slab, 128-byte swizzle. Stores
+// through it are clipped at N, at M (per slab) and at the slab count.
+int make_output_map(void* ptr, uint64_t M, uint64_t N, uint64_t ld, uint64_t splits, int out_kind, CUtensorMap* out) {
+    const MapKey key{ptr, M, N, ld, static_cast<uint32_t>(splits), static_cast<uint32_t>(100 + out_kind)};
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) {
+        *out = it->second;
+        return QGEMM_OK;
+    }
+    CUtensorMapDataType dt;
+    uint32_t es;
+    switch (out_kind) {
+        case OUT_F32: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; es = 4; break;
+        case OUT_RAW32: dt = CU_TENSOR_MAP_DATA_TYPE_INT32; es = 4; break;
+        case OUT_BF16: dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; es = 2; break;
+        default: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; es = 2; break;
+    }
+    const cuuint64_t dims[3] = {N, M, splits};
+    const cuuint64_t strides[2] = {ld * es, M * ld * es};
+    const cuuint32_t box[3] = {128u / es, 32u, 1u};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUtensorMap m;
+    const CUresult r = g_encode(&m, dt, 3, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return QGEMM_ERR_CUDA;
+    if (g_maps.size() > 4096) g_maps.clear();
+    g_maps.emplace(key, m);
+    *out = m;
+    return QGEMM_OK;
+}
+
 // ---------------------------------------------------------------- configuration
 struct Config {
     int bn, splits, kb_per_split, group_m;
@@ -362,6 +395,15 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
         p.c_vec_ok = (reinterpret_cast<uintptr_t>(C) % 16 == 0) && ((ldc * out_bytes) % 16 == 0);
     }
 
+    // The epilogue goes through shared memory + TMA stores when the destination qualifies for a tensor map.
+    CUtensorMap tc;
+    std::memset(&tc, 0, sizeof(tc));
+    if (p.c_vec_ok && env_int("QGEMM_DIRECT_STORE") == 0) {
+        const int map_rc = make_output_map(p.C, M, N, static_cast<uint64_t>(p.ldc), static_cast<uint64_t>(cfg.splits),
+                                           launch_out, &tc);
+        p.c_tma_ok = (map_rc == QGEMM_OK) ? 1 : 0;
+    }
+
     const long long work = static_cast<long long>(p.m_tiles) * p.n_tiles * p.splits;
     if (work > 0x7fffffffLL) return QGEMM_ERR_UNSUPPORTED;
     int grid = static_cast<int>(std::min<long long>(work, st->sm_count));
@@ -374,15 +416,15 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
         int clusters = static_cast<int>(std::min<long long>(work, st->sm_count / 2));
         if (cap > 0) clusters = std::min(clusters, std::max(1, cap / 2));
         switch (plan.ti.kind) {
-            case ptx::KIND_F16: e = launch_gemm_pair_f16(launch_out, ta, tb, p, clusters, stream); break;
-            case ptx::KIND_I8: e = launch_gemm_pair_i8(launch_out, ta, tb, p, clusters, stream); break;
-            default: e = launch_gemm_pair_f8(launch_out, ta, tb, p, clusters, stream); break;
+            case ptx::KIND_F16: e = launch_gemm_pair_f16(launch_out, ta, tb, tc, p, clusters, stream); break;
+            case ptx::KIND_I8: e = launch_gemm_pair_i8(launch_out, ta, tb, tc, p, clusters, stream); break;
+            default: e = launch_gemm_pair_f8(launch_out, ta, tb, tc, p, clusters, stream); break;
         }
     } else {
         switch (plan.ti.kind) {
-            case ptx::KIND_F16: e = launch_gemm_f16(cfg.bn, launch_out, ta, tb, p, grid, stream); break;
-            case ptx::KIND_I8: e = launch_gemm_i8(cfg.bn, launch_out, ta, tb, p, grid, stream); break;
-            default: e = launch_gemm_f8(cfg.bn, launch_out, ta, tb, p, grid, stream); break;
+            case ptx::KIND_F16: e = launch_gemm_f16(cfg.bn, launch_out, ta, tb, tc, p, grid, stream); break;
+            case ptx::KIND_I8: e = launch_gemm_i8(cfg.bn, launch_out, ta, tb, tc, p, grid, stream); break;
+            default: e = launch_gemm_f8(cfg.bn, launch_out, ta, tb, tc, p, grid, stream); break;
         }
     }
     if (e != cudaSuccess) return QGEMM_ERR_CUDA;

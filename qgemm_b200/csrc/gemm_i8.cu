@@ -2,12 +2,12 @@
 #include "gemm_launch.cuh"
 
 namespace qgemm {
-cudaError_t launch_gemm_i8(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+cudaError_t launch_gemm_i8(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                            int grid, cudaStream_t stream) {
-    return launch_kind<ptx::KIND_I8>(bn, out, ta, tb, p, grid, stream);
+    return launch_kind<ptx::KIND_I8>(bn, out, ta, tb, tc, p, grid, stream);
 }
-cudaError_t launch_gemm_pair_i8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+cudaError_t launch_gemm_pair_i8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                                  int clusters, cudaStream_t stream) {
-    return launch_pair_kind<ptx::KIND_I8>(out, ta, tb, p, clusters, stream);
+    return launch_pair_kind<ptx::KIND_I8>(out, ta, tb, tc, p, clusters, stream);
 }
 }  // namespace qgemm

@@ -12,7 +12,7 @@ struct StagesFor {
 };
 
 template <int KIND, int BN, int OUT>
-cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
+cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
                        cudaStream_t stream) {
     constexpr int STAGES = StagesFor<BN>::value;
     auto kernel = gemm_tcgen05_kernel<KIND, BN, STAGES, OUT>;
@@ -27,15 +27,15 @@ cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    kernel<<<grid, kGemmThreads, smem, stream>>>(ta, tb, p);
+    kernel<<<grid, kGemmThreads, smem, stream>>>(ta, tb, tc, p);
     return cudaGetLastError();
 }
 
 template <int KIND>
-cudaError_t launch_kind(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
+cudaError_t launch_kind(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
                         cudaStream_t stream) {
 #define QGEMM_CASE(BN_, OUT_) \
-    if (bn == BN_ && out == OUT_) return launch_one<KIND, BN_, OUT_>(ta, tb, p, grid, stream);
+    if (bn == BN_ && out == OUT_) return launch_one<KIND, BN_, OUT_>(ta, tb, tc, p, grid, stream);
     QGEMM_CASE(256, OUT_F32)
     QGEMM_CASE(256, OUT_BF16)
     QGEMM_CASE(256, OUT_F16)
@@ -55,7 +55,7 @@ cudaError_t launch_kind(int bn, int out, const CUtensorMap& ta, const CUtensorMa
 // CTA-pair kernel (256 x 256 tiles, clusters of two). `max_clusters_out`, when non-null, receives how many
 // clusters the device can keep resident at once (queried once per device).
 template <int KIND, int OUT>
-cudaError_t launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int clusters,
+cudaError_t launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int clusters,
                             cudaStream_t stream) {
     auto kernel = gemm_tcgen05_pair_kernel<KIND, OUT>;
     constexpr int smem = PairSmem::kDynamicBytes;
@@ -89,35 +89,35 @@ cudaError_t launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const 
     }
     if (clusters > max_clusters[dev]) clusters = max_clusters[dev];
     if (clusters < 1) clusters = 1;
-    kernel<<<2 * clusters, kGemmThreads, smem, stream>>>(ta, tb, p);
+    kernel<<<2 * clusters, kGemmThreads, smem, stream>>>(ta, tb, tc, p);
     return cudaGetLastError();
 }
 
 template <int KIND>
-cudaError_t launch_pair_kind(int out, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int clusters,
+cudaError_t launch_pair_kind(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int clusters,
                              cudaStream_t stream) {
     switch (out) {
-        case OUT_F32: return launch_pair_one<KIND, OUT_F32>(ta, tb, p, clusters, stream);
-        case OUT_BF16: return launch_pair_one<KIND, OUT_BF16>(ta, tb, p, clusters, stream);
-        case OUT_F16: return launch_pair_one<KIND, OUT_F16>(ta, tb, p, clusters, stream);
-        case OUT_RAW32: return launch_pair_one<KIND, OUT_RAW32>(ta, tb, p, clusters, stream);
+        case OUT_F32: return launch_pair_one<KIND, OUT_F32>(ta, tb, tc, p, clusters, stream);
+        case OUT_BF16: return launch_pair_one<KIND, OUT_BF16>(ta, tb, tc, p, clusters, stream);
+        case OUT_F16: return launch_pair_one<KIND, OUT_F16>(ta, tb, tc, p, clusters, stream);
+        case OUT_RAW32: return launch_pair_one<KIND, OUT_RAW32>(ta, tb, tc, p, clusters, stream);
         default: return cudaErrorInvalidValue;
     }
 }
 
-cudaError_t launch_gemm_pair_f16(int out, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+cudaError_t launch_gemm_pair_f16(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                                  int clusters, cudaStream_t stream);
-cudaError_t launch_gemm_pair_i8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+cudaError_t launch_gemm_pair_i8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                                 int clusters, cudaStream_t stream);
-cudaError_t launch_gemm_pair_f8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+cudaError_t launch_gemm_pair_f8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                                 int clusters, cudaStream_t stream);
 
 // Defined one per translation unit so the kinds compile in parallel.
-cudaError_t launch_gemm_f16(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+cudaError_t launch_gemm_f16(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                             int grid, cudaStream_t stream);
-cudaError_t launch_gemm_i8(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+cudaError_t launch_gemm_i8(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                            int grid, cudaStream_t stream);
-cudaError_t launch_gemm_f8(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+cudaError_t launch_gemm_f8(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                            int grid, cudaStream_t stream);
 
 }  // namespace qgemm

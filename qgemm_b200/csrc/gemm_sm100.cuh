@@ -48,6 +48,7 @@ struct GemmParams {
     const float* scale_b;
     int* status;   // device status words: [0] code, [1] cta, [2] role, [3] stage/tile
     int c_vec_ok;  // C base and ldc allow 16-byte vector stores
+    int c_tma_ok;  // the C tensor map is valid: the epilogue stores through shared memory + TMA
 };
 
 constexpr int kBM = 128;
@@ -173,12 +174,80 @@ __device__ __forceinline__ void store_chunk(uint8_t* c_base, long long ldc, long
     }
 }
 
+// Shared-memory staging of the TMA-store epilogue: every epilogue warp owns two 4 KB buffers, each
+// one 32-row x 128-byte box in the 128-byte-swizzled layout the C tensor map expects.
+constexpr int kEpilogueStagingBytes = 4 * 2 * 4096;
+
+// Drains one accumulator (this warp's 32 rows x BN columns) to C: tcgen05.ld -> scale/convert ->
+// swizzled shared memory -> one TMA store per 128-byte-wide column chunk. The store clips rows and
+// columns that fall outside C. `buf` alternates between the warp's two staging buffers.
+template <int KIND, int OUT, int BN>
+__device__ __forceinline__ void epilogue_tma(const CUtensorMap* tmap_c, uint32_t t_addr, int row0, int m_total,
+                                             int n_base, int n_total, int split, uint32_t stage_base, int lane,
+                                             float alpha, uint32_t& buf) {
+    constexpr int OB = OutBytes<OUT>::value;
+    constexpr int CW = 128 / OB;  // columns per chunk: 64 (16-bit out) or 32 (32-bit out)
+    if (row0 >= m_total) return;  // this warp's 32 rows are all padding (warp-uniform)
+#pragma unroll 1
+    for (int c = 0; c < BN / CW; ++c) {
+        const int n0 = n_base + c * CW;
+        if (n0 >= n_total) break;  // warp-uniform
+        uint32_t v[CW];
+        ptx::tmem_ld_32x32b_x32(t_addr + c * CW, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+        if constexpr (CW == 64) ptx::tmem_ld_32x32b_x32(t_addr + c * CW + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+        // the buffer about to be overwritten was handed to a TMA store two chunks ago: wait until it was read
+        if (lane == 0) ptx::tma_store_wait_read<1>();
+        __syncwarp();
+        ptx::tmem_ld_wait();
+        uint32_t u[32];  // 8 sixteen-byte units of this row
+        if constexpr (OUT == OUT_RAW32) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) u[j] = v[j];
+        } else {
+#pragma unroll
+            for (int j = 0; j < CW; ++j) {
+                const float a =
+                    (KIND == ptx::KIND_I8) ? static_cast<float>(static_cast<int>(v[j])) : __uint_as_float(v[j]);
+                v[j] = __float_as_uint(a * alpha);
+            }
+            if constexpr (OUT == OUT_F32) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) u[j] = v[j];
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    if constexpr (OUT == OUT_BF16) {
+                        __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                        u[j] = *reinterpret_cast<uint32_t*>(&h);
+                    } else {
+                        __half2 h = __floats2half2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                        u[j] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                }
+            }
+        }
+        const uint32_t row_addr = stage_base + buf * 4096u + static_cast<uint32_t>(lane) * 128u;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            ptx::st_shared_v4(row_addr + static_cast<uint32_t>((j ^ (lane & 7)) * 16), u[4 * j], u[4 * j + 1],
+                              u[4 * j + 2], u[4 * j + 3]);
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            ptx::tma_store_3d(tmap_c, stage_base + buf * 4096u, n0, row0, split);
+            ptx::tma_store_commit();
+        }
+        buf ^= 1u;
+    }
+}
+
 template <int BN, int STAGES>
 struct GemmSmem {
     static constexpr int kAStage = kBM * 128;
     static constexpr int kBStage = BN * 128;
     static constexpr int kTiles = STAGES * (kAStage + kBStage);
-    static constexpr int kBarOffset = kTiles;                    // full[STAGES], empty[STAGES], tfull[2], tempty[2]
+    static constexpr int kOutOffset = kTiles;                    // epilogue staging: 4 warps x 2 buffers x 4 KB
+    static constexpr int kBarOffset = kTiles + kEpilogueStagingBytes;  // full[STAGES], empty[STAGES], tfull[2], tempty[2]
     static constexpr int kMiscOffset = kBarOffset + (2 * STAGES + 4) * 8;  // tmem base, abort flag
     static constexpr int kTotal = kMiscOffset + 16;
     static constexpr int kDynamicBytes = kTotal + 1024;          // slack for the 1024-byte alignment
@@ -187,7 +256,7 @@ struct GemmSmem {
 template <int KIND, int BN, int STAGES, int OUT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
     using L = GemmSmem<BN, STAGES>;
     constexpr int ELT = (KIND == ptx::KIND_F16) ? 2 : 1;
     constexpr int BK = 128 / ELT;  // elements per 128-byte K block
@@ -228,6 +297,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     if (warp == 0 && lane == 0) {
         ptx::prefetch_tensormap(&tmap_a);
         ptx::prefetch_tensormap(&tmap_b);
+        if (p.c_tma_ok) ptx::prefetch_tensormap(&tmap_c);
     }
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
@@ -309,6 +379,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             if (p.scale_b != nullptr) alpha *= __ldg(p.scale_b);
         }
         uint32_t it = 0;
+        uint32_t out_buf = 0;
         for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++it) {
             const TileCoord t = decode_tile(w, p);
             const uint32_t acc = it & 1u;
@@ -319,20 +390,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint8_t* c_base = reinterpret_cast<uint8_t*>(p.C) +
                               static_cast<long long>(t.split) * p.split_stride * OutBytes<OUT>::value;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+            if (p.c_tma_ok) {
+                epilogue_tma<KIND, OUT, BN>(&tmap_c, t_addr, t.m_blk * kBM + quad * 32, p.M, t.n_blk * BN, p.N, t.split,
+                                            smem_base + L::kOutOffset + (warp - 2) * 8192, lane, alpha, out_buf);
+            } else {
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                const int n0 = t.n_blk * BN + c * 32;
-                if (n0 >= p.N) break;  // warp-uniform
-                uint32_t v[32];
-                ptx::tmem_ld_32x32b_x32(t_addr + c * 32, v);
-                ptx::tmem_ld_wait();
-                if (row < p.M)
-                    store_chunk<KIND, OUT>(c_base, p.ldc, row, n0, min(32, p.N - n0), p.c_vec_ok != 0, v, alpha);
+                for (int c = 0; c < BN / 32; ++c) {
+                    const int n0 = t.n_blk * BN + c * 32;
+                    if (n0 >= p.N) break;  // warp-uniform
+                    uint32_t v[32];
+                    ptx::tmem_ld_32x32b_x32(t_addr + c * 32, v);
+                    ptx::tmem_ld_wait();
+                    if (row < p.M)
+                        store_chunk<KIND, OUT>(c_base, p.ldc, row, n0, min(32, p.N - n0), p.c_vec_ok != 0, v, alpha);
+                }
             }
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bar_tempty + acc * 8);
         }
+        // every TMA store of this warp must have completed before the CTA may exit
+        if (lane == 0) ptx::tma_store_wait_all<0>();
     }
 
     // ---------------------------------------------------------------- teardown

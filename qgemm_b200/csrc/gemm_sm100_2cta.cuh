@@ -27,7 +27,8 @@ struct PairSmem {
     static constexpr int kAStage = 128 * 128;
     static constexpr int kBStage = 128 * 128;
     static constexpr int kTiles = kPairStages * (kAStage + kBStage);
-    static constexpr int kBarOffset = kTiles;
+    static constexpr int kOutOffset = kTiles;  // epilogue staging (see epilogue_tma)
+    static constexpr int kBarOffset = kTiles + kEpilogueStagingBytes;
     static constexpr int kMiscOffset = kBarOffset + (2 * kPairStages + 4) * 8;
     static constexpr int kTotal = kMiscOffset + 16;
     static constexpr int kDynamicBytes = kTotal + 1024;
@@ -37,7 +38,7 @@ struct PairSmem {
 template <int KIND, int OUT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                         const GemmParams p) {
+                         const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
     using L = PairSmem;
     constexpr int STAGES = kPairStages;
     constexpr int ELT = (KIND == ptx::KIND_F16) ? 2 : 1;
@@ -81,6 +82,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     if (warp == 0 && lane == 0) {
         ptx::prefetch_tensormap(&tmap_a);
         ptx::prefetch_tensormap(&tmap_b);
+        if (p.c_tma_ok) ptx::prefetch_tensormap(&tmap_c);
     }
     if (warp == 1) {
         ptx::tmem_alloc_pair(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
@@ -167,6 +169,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             if (p.scale_b != nullptr) alpha *= __ldg(p.scale_b);
         }
         uint32_t it = 0;
+        uint32_t out_buf = 0;
         for (int w = cluster_id; w < total_work; w += n_clusters, ++it) {
             const TileCoord t = decode_tile(w, p);
             const uint32_t acc = it & 1u;
@@ -178,20 +181,27 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             uint8_t* c_base = reinterpret_cast<uint8_t*>(p.C) +
                               static_cast<long long>(t.split) * p.split_stride * OutBytes<OUT>::value;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+            if (p.c_tma_ok) {
+                epilogue_tma<KIND, OUT, BN>(&tmap_c, t_addr, (t.m_blk * 2 + static_cast<int>(rank)) * 128 + quad * 32,
+                                            p.M, t.n_blk * BN, p.N, t.split,
+                                            smem_base + L::kOutOffset + (warp - 2) * 8192, lane, alpha, out_buf);
+            } else {
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                const int n0 = t.n_blk * BN + c * 32;
-                if (n0 >= p.N) break;
-                uint32_t v[32];
-                ptx::tmem_ld_32x32b_x32(t_addr + c * 32, v);
-                ptx::tmem_ld_wait();
-                if (row < p.M)
-                    store_chunk<KIND, OUT>(c_base, p.ldc, row, n0, min(32, p.N - n0), p.c_vec_ok != 0, v, alpha);
+                for (int c = 0; c < BN / 32; ++c) {
+                    const int n0 = t.n_blk * BN + c * 32;
+                    if (n0 >= p.N) break;
+                    uint32_t v[32];
+                    ptx::tmem_ld_32x32b_x32(t_addr + c * 32, v);
+                    ptx::tmem_ld_wait();
+                    if (row < p.M)
+                        store_chunk<KIND, OUT>(c_base, p.ldc, row, n0, min(32, p.N - n0), p.c_vec_ok != 0, v, alpha);
+                }
             }
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa_shared(bar_tempty + acc * 8, 0));
         }
+        if (lane == 0) ptx::tma_store_wait_all<0>();
     }
 
     // ---------------------------------------------------------------- teardown

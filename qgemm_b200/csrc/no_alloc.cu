@@ -102,6 +102,18 @@ int encode_operand(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, i
     return r == CUDA_SUCCESS ? QGEMM_OK : QGEMM_ERR_CUDA;
 }
 
+// [splits][M][ldw] 32-bit partial sums in the static scratch, for the kernel's TMA-store epilogue.
+int encode_partials(void* ptr, uint64_t M, uint64_t N, uint64_t ldw, uint64_t splits, CUtensorMap* out) {
+    const cuuint64_t dims[3] = {N, M, splits};
+    const cuuint64_t strides[2] = {ldw * 4, M * ldw * 4};
+    const cuuint32_t box[3] = {32u, 32u, 1u};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = g_static_encode(out, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, ptr, dims, strides, box, estr,
+                                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                       CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? QGEMM_OK : QGEMM_ERR_CUDA;
+}
+
 }  // namespace
 }  // namespace qgemm
 
@@ -160,6 +172,10 @@ extern "C" int qgemm_mix_gemm_splitk_static(int in_dtype, int out_dtype, const v
     rc = encode_operand(B, N, K, ldb, in_dtype, kTileN, &tb);
     if (rc != QGEMM_OK) return rc;
 
+    CUtensorMap tc;
+    rc = encode_partials(st->scratch, M, N, ldw, static_cast<uint64_t>(splits), &tc);
+    if (rc != QGEMM_OK) return rc;
+
     GemmParams p;
     std::memset(&p, 0, sizeof(p));
     p.C = st->scratch;
@@ -177,6 +193,7 @@ extern "C" int qgemm_mix_gemm_splitk_static(int in_dtype, int out_dtype, const v
     p.idesc = ptx::make_idesc(cfmt, fmt, fmt, kBM, kTileN);
     p.status = st->status;
     p.c_vec_ok = 1;
+    p.c_tma_ok = 1;
 
     const long long work = static_cast<long long>(p.m_tiles) * p.n_tiles * p.splits;
     if (work > 0x7fffffffLL) return QGEMM_ERR_UNSUPPORTED;
@@ -184,9 +201,9 @@ extern "C" int qgemm_mix_gemm_splitk_static(int in_dtype, int out_dtype, const v
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     cudaError_t e;
     switch (kind) {
-        case ptx::KIND_F16: e = launch_gemm_f16(kTileN, OUT_RAW32, ta, tb, p, grid, s); break;
-        case ptx::KIND_I8: e = launch_gemm_i8(kTileN, OUT_RAW32, ta, tb, p, grid, s); break;
-        default: e = launch_gemm_f8(kTileN, OUT_RAW32, ta, tb, p, grid, s); break;
+        case ptx::KIND_F16: e = launch_gemm_f16(kTileN, OUT_RAW32, ta, tb, tc, p, grid, s); break;
+        case ptx::KIND_I8: e = launch_gemm_i8(kTileN, OUT_RAW32, ta, tb, tc, p, grid, s); break;
+        default: e = launch_gemm_f8(kTileN, OUT_RAW32, ta, tb, tc, p, grid, s); break;
     }
     if (e != cudaSuccess) return QGEMM_ERR_CUDA;
     return splitk_reduce_launch(st->scratch, p.split_stride, p.ldc, splits, acc_int, C, static_cast<long long>(ldc),
