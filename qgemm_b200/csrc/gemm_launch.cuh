@@ -1,9 +1,38 @@
 // Host-side launch helper shared by the per-kind instantiation files.
 #pragma once
+#include <cstdlib>
+
 #include "gemm_sm100.cuh"
 #include "gemm_sm100_2cta.cuh"
 
 namespace qgemm {
+
+// Launch with the programmatic-stream-serialization attribute (see ptx::pdl_wait). QGEMM_PDL=0 in the
+// environment turns it off.
+inline bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = std::getenv("QGEMM_PDL");
+        v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 // Stages per tile width: a stage holds a 128x128-byte A tile and a BNx128-byte B tile.
 template <int BN>
@@ -27,8 +56,7 @@ cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    kernel<<<grid, kGemmThreads, smem, stream>>>(ta, tb, tc, p);
-    return cudaGetLastError();
+    return launch_pdl(kernel, dim3(grid), dim3(kGemmThreads), smem, stream, ta, tb, tc, p);
 }
 
 template <int KIND>
@@ -89,8 +117,7 @@ cudaError_t launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const 
     }
     if (clusters > max_clusters[dev]) clusters = max_clusters[dev];
     if (clusters < 1) clusters = 1;
-    kernel<<<2 * clusters, kGemmThreads, smem, stream>>>(ta, tb, tc, p);
-    return cudaGetLastError();
+    return launch_pdl(kernel, dim3(2 * clusters), dim3(kGemmThreads), smem, stream, ta, tb, tc, p);
 }
 
 template <int KIND>

@@ -307,6 +307,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above touched no global memory; from here on the predecessor's results are needed.
+    ptx::pdl_launch_dependents();
+    ptx::pdl_wait();
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer

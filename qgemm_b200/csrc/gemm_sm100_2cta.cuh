@@ -95,6 +95,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     ptx::cluster_wait();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    ptx::pdl_launch_dependents();
+    ptx::pdl_wait();
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (both CTAs)

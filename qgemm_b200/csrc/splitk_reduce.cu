@@ -5,7 +5,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
-#include "gemm_sm100.cuh"
+#include "gemm_launch.cuh"
 #include "qgemm_internal.h"
 
 namespace qgemm {
@@ -17,6 +17,8 @@ __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const uint32_t* __restrict__ partials, long long split_stride, long long ldw, int splits,
                      void* __restrict__ C, long long ldc, int M, int N, int out_kind,
                      const float* __restrict__ scale_a, const float* __restrict__ scale_b, int c_vec_ok) {
+    ptx::pdl_launch_dependents();
+    ptx::pdl_wait();
     const long long quads_per_row = ldw >> 2;
     const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= quads_per_row * M) return;
@@ -114,12 +116,14 @@ int splitk_reduce_launch(const void* partials, long long split_stride, long long
     if (blocks <= 0) return QGEMM_OK;
     if (blocks > 0x7fffffffLL) return QGEMM_ERR_UNSUPPORTED;
     const uint32_t* p = reinterpret_cast<const uint32_t*>(partials);
+    cudaError_t e;
     if (acc_is_int)
-        splitk_reduce_kernel<true><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
-            p, split_stride, ldw, splits, C, ldc, M, N, out_kind, scale_a, scale_b, c_vec_ok);
+        e = launch_pdl(splitk_reduce_kernel<true>, dim3(static_cast<unsigned>(blocks)), dim3(threads), 0, stream, p,
+                       split_stride, ldw, splits, C, ldc, M, N, out_kind, scale_a, scale_b, c_vec_ok);
     else
-        splitk_reduce_kernel<false><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
-            p, split_stride, ldw, splits, C, ldc, M, N, out_kind, scale_a, scale_b, c_vec_ok);
+        e = launch_pdl(splitk_reduce_kernel<false>, dim3(static_cast<unsigned>(blocks)), dim3(threads), 0, stream, p,
+                       split_stride, ldw, splits, C, ldc, M, N, out_kind, scale_a, scale_b, c_vec_ok);
+    if (e != cudaSuccess) return QGEMM_ERR_CUDA;
     return cudaGetLastError() == cudaSuccess ? QGEMM_OK : QGEMM_ERR_CUDA;
 }
 

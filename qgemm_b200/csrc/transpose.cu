@@ -16,6 +16,7 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 
+#include "gemm_launch.cuh"
 #include "qgemm_internal.h"
 
 namespace qgemm {
@@ -89,6 +90,9 @@ transpose_kernel(const void* __restrict__ in_v, void* __restrict__ out_v, int ro
     const int bc = tid % G::TBC;  // block column of this thread (lanes side by side along the row)
     const int br = tid / G::TBC;  // block row
 
+    ptx::pdl_launch_dependents();
+    ptx::pdl_wait();
+
     // ---- load the B x B block: rows r0 + br*B + i, columns c0 + bc*B .. +B-1
     uint4 blk[B];
     const long long gc = c0 + static_cast<long long>(bc) * B;
@@ -160,12 +164,14 @@ int transpose_launch(const void* in, void* out, size_t rows, size_t cols, size_t
     const int in_vec_ok = (reinterpret_cast<uintptr_t>(in) % 16 == 0) && ((ld_in * elem_bytes) % 16 == 0);
     const int out_vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && ((ld_out * elem_bytes) % 16 == 0);
     dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
+    cudaError_t e;
     if (elem_bytes == 2)
-        transpose_kernel<2><<<grid, TransposeGeom<2>::THREADS, 0, stream>>>(
-            in, out, (int)rows, (int)cols, (long long)ld_in, (long long)ld_out, in_vec_ok, out_vec_ok);
+        e = launch_pdl(transpose_kernel<2>, grid, dim3(TransposeGeom<2>::THREADS), 0, stream, in, out, (int)rows,
+                       (int)cols, (long long)ld_in, (long long)ld_out, in_vec_ok, out_vec_ok);
     else
-        transpose_kernel<1><<<grid, TransposeGeom<1>::THREADS, 0, stream>>>(
-            in, out, (int)rows, (int)cols, (long long)ld_in, (long long)ld_out, in_vec_ok, out_vec_ok);
+        e = launch_pdl(transpose_kernel<1>, grid, dim3(TransposeGeom<1>::THREADS), 0, stream, in, out, (int)rows,
+                       (int)cols, (long long)ld_in, (long long)ld_out, in_vec_ok, out_vec_ok);
+    if (e != cudaSuccess) return QGEMM_ERR_CUDA;
     return cudaGetLastError() == cudaSuccess ? QGEMM_OK : QGEMM_ERR_CUDA;
 }
 
