@@ -89,6 +89,27 @@ int qgemm_gemm_ex(int in_dtype, int out_dtype, int b_layout, const void* A, size
                   const float* scale_a, const float* scale_b, void* C, size_t ldc, size_t M, size_t N, size_t K,
                   const qgemm_tuning_t* tuning, qgemm_stream_t stream);
 
+/* How the M x K operand A is laid out in memory (block-scaled entry point only). */
+typedef enum {
+    QGEMM_A_ROW_MAJOR = 0, /* A[m*lda + k] */
+    QGEMM_A_COL_MAJOR = 1  /* A[m + k*lda]: how fp8_mm receives a (src/mix_gemm/hip_mix_gemm_kernel.cpp:96, 425-439) */
+} qgemm_a_layout_t;
+
+/*
+ * FP8 e4m3 GEMM with block scales. Replaces fp8_mm / FP8_GEMM_kernel, the one mixed kernel the reference
+ * implements (AMD only; src/mix_gemm/hip_mix_gemm_kernel.cpp:249-378, entry :508-516):
+ *   C[m,n] = sum_kb ( sum_{k in block kb} A[m,k] B[k,n] ) * a_scale[kb*M + m] * b_scale[kb*ceil(N/128) + n/128]
+ * with 128-wide K blocks (a_scale: one per row and block, "[m, k/128] col-major"; b_scale: one per 128 x 128
+ * block of B, "[k/128, n/128] row-major"; :124-169, :425-439), fp32 accumulation, one rounding to out_dtype
+ * (BF16 as the reference, or FP16 / FP32). A: see qgemm_a_layout_t; B: qgemm_b_layout_t (the reference passes
+ * a col-major A and a row-major [K,N] B; both are relaid out to K-major scratch by the transpose kernel, K-major
+ * operands are used in place and need 16-byte alignment). The FP8 format is OCP e4m3 (include/gpu_type.h:7).
+ * Any M, N, K > 0 (the reference needs all three divisible by 32, :442-505).
+ */
+int qgemm_fp8_block_scaled_gemm(int out_dtype, int a_layout, int b_layout, const void* A, size_t lda, const void* B,
+                                size_t ldb, const float* a_scale, const float* b_scale, void* C, size_t ldc, size_t M,
+                                size_t N, size_t K, qgemm_stream_t stream);
+
 /*
  * out[c*ld_out + r] = in[r*ld_in + c] for 1- or 2-byte elements. Replaces matrix_transpose<T>
  * (src/include/matrix_transpose.h:3-4; src/transpose/transpose.cu:60-77). Any rows, cols >= 0;

@@ -179,6 +179,24 @@ def gemm_i8_blocked(A: np.ndarray, Bt: np.ndarray) -> np.ndarray:
     return Cm
 
 
+def gemm_fp8_block_scaled(A: np.ndarray, Bt: np.ndarray, a_scale: np.ndarray, b_scale: np.ndarray,
+                          out_kind: int = OUT_F32) -> np.ndarray:
+    """Block-scaled FP8 GEMM on decoded operand values: A [M,K], Bt [N,K], a_scale [ceil(K/128), M],
+    b_scale [ceil(K/128), ceil(N/128)]. Returns fp32 values or bf16/fp16 bit patterns [M,N]."""
+    A = np.ascontiguousarray(A, np.float32)
+    Bt = np.ascontiguousarray(Bt, np.float32)
+    a_scale = np.ascontiguousarray(a_scale, np.float32)
+    b_scale = np.ascontiguousarray(b_scale, np.float32)
+    M, K = A.shape
+    N = Bt.shape[0]
+    kbs, nbs = -(-K // 128), -(-N // 128)
+    assert Bt.shape[1] == K and a_scale.shape == (kbs, M) and b_scale.shape == (kbs, nbs)
+    out = np.empty((M, N), np.float32 if out_kind == OUT_F32 else np.uint16)
+    lib().oracle_gemm_fp8_block_scaled(_p(A), _sz(K), _p(Bt), _sz(K), _p(a_scale), _p(b_scale), _p(out), _sz(N),
+                                       _sz(M), _sz(N), _sz(K), C.c_int(out_kind))
+    return out
+
+
 def scale_cast(acc: np.ndarray, sA: float, sB: float, out_kind: int) -> np.ndarray:
     """out = cast(sA*sB*acc): fp32 values, or bf16 / fp16 bit patterns."""
     acc = np.ascontiguousarray(acc)

@@ -275,6 +275,38 @@ void oracle_scale_cast_f32(const float* acc, size_t n, float sA, float sB, int o
     }
 }
 
+/* Block-scaled FP8 GEMM, the one mixed kernel the reference implements
+ * (src/mix_gemm/hip_mix_gemm_kernel.cpp:249-378). Operands are the decoded e4m3 values held as fp32:
+ * A [M,K] row-major, Bt [N,K] (K-major). Scales as the reference lays them out (:124-169, :425-439):
+ *   a_scale[kb*M + m]            one per row and 128-wide K block,
+ *   b_scale[kb*ceil(N/128) + nb] one per 128 x 128 block of B.
+ * Each K block is accumulated on its own in fp32 from zero and then folded in as
+ * acc += local * a_scale * b_scale (:193-244); the result is rounded once to the output type
+ * (:363-367). out_kind: 0 = fp32, 1 = bf16 bits, 2 = fp16 bits. */
+void oracle_gemm_fp8_block_scaled(const float* A, size_t lda, const float* Bt, size_t ldb, const float* a_scale,
+                                  const float* b_scale, void* C, size_t ldc, size_t M, size_t N, size_t K,
+                                  int out_kind) {
+    const size_t SB = 128;
+    const size_t nbs = (N + SB - 1) / SB;
+#pragma omp parallel for schedule(static)
+    for (ptrdiff_t m = 0; m < (ptrdiff_t)M; ++m) {
+        for (size_t n = 0; n < N; ++n) {
+            const float* a = A + m * lda;
+            const float* b = Bt + n * ldb;
+            float acc = 0.0f;
+            for (size_t k0 = 0, kb = 0; k0 < K; k0 += SB, ++kb) {
+                size_t k1 = k0 + SB < K ? k0 + SB : K;
+                float local = 0.0f;
+                for (size_t k = k0; k < k1; ++k) local += a[k] * b[k];
+                acc += local * a_scale[kb * M + m] * b_scale[kb * nbs + n / SB];
+            }
+            if (out_kind == 0) ((float*)C)[m * ldc + n] = acc;
+            else if (out_kind == 1) ((uint16_t*)C)[m * ldc + n] = oracle_f32_to_bf16(acc);
+            else ((uint16_t*)C)[m * ldc + n] = oracle_f32_to_f16(acc);
+        }
+    }
+}
+
 /* Transpose: out[n*M + m] = in[m*N + n] (src/transpose/transpose.cu:42,57), any element size,
  * with explicit leading dimensions (in elements). */
 void oracle_transpose(const void* in, void* out, size_t rows, size_t cols, size_t ld_in, size_t ld_out,

@@ -27,6 +27,7 @@ C_ABI_SYMBOLS = (
     "qgemm_gemm", "qgemm_mix_gemm", "qgemm_gemm_ex", "qgemm_transpose", "qgemm_workspace_reserve",
     "qgemm_workspace_bytes", "qgemm_workspace_query", "qgemm_device_status", "qgemm_shutdown",
     "qgemm_status_string", "qgemm_version", "qgemm_mix_gemm_splitk_static",
+    "qgemm_fp8_block_scaled_gemm",
 )
 
 
@@ -67,6 +68,8 @@ def lib() -> C.CDLL:
         L.qgemm_status_string.restype = C.c_char_p
         L.qgemm_mix_gemm_splitk_static.argtypes = [i, i, vp, sz, vp, sz, fp, fp, vp, sz, sz, sz, sz, i, vp]
         L.qgemm_mix_gemm_splitk_static.restype = i
+        L.qgemm_fp8_block_scaled_gemm.argtypes = [i, i, i, vp, sz, vp, sz, fp, fp, vp, sz, sz, sz, sz, vp]
+        L.qgemm_fp8_block_scaled_gemm.restype = i
         for name in ("qgemm_gemm", "qgemm_mix_gemm", "qgemm_gemm_ex", "qgemm_transpose", "qgemm_workspace_reserve",
                      "qgemm_device_status", "qgemm_shutdown", "qgemm_version"):
             getattr(L, name).restype = i
@@ -102,7 +105,7 @@ def _dtype_code(t) -> int:
 def _require_cuda_2d(name, t):
     if not t.is_cuda:
         raise QgemmError(ERR_INVALID_ARG, f"{name} must be a CUDA tensor (there is no CPU path)")
-    if t.dim() != 2 or t.stride(1) != 1:
+    if t.dim() != 2 or (t.stride(1) != 1 and t.shape[1] > 1):
         raise QgemmError(ERR_INVALID_ARG, f"{name} must be 2-D with unit inner stride")
 
 
@@ -166,6 +169,43 @@ def fp8_mm(a, b, a_scale, b_scale, c) -> None:
     """fp8-e4m3 a [m,k], b [n,k], per-matrix float32 scales -> c [m,n]
     (src/mix_gemm/hip_mix_gemm_kernel.cpp:508-516; per-matrix instead of block scales)."""
     _gemm(a, b, a_scale, b_scale, c, True, None, mixed=True)
+
+
+A_ROW_MAJOR, A_COL_MAJOR = 0, 1
+
+
+def fp8_block_mm(a, b, a_scale, b_scale, c, reference_layout: bool = True) -> None:
+    """Block-scaled FP8 GEMM, fp8_mm(a, b, as, bs, c) of src/mix_gemm/hip_mix_gemm_kernel.cpp:425-439,508-516.
+
+    With ``reference_layout`` the operands are laid out as the reference takes them: ``a`` is the
+    [m,k] matrix stored column-major, i.e. a contiguous tensor of shape [k, m]; ``b`` is [n,k]
+    column-major, i.e. a contiguous [k, n]; otherwise ``a`` is [m,k] and ``b`` is [n,k], both row-major
+    (K-major). ``a_scale`` [ceil(k/128), m] and ``b_scale`` [ceil(k/128), ceil(n/128)] are float32 (the
+    reference's "[m, k/128] col-major" and "[k/128, n/128] row-major"). ``c`` [m,n] bf16/fp16/fp32."""
+    torch = _torch()
+    for name, t in (("a", a), ("b", b), ("c", c), ("a_scale", a_scale), ("b_scale", b_scale)):
+        _require_cuda_2d(name, t)
+    M, N = c.shape
+    if reference_layout:
+        K = a.shape[0]
+        ok = tuple(a.shape) == (K, M) and tuple(b.shape) == (K, N)
+        a_layout, b_layout = A_COL_MAJOR, B_ROW_MAJOR
+    else:
+        K = a.shape[1]
+        ok = tuple(a.shape) == (M, K) and tuple(b.shape) == (N, K)
+        a_layout, b_layout = A_ROW_MAJOR, B_K_MAJOR
+    kbs, nbs = -(-K // 128), -(-N // 128)
+    ok = ok and tuple(a_scale.shape) == (kbs, M) and tuple(b_scale.shape) == (kbs, nbs)
+    ok = ok and a_scale.dtype == torch.float32 and b_scale.dtype == torch.float32
+    ok = ok and a_scale.is_contiguous() and b_scale.is_contiguous()
+    if not ok or _dtype_code(a) != FP8_E4M3 or _dtype_code(b) != FP8_E4M3:
+        raise QgemmError(ERR_INVALID_ARG, "fp8_block_mm: shape, dtype or layout mismatch")
+    with torch.cuda.device(a.device):
+        rc = lib().qgemm_fp8_block_scaled_gemm(
+            _dtype_code(c), a_layout, b_layout, a.data_ptr(), max(a.stride(0), a.shape[1]), b.data_ptr(),
+            max(b.stride(0), b.shape[1]), a_scale.data_ptr(), b_scale.data_ptr(), c.data_ptr(), max(c.stride(0), N),
+            M, N, K, _stream_ptr(a))
+    _check(rc, "qgemm_fp8_block_scaled_gemm")
 
 
 STATIC_SCRATCH_BYTES = 32 << 20  # QGEMM_STATIC_SCRATCH_BYTES

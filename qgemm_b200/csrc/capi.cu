@@ -250,7 +250,12 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
         best.splits = 1;
         best.kb_per_split = kb_total;
     }
-    best.group_m = want_group > 0 ? want_group : (best.pair ? 8 : (best.bn == 256 ? 16 : 8));
+    // Tile rows per scheduling group: as many as keep the group's A panel (rows x K bytes) near 32 MiB, so that
+    // it stays in L2 while the B panels stream past it.
+    const long long panel_rows = (32ll << 20) / (static_cast<long long>(kb_total) * 128);
+    const int tile_m = best.pair ? kPairTileM : kBM;
+    const int auto_group = static_cast<int>(std::max<long long>(4, std::min<long long>(4096, panel_rows / tile_m)));
+    best.group_m = want_group > 0 ? want_group : auto_group;
     return best;
 }
 
@@ -437,6 +442,89 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     return QGEMM_OK;
 }
 
+int blockscale_dispatch(int out_dtype, int a_layout, int b_layout, const void* A, size_t lda, const void* B,
+                        size_t ldb, const float* a_scale, const float* b_scale, void* C, size_t ldc, size_t M, size_t N,
+                        size_t K, cudaStream_t stream) {
+    if (M == 0 || N == 0) return QGEMM_OK;
+    if (A == nullptr || B == nullptr || C == nullptr || a_scale == nullptr || b_scale == nullptr || K == 0)
+        return QGEMM_ERR_INVALID_ARG;
+    if (a_layout != QGEMM_A_ROW_MAJOR && a_layout != QGEMM_A_COL_MAJOR) return QGEMM_ERR_INVALID_ARG;
+    if (b_layout != QGEMM_B_ROW_MAJOR && b_layout != QGEMM_B_K_MAJOR) return QGEMM_ERR_INVALID_ARG;
+    if (lda < (a_layout == QGEMM_A_ROW_MAJOR ? K : M) || ldb < (b_layout == QGEMM_B_K_MAJOR ? K : N) || ldc < N)
+        return QGEMM_ERR_INVALID_ARG;
+    if (M > 0x7fffff00ull || N > 0x7fffff00ull || K > 0x7fffff00ull) return QGEMM_ERR_INVALID_ARG;
+    const int out_kind = out_kind_of(out_dtype);
+    if (out_kind != OUT_F32 && out_kind != OUT_BF16 && out_kind != OUT_F16) return QGEMM_ERR_UNSUPPORTED;
+    const int out_bytes = (out_kind == OUT_F32) ? 4 : 2;
+
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState* st = nullptr;
+    int rc = get_state(&st);
+    if (rc != QGEMM_OK) return rc;
+
+    // Operands that arrive M-major / N-major are relaid out to K-major scratch: [A' | B'].
+    const size_t ldk = round_up(K, 16);
+    const size_t a_bytes = (a_layout == QGEMM_A_COL_MAJOR) ? round_up(M * ldk, 256) : 0;
+    const size_t b_bytes = (b_layout == QGEMM_B_ROW_MAJOR) ? round_up(N * ldk, 256) : 0;
+    rc = ensure_workspace(*st, a_bytes + b_bytes);
+    if (rc != QGEMM_OK) return rc;
+    const void* a_k = A;
+    size_t lda_k = lda;
+    if (a_layout == QGEMM_A_COL_MAJOR) {
+        rc = transpose_launch(A, st->ws, K, M, lda, ldk, 1, stream);  // in: [K rows][M cols] -> out [M][K]
+        if (rc != QGEMM_OK) return rc;
+        a_k = st->ws;
+        lda_k = ldk;
+    } else if (reinterpret_cast<uintptr_t>(A) % 16 != 0 || lda % 16 != 0) {
+        return QGEMM_ERR_ALIGNMENT;
+    }
+    const void* b_k = B;
+    size_t ldb_k = ldb;
+    if (b_layout == QGEMM_B_ROW_MAJOR) {
+        void* dst = static_cast<uint8_t*>(st->ws) + a_bytes;
+        rc = transpose_launch(B, dst, K, N, ldb, ldk, 1, stream);
+        if (rc != QGEMM_OK) return rc;
+        b_k = dst;
+        ldb_k = ldk;
+    } else if (reinterpret_cast<uintptr_t>(B) % 16 != 0 || ldb % 16 != 0) {
+        return QGEMM_ERR_ALIGNMENT;
+    }
+
+    CUtensorMap ta, tb, tc;
+    rc = make_operand_map(a_k, M, K, lda_k, QGEMM_DTYPE_FP8_E4M3, kBM, &ta);
+    if (rc != QGEMM_OK) return rc;
+    rc = make_operand_map(b_k, N, K, ldb_k, QGEMM_DTYPE_FP8_E4M3, 128u, &tb);
+    if (rc != QGEMM_OK) return rc;
+
+    BlockScaleParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.C = C;
+    p.ldc = static_cast<long long>(ldc);
+    p.M = static_cast<int>(M);
+    p.N = static_cast<int>(N);
+    p.K = static_cast<int>(K);
+    p.m_tiles = static_cast<int>((M + kBM - 1) / kBM);
+    p.n_tiles = static_cast<int>((N + 127) / 128);
+    p.kb_total = static_cast<int>((K + 127) / 128);
+    p.n_scale_blocks = p.n_tiles;
+    p.group_m = env_int("QGEMM_GROUP_M") > 0
+                    ? env_int("QGEMM_GROUP_M")
+                    : static_cast<int>(std::max<long long>(4, std::min<long long>(4096, (32ll << 20) / (128ll * p.kb_total * kBM))));
+    p.idesc = ptx::make_idesc(1u, 0u, 0u, kBM, 128u);
+    p.a_scale = a_scale;
+    p.b_scale = b_scale;
+    p.status = st->status;
+    std::memset(&tc, 0, sizeof(tc));
+    if (reinterpret_cast<uintptr_t>(C) % 16 == 0 && (ldc * out_bytes) % 16 == 0 &&
+        env_int("QGEMM_DIRECT_STORE") == 0)
+        p.c_tma_ok = make_output_map(C, M, N, ldc, 1, out_kind, &tc) == QGEMM_OK ? 1 : 0;
+
+    const long long work = static_cast<long long>(p.m_tiles) * p.n_tiles;
+    if (work > 0x7fffffffLL) return QGEMM_ERR_UNSUPPORTED;
+    const int grid = static_cast<int>(std::min<long long>(work, st->sm_count));
+    return launch_fp8_blockscale(out_kind, ta, tb, tc, p, grid, stream) == cudaSuccess ? QGEMM_OK : QGEMM_ERR_CUDA;
+}
+
 }  // namespace
 
 }  // namespace qgemm
@@ -470,6 +558,13 @@ int qgemm_mix_gemm(int in_dtype, int out_dtype, int b_layout, const void* A, siz
         return QGEMM_ERR_UNSUPPORTED;
     return gemm_dispatch(in_dtype, out_dtype, b_layout, A, lda, B, ldb, scale_a, scale_b, C, ldc, M, N, K, nullptr,
                          reinterpret_cast<cudaStream_t>(stream));
+}
+
+int qgemm_fp8_block_scaled_gemm(int out_dtype, int a_layout, int b_layout, const void* A, size_t lda, const void* B,
+                                size_t ldb, const float* a_scale, const float* b_scale, void* C, size_t ldc, size_t M,
+                                size_t N, size_t K, qgemm_stream_t stream) {
+    return blockscale_dispatch(out_dtype, a_layout, b_layout, A, lda, B, ldb, a_scale, b_scale, C, ldc, M, N, K,
+                               reinterpret_cast<cudaStream_t>(stream));
 }
 
 int qgemm_transpose(const void* in, void* out, size_t rows, size_t cols, size_t ld_in, size_t ld_out,

@@ -139,6 +139,24 @@ cudaError_t launch_gemm_pair_i8(int out, const CUtensorMap& ta, const CUtensorMa
 cudaError_t launch_gemm_pair_f8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                                 int clusters, cudaStream_t stream);
 
+// Block-scaled FP8 GEMM (gemm_blockscale.cu): 128 x 128 tiles, one partial accumulator per 128-wide K block.
+struct BlockScaleParams {
+    void* C;
+    long long ldc;
+    int M, N, K;
+    int m_tiles, n_tiles;
+    int group_m;         // tile rows per scheduling group
+    int kb_total;        // 128-element K blocks
+    int n_scale_blocks;  // ceil(N / 128): row length of b_scale
+    uint32_t idesc;
+    const float* a_scale;  // [kb_total][M]
+    const float* b_scale;  // [kb_total][n_scale_blocks]
+    int* status;
+    int c_tma_ok;
+};
+cudaError_t launch_fp8_blockscale(int out_kind, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                                  const BlockScaleParams& p, int grid, cudaStream_t stream);
+
 // Defined one per translation unit so the kinds compile in parallel.
 cudaError_t launch_gemm_f16(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                             int grid, cudaStream_t stream);

@@ -91,6 +91,25 @@ def test_gemm_i8_exact(oracle, M, N, K):
     assert np.array_equal(oracle.gemm_i8_rows(A, Bt, 0, m1), truth[:m1])
 
 
+def test_block_scaled_fp8_against_numpy(oracle):
+    rng = np.random.default_rng(8)
+    M, N, K = 50, 300, 400
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    Bt = rng.standard_normal((N, K)).astype(np.float32)
+    kbs, nbs = -(-K // 128), -(-N // 128)
+    sa = rng.uniform(0.5, 2, (kbs, M)).astype(np.float32)
+    sb = rng.uniform(0.5, 2, (kbs, nbs)).astype(np.float32)
+    ref = np.zeros((M, N))
+    for kb in range(kbs):
+        k0, k1 = kb * 128, min(K, kb * 128 + 128)
+        loc = A[:, k0:k1].astype(np.float64) @ Bt[:, k0:k1].astype(np.float64).T
+        ref += loc * sa[kb][:, None] * np.repeat(sb[kb], 128)[:N][None, :]
+    c = oracle.gemm_fp8_block_scaled(A, Bt, sa, sb)
+    assert oracle.rel_l2(c, ref) < 2e-6
+    bits = oracle.gemm_fp8_block_scaled(A, Bt, sa, sb, oracle.OUT_BF16)
+    assert np.array_equal(bits, oracle.round_bf16(c)[0])
+
+
 def test_int8_accumulator_cannot_overflow_at_benchmark_k():
     assert 8192 * 127 * 127 < 2 ** 31
 
