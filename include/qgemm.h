@@ -119,6 +119,18 @@ int qgemm_transpose(const void* in, void* out, size_t rows, size_t cols, size_t 
                     size_t elem_bytes, qgemm_stream_t stream);
 
 /*
+ * Per-matrix quantisation, the step in front of qgemm_mix_gemm (the reference's roadmap names it,
+ * develop.md:9-12, README.md:1, but has no kernel for it):
+ *   *amax_out = max |in|;  *scale_out = amax / qmax (qmax = 448 for FP8_E4M3, 127 for INT8; 1 if amax == 0);
+ *   out[r*ld_out + c] = round_to_nearest_even(in[r*ld_in + c] / scale), saturated to +-qmax.
+ * in: FP32 or BF16 [rows, cols]; out: FP8_E4M3 or INT8, same shape. scale_out and amax_out are DEVICE pointers
+ * to one float each (amax_out doubles as the reduction's scratch); pass scale_out as scale_a / scale_b of
+ * qgemm_mix_gemm. Everything stays on `stream`; nothing is read back to the host.
+ */
+int qgemm_quantize(int in_dtype, int out_dtype, const void* in, size_t ld_in, void* out, size_t ld_out,
+                   float* scale_out, float* amax_out, size_t rows, size_t cols, qgemm_stream_t stream);
+
+/*
  * Library-owned scratch of the current device (relaid-out B, split-K partial sums). It grows on
  * demand (a growth step synchronises the device and allocates); reserve it up front to keep
  * allocation out of timed or captured regions. The reference API has no workspace argument

@@ -37,6 +37,7 @@ def lib() -> C.CDLL:
             build()
         _lib = C.CDLL(_LIB_PATH)
         _lib.oracle_quantize_e4m3.restype = C.c_float
+        _lib.oracle_quantize_int8.restype = C.c_float
         _lib.oracle_num_threads.restype = C.c_int
     return _lib
 
@@ -82,6 +83,14 @@ def quantize_e4m3(x: np.ndarray):
     val = np.empty(x.shape, np.float32)
     scale = lib().oracle_quantize_e4m3(_p(x), _p(bits), _p(val), _sz(x.size))
     return bits, val, float(scale)
+
+
+def quantize_int8(x: np.ndarray):
+    """Per-matrix int8 quantisation: returns (int8 values, scale = amax/127)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    q = np.empty(x.shape, np.int8)
+    scale = lib().oracle_quantize_int8(_p(x), _p(q), _sz(x.size))
+    return q, float(scale)
 
 
 def e4m3_decode(bits: np.ndarray) -> np.ndarray:

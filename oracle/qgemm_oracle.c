@@ -155,6 +155,20 @@ float oracle_quantize_e4m3(const float* in, uint8_t* out_bits, float* out_f32, s
     return scale;
 }
 
+/* Per-matrix int8 quantisation: scale = amax / 127, q = clamp(round_to_nearest_even(x / scale), -127, 127). */
+float oracle_quantize_int8(const float* in, int8_t* out, size_t n) {
+    float amax = 0.0f;
+    for (size_t i = 0; i < n; ++i) { float a = fabsf(in[i]); if (a > amax) amax = a; }
+    float scale = amax > 0.0f ? amax / 127.0f : 1.0f;
+    for (size_t i = 0; i < n; ++i) {
+        float r = rintf(in[i] / scale);
+        if (r > 127.0f) r = 127.0f;
+        if (r < -127.0f) r = -127.0f;
+        out[i] = (int8_t)(int)r;
+    }
+    return scale;
+}
+
 void oracle_e4m3_decode(const uint8_t* in, float* out, size_t n) {
     for (size_t i = 0; i < n; ++i) out[i] = oracle_e4m3_to_f32(in[i]);
 }

@@ -27,7 +27,7 @@ C_ABI_SYMBOLS = (
     "qgemm_gemm", "qgemm_mix_gemm", "qgemm_gemm_ex", "qgemm_transpose", "qgemm_workspace_reserve",
     "qgemm_workspace_bytes", "qgemm_workspace_query", "qgemm_device_status", "qgemm_shutdown",
     "qgemm_status_string", "qgemm_version", "qgemm_mix_gemm_splitk_static",
-    "qgemm_fp8_block_scaled_gemm",
+    "qgemm_fp8_block_scaled_gemm", "qgemm_quantize",
 )
 
 
@@ -70,6 +70,8 @@ def lib() -> C.CDLL:
         L.qgemm_mix_gemm_splitk_static.restype = i
         L.qgemm_fp8_block_scaled_gemm.argtypes = [i, i, i, vp, sz, vp, sz, fp, fp, vp, sz, sz, sz, sz, vp]
         L.qgemm_fp8_block_scaled_gemm.restype = i
+        L.qgemm_quantize.argtypes = [i, i, vp, sz, vp, sz, fp, fp, sz, sz, vp]
+        L.qgemm_quantize.restype = i
         for name in ("qgemm_gemm", "qgemm_mix_gemm", "qgemm_gemm_ex", "qgemm_transpose", "qgemm_workspace_reserve",
                      "qgemm_device_status", "qgemm_shutdown", "qgemm_version"):
             getattr(L, name).restype = i
@@ -172,6 +174,27 @@ def fp8_mm(a, b, a_scale, b_scale, c) -> None:
 
 
 A_ROW_MAJOR, A_COL_MAJOR = 0, 1
+
+
+def quantize(x, out_dtype, out=None):
+    """Per-matrix quantisation of a float32 / bfloat16 CUDA matrix to ``torch.float8_e4m3fn`` or ``torch.int8``.
+    Returns ``(q, scale)`` with ``scale`` a 1-element float32 CUDA tensor (amax/448 or amax/127) ready to be
+    passed to :func:`mix_gemm`; nothing is synchronised or copied to the host."""
+    torch = _torch()
+    _require_cuda_2d("x", x)
+    rows, cols = x.shape
+    if out is None:
+        out = torch.empty((rows, cols), dtype=out_dtype, device=x.device)
+    _require_cuda_2d("out", out)
+    if tuple(out.shape) != (rows, cols) or out.dtype != out_dtype:
+        raise QgemmError(ERR_INVALID_ARG, "out must have the input's shape and the requested dtype")
+    sc = torch.empty(2, dtype=torch.float32, device=x.device)  # [scale, amax]
+    with torch.cuda.device(x.device):
+        rc = lib().qgemm_quantize(_dtype_code(x), _dtype_code(out), x.data_ptr(), max(x.stride(0), cols),
+                                  out.data_ptr(), max(out.stride(0), cols), sc.data_ptr(), sc.data_ptr() + 4, rows,
+                                  cols, _stream_ptr(x))
+    _check(rc, "qgemm_quantize")
+    return out, sc[:1]
 
 
 def fp8_block_mm(a, b, a_scale, b_scale, c, reference_layout: bool = True) -> None:

@@ -509,7 +509,7 @@ int blockscale_dispatch(int out_dtype, int a_layout, int b_layout, const void* A
     p.n_scale_blocks = p.n_tiles;
     p.group_m = env_int("QGEMM_GROUP_M") > 0
                     ? env_int("QGEMM_GROUP_M")
-                    : static_cast<int>(std::max<long long>(4, std::min<long long>(4096, (32ll << 20) / (128ll * p.kb_total * kBM))));
+                    : static_cast<int>(std::max<long long>(4, std::min<long long>(4096, (16ll << 20) / (128ll * p.kb_total * kBM))));
     p.idesc = ptx::make_idesc(1u, 0u, 0u, kBM, 128u);
     p.a_scale = a_scale;
     p.b_scale = b_scale;
@@ -565,6 +565,12 @@ int qgemm_fp8_block_scaled_gemm(int out_dtype, int a_layout, int b_layout, const
                                 size_t N, size_t K, qgemm_stream_t stream) {
     return blockscale_dispatch(out_dtype, a_layout, b_layout, A, lda, B, ldb, a_scale, b_scale, C, ldc, M, N, K,
                                reinterpret_cast<cudaStream_t>(stream));
+}
+
+int qgemm_quantize(int in_dtype, int out_dtype, const void* in, size_t ld_in, void* out, size_t ld_out,
+                   float* scale_out, float* amax_out, size_t rows, size_t cols, qgemm_stream_t stream) {
+    return quantize_launch(in_dtype, out_dtype, in, ld_in, out, ld_out, scale_out, amax_out, rows, cols,
+                           reinterpret_cast<cudaStream_t>(stream));
 }
 
 int qgemm_transpose(const void* in, void* out, size_t rows, size_t cols, size_t ld_in, size_t ld_out,

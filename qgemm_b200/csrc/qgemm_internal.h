@@ -18,4 +18,8 @@ int splitk_reduce_launch(const void* partials, long long split_stride, long long
                          void* C, long long ldc, int M, int N, int out_kind, const float* scale_a,
                          const float* scale_b, cudaStream_t stream);
 
+// Per-matrix quantisation: amax reduction, scale = amax / qmax, out = round(in / scale) (quantize.cu).
+int quantize_launch(int in_dtype, int out_dtype, const void* in, size_t ld_in, void* out, size_t ld_out,
+                    float* scale_out, float* amax_out, size_t rows, size_t cols, cudaStream_t stream);
+
 }  // namespace qgemm
