@@ -30,7 +30,7 @@ def test_cpp_harness(qlib, dev):
         if problem and len(parts) >= 7 and parts[4] in ("PASS", "FAIL"):
             float(parts[1]), float(parts[2]), float(parts[6])  # the columns the reference's parser reads
             rows.setdefault(problem, []).append((parts[0], parts[4]))
-    assert len(rows) >= 6
+    assert len(rows) >= 5  # distinct (M, N, K) keys; several precisions share 4096^3 and 1024^3
     for lst in rows.values():
         assert all(v == "PASS" for _, v in lst), lst
         assert any(n.startswith(("GEMM_kernel", "MIX_GEMM")) for n, _ in lst)
