@@ -57,6 +57,8 @@ typedef struct {
     int group_m; /* tile rows per scheduling group */
     int max_ctas; /* cap on the persistent grid (testing) */
     int cta_pair; /* 1 = pair two CTAs on 256x256 tiles (tcgen05 cta_group::2), -1 = never, 0 = heuristic */
+    int relayout_b; /* row-major B: 1 = always relay it out to K-major with the transpose kernel first,
+                       0 = read it in place (MN-major tensor-core operand) when its base and ldb are 16-byte aligned */
 } qgemm_tuning_t;
 
 /*
@@ -67,8 +69,10 @@ typedef struct {
  *   C: [M,N] row-major, ldc.   in_dtype x out_dtype: {BF16,FP16} -> {FP32,BF16,FP16} (fp32
  *   accumulate), INT8 -> INT32 (exact).
  * A, and B when K-major, need a 16-byte aligned base and ld*sizeof(T) % 16 == 0 (the reference
- * needs the same for its float4 / cp.async loads). Row-major B of any alignment is relaid out
- * into library scratch first.
+ * needs the same for its float4 / cp.async loads). A row-major B that is aligned the same way is read in
+ * place as an MN-major tensor-core operand; one that is not (or when qgemm_tuning_t.relayout_b / the
+ * environment variable QGEMM_RELAYOUT_B=1 asks for it) is first relaid out to K-major in library scratch
+ * by the transpose kernel.
  */
 int qgemm_gemm(int in_dtype, int out_dtype, int b_layout, const void* A, size_t lda, const void* B, size_t ldb,
                void* C, size_t ldc, size_t M, size_t N, size_t K, qgemm_stream_t stream);
@@ -139,7 +143,7 @@ int qgemm_quantize(int in_dtype, int out_dtype, const void* in, size_t ld_in, vo
 int qgemm_workspace_reserve(size_t bytes);
 size_t qgemm_workspace_bytes(void);
 
-/* Bytes of scratch a call with these arguments would use (0 if none). */
+/* Bytes of scratch a call with these arguments would use at most (row-major B counted as relaid out). */
 size_t qgemm_workspace_query(int in_dtype, int b_layout, size_t M, size_t N, size_t K, const qgemm_tuning_t* tuning);
 
 /*

@@ -34,7 +34,7 @@ C_ABI_SYMBOLS = (
 class Tuning(C.Structure):
     """qgemm_tuning_t: zero fields mean "library heuristic"."""
     _fields_ = [("tile_n", C.c_int), ("split_k", C.c_int), ("group_m", C.c_int), ("max_ctas", C.c_int),
-                ("cta_pair", C.c_int)]
+                ("cta_pair", C.c_int), ("relayout_b", C.c_int)]
 
 
 class QgemmError(RuntimeError):

@@ -211,7 +211,7 @@ double estimate(int bn, bool pair, int splits, size_t M, size_t N, int kb_total,
     return t;
 }
 
-Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuning_t* tuning) {
+Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuning_t* tuning, int min_bn = 64) {
     int want_bn = tuning ? tuning->tile_n : 0;
     int want_split = tuning ? tuning->split_k : 0;
     int want_group = tuning ? tuning->group_m : 0;
@@ -229,6 +229,7 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
         if (c.pair && (want_pair < 0 || (want_bn && want_bn != 256))) continue;
         if (!c.pair && want_pair > 0) continue;
         if (want_bn && c.bn != want_bn) continue;
+        if (c.bn < min_bn) continue;
         const int max_split = want_split ? want_split : std::min(kb_total, 16);
         for (int s = want_split ? want_split : 1; s <= max_split; ++s) {
             if (s > kb_total) break;
@@ -301,7 +302,7 @@ struct Plan {
 };
 
 int make_plan(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, size_t K, int sms,
-              const qgemm_tuning_t* tuning, Plan* p) {
+              const qgemm_tuning_t* tuning, Plan* p, bool b_direct = false) {
     if (!type_info(in_dtype, &p->ti)) return QGEMM_ERR_UNSUPPORTED;
     p->out_kind = out_kind_of(out_dtype);
     if (p->out_kind < 0) return QGEMM_ERR_UNSUPPORTED;
@@ -310,9 +311,12 @@ int make_plan(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, siz
     if (M > 0x7fffff00ull || N > 0x7fffff00ull || K > 0x7fffff00ull) return QGEMM_ERR_INVALID_ARG;
     const size_t kblk = 128 / p->ti.elem_bytes;
     p->kb_total = static_cast<int>((K + kblk - 1) / kblk);
-    p->cfg = choose_config(M, N, std::max(p->kb_total, 1), sms, tuning);
+    // an 8-bit B read in place comes in 128-column chunks: no 64-wide tiles then
+    p->cfg = choose_config(M, N, std::max(p->kb_total, 1), sms, tuning,
+                           (b_direct && p->ti.elem_bytes == 1) ? 128 : 64);
     p->ld_relayout = round_up(K, 16 / p->ti.elem_bytes);
-    p->relayout_bytes = (b_layout == QGEMM_B_ROW_MAJOR) ? round_up(N * p->ld_relayout * p->ti.elem_bytes, 256) : 0;
+    p->relayout_bytes =
+        (b_layout == QGEMM_B_ROW_MAJOR && !b_direct) ? round_up(N * p->ld_relayout * p->ti.elem_bytes, 256) : 0;
     p->ldw = round_up(N, 4);
     p->partial_bytes = p->cfg.splits > 1 ? static_cast<size_t>(p->cfg.splits) * M * p->ldw * 4 : 0;
     return QGEMM_OK;
@@ -331,8 +335,14 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     int rc = get_state(&st);
     if (rc != QGEMM_OK) return rc;
 
+    // A row-major B whose rows TMA can address is fed to the tensor cores in place (MN-major operand).
+    TypeInfo ti0;
+    if (!type_info(in_dtype, &ti0)) return QGEMM_ERR_UNSUPPORTED;
+    const bool want_relayout = (tuning && tuning->relayout_b > 0) || env_int("QGEMM_RELAYOUT_B") > 0;
+    const bool b_direct = b_layout == QGEMM_B_ROW_MAJOR && !want_relayout && K > 0 &&
+                          reinterpret_cast<uintptr_t>(B) % 16 == 0 && (ldb * ti0.elem_bytes) % 16 == 0;
     Plan plan;
-    rc = make_plan(in_dtype, out_dtype, b_layout, M, N, K, st->sm_count, tuning, &plan);
+    rc = make_plan(in_dtype, out_dtype, b_layout, M, N, K, st->sm_count, tuning, &plan, b_direct);
     if (rc != QGEMM_OK) return rc;
     if (plan.out_kind == OUT_RAW32 && (scale_a != nullptr || scale_b != nullptr)) return QGEMM_ERR_INVALID_ARG;
     const int out_bytes = (plan.out_kind == OUT_BF16 || plan.out_kind == OUT_F16) ? 2 : 4;
@@ -352,7 +362,7 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
 
     const void* b_kmajor = B;
     size_t ldb_k = ldb;
-    if (b_layout == QGEMM_B_ROW_MAJOR) {
+    if (b_layout == QGEMM_B_ROW_MAJOR && !b_direct) {
         // B arrives N-major: relayout to K-major [N, K] in scratch (rows = K, cols = N on the way in).
         rc = transpose_launch(B, st->ws, K, N, ldb, plan.ld_relayout, es, stream);
         if (rc != QGEMM_OK) return rc;
@@ -364,7 +374,10 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     CUtensorMap ta, tb;
     rc = make_operand_map(A, M, K, lda, in_dtype, kBM, &ta);
     if (rc != QGEMM_OK) return rc;
-    rc = make_operand_map(b_kmajor, N, K, ldb_k, in_dtype, cfg.pair ? 128u : static_cast<uint32_t>(cfg.bn), &tb);
+    if (b_direct)  // [K rows, N columns]; one box = 128 bytes of N x one 128-byte K block of rows
+        rc = make_operand_map(B, K, N, ldb, in_dtype, 128u / static_cast<uint32_t>(es), &tb);
+    else
+        rc = make_operand_map(b_kmajor, N, K, ldb_k, in_dtype, cfg.pair ? 128u : static_cast<uint32_t>(cfg.bn), &tb);
     if (rc != QGEMM_OK) return rc;
 
     GemmParams p;
@@ -380,7 +393,8 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     p.kb_per_split = cfg.kb_per_split;
     p.group_m = cfg.group_m;
     p.idesc = ptx::make_idesc(plan.ti.cfmt, plan.ti.fmt, plan.ti.fmt, static_cast<uint32_t>(tile_m),
-                              static_cast<uint32_t>(cfg.bn));
+                              static_cast<uint32_t>(cfg.bn), b_direct ? 1u : 0u);
+    p.b_mn_major = b_direct ? 1 : 0;
     p.status = st->status;
 
     int launch_out = plan.out_kind;

@@ -49,6 +49,7 @@ struct GemmParams {
     int* status;   // device status words: [0] code, [1] cta, [2] role, [3] stage/tile
     int c_vec_ok;  // C base and ldc allow 16-byte vector stores
     int c_tma_ok;  // the C tensor map is valid: the epilogue stores through shared memory + TMA
+    int b_mn_major;  // B is read in place as [K,N] row-major (N contiguous): tmap_b is over [K rows, N cols]
 };
 
 constexpr int kBM = 128;
@@ -328,7 +329,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const uint32_t full = bar_full + stage * 8;
                     ptx::mbar_arrive_expect_tx(full, L::kAStage + L::kBStage);
                     ptx::tma_load_2d(smem_a + stage * L::kAStage, &tmap_a, full, kb * BK, t.m_blk * kBM);
-                    ptx::tma_load_2d(smem_b + stage * L::kBStage, &tmap_b, full, kb * BK, t.n_blk * BN);
+                    if (p.b_mn_major) {
+                        // one box per 128-byte chunk of N: [BK rows of K] x [CHUNK columns]
+                        constexpr int CHUNK = 128 / ELT;
+#pragma unroll
+                        for (int j = 0; j < BN / CHUNK; ++j)
+                            ptx::tma_load_2d(smem_b + stage * L::kBStage + j * (BK * 128), &tmap_b, full,
+                                             t.n_blk * BN + j * CHUNK, kb * BK);
+                    } else {
+                        ptx::tma_load_2d(smem_b + stage * L::kBStage, &tmap_b, full, kb * BK, t.n_blk * BN);
+                    }
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1u;
@@ -358,10 +368,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                     ptx::tc_fence_after();
                     const uint64_t a_desc = ptx::make_kmajor_sw128_desc(smem_a + stage * L::kAStage);
-                    const uint64_t b_desc = ptx::make_kmajor_sw128_desc(smem_b + stage * L::kBStage);
+                    const uint64_t b_desc =
+                        p.b_mn_major ? ptx::make_mnmajor_sw128_desc(smem_b + stage * L::kBStage, BK * 128)
+                                     : ptx::make_kmajor_sw128_desc(smem_b + stage * L::kBStage);
+                    // K step of one MMA in 16-byte units: 32 bytes inside a K-major row, or (32 / ELT) rows of
+                    // 128 bytes for an MN-major tile
+                    const uint32_t b_step = p.b_mn_major ? static_cast<uint32_t>((32 / ELT) * 128 / 16) : 2u;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per 128-byte block
-                        ptx::umma_ss<KIND>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc,
+                        ptx::umma_ss<KIND>(d_tmem, a_desc + 2u * k, b_desc + b_step * k, p.idesc,
                                            (kb > kb0 || k > 0) ? 1u : 0u);
                     }
                     ptx::tc_commit(bar_empty + stage * 8);

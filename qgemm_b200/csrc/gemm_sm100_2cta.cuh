@@ -117,7 +117,15 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     if (rank == 0) ptx::mbar_arrive_expect_tx(bar_full + stage * 8, 2 * (L::kAStage + L::kBStage));
                     const uint32_t leader_full = ptx::mapa_shared(bar_full + stage * 8, 0);
                     ptx::tma_load_2d_pair(smem_a + stage * L::kAStage, &tmap_a, leader_full, kb * BK, row_a);
-                    ptx::tma_load_2d_pair(smem_b + stage * L::kBStage, &tmap_b, leader_full, kb * BK, row_b);
+                    if (p.b_mn_major) {
+                        constexpr int CHUNK = 128 / ELT;  // this CTA's 128 columns of B: 128-byte chunks of N
+#pragma unroll
+                        for (int j = 0; j < 128 / CHUNK; ++j)
+                            ptx::tma_load_2d_pair(smem_b + stage * L::kBStage + j * (BK * 128), &tmap_b, leader_full,
+                                                  row_b + j * CHUNK, kb * BK);
+                    } else {
+                        ptx::tma_load_2d_pair(smem_b + stage * L::kBStage, &tmap_b, leader_full, kb * BK, row_b);
+                    }
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1u;
@@ -147,10 +155,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     }
                     ptx::tc_fence_after();
                     const uint64_t a_desc = ptx::make_kmajor_sw128_desc(smem_a + stage * L::kAStage);
-                    const uint64_t b_desc = ptx::make_kmajor_sw128_desc(smem_b + stage * L::kBStage);
+                    const uint64_t b_desc =
+                        p.b_mn_major ? ptx::make_mnmajor_sw128_desc(smem_b + stage * L::kBStage, BK * 128)
+                                     : ptx::make_kmajor_sw128_desc(smem_b + stage * L::kBStage);
+                    const uint32_t b_step = p.b_mn_major ? static_cast<uint32_t>((32 / ELT) * 128 / 16) : 2u;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        ptx::umma_ss_pair<KIND>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc,
+                        ptx::umma_ss_pair<KIND>(d_tmem, a_desc + 2u * k, b_desc + b_step * k, p.idesc,
                                                 (kb > kb0 || k > 0) ? 1u : 0u);
                     }
                     ptx::tc_commit_pair(bar_empty + stage * 8, 3);

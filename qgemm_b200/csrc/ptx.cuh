@@ -184,6 +184,22 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
     return d;
 }
 
+// Descriptor for an MN-major operand tile (the K x N operand B given row-major, N contiguous) as TMA
+// lays it down with a 128-byte inner box and the 128-byte swizzle: chunks of 128 bytes along N (64
+// two-byte or 128 one-byte elements) x BK rows of K. Inside a chunk consecutive K rows are 128 bytes
+// apart, groups of 8 rows 1024 bytes apart (stride-byte-offset); successive N chunks are
+// `chunk_bytes` apart (leading-byte-offset). Stepping along K by one MMA (32 bytes of K = 16 or 32
+// rows) adds rows * 128 bytes to the start address.
+__device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_addr, uint32_t chunk_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((chunk_bytes >> 4) & 0x3FFFu) << 16;  // leading byte offset: next N chunk
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;                     // stride byte offset: next 8 K rows
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
 // Instruction descriptor for kind::f16 / kind::i8 / kind::f8f6f4 with both operands K-major.
 //   bits [4,6)  accumulator format: 1 = fp32, 2 = int32
 //   bits [7,10) A format, [10,13) B format: f16 kinds 0 = fp16, 1 = bf16; i8 kind 1 = signed;
@@ -191,8 +207,8 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
 //   bit 15 / 16 A / B major-ness (0 = K-major)
 //   bits [17,23) N >> 3, bits [24,29) M >> 4
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t c_fmt, uint32_t a_fmt, uint32_t b_fmt, uint32_t m,
-                                                  uint32_t n) {
-    return (c_fmt << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+                                                  uint32_t n, uint32_t b_mn_major = 0) {
+    return (c_fmt << 4) | (a_fmt << 7) | (b_fmt << 10) | (b_mn_major << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
 // ---------------------------------------------------------------- tensor memory -> registers

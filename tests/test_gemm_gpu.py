@@ -74,17 +74,21 @@ def test_config1_fp16_1024_b_colmajor(qlib, oracle, dev):
     _status_ok(q)
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (200, 264, 136), (77, 130, 56), (512, 768, 320)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (200, 264, 136), (77, 130, 56), (512, 768, 320), (300, 1000, 264)])
 @pytest.mark.parametrize("out_name", ["fp32", "bf16", "fp16"])
-def test_bf16_row_major_b_goes_through_relayout(qlib, oracle, dev, M, N, K, out_name):
-    """B given as [K,N] row-major: the library relays it out to K-major with the transpose kernel."""
+@pytest.mark.parametrize("relayout", [0, 1])
+def test_bf16_row_major_b(qlib, oracle, dev, M, N, K, out_name, relayout):
+    """B given as [K,N] row-major: read in place as an MN-major tensor-core operand when its rows are 16-byte
+    aligned (relayout = 0), or relaid out to K-major by the transpose kernel first (relayout = 1, and always
+    for an unaligned B such as N = 130)."""
     q = qlib
+    tuning = q.Tuning(0, 0, 0, 0, 0, relayout)
     a_bits, a_val = oracle.round_bf16(datagen.normal((M, K), seed=7, stream=0))
     b_bits, b_val = oracle.round_bf16(datagen.normal((K, N), seed=7, stream=1))
     a, b = _to_dev16(a_bits, torch.bfloat16, dev), _to_dev16(b_bits, torch.bfloat16, dev)
     odt = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}[out_name]
     c = torch.zeros((M, N), dtype=odt, device=dev)
-    q.gemm(a, b, c, b_kmajor=False)
+    q.gemm(a, b, c, b_kmajor=False, tuning=tuning)
     ref = oracle.gemm_f32(a_val, b_val, False)
     got = c.float().cpu().numpy()
     tol = REL_L2_TOL if out_name == "fp32" else 4e-3  # one extra rounding to a 16-bit output
@@ -94,9 +98,47 @@ def test_bf16_row_major_b_goes_through_relayout(qlib, oracle, dev, M, N, K, out_
         # the rounding of the same kernel's fp32 output bit for bit (an ulp bound against the oracle's
         # differently ordered fp32 sum is meaningless where the sum cancels to near zero).
         c32 = torch.zeros((M, N), dtype=torch.float32, device=dev)
-        q.gemm(a, b, c32, b_kmajor=False)
+        q.gemm(a, b, c32, b_kmajor=False, tuning=tuning)
         kind = oracle.OUT_BF16 if out_name == "bf16" else oracle.OUT_F16
         assert np.array_equal(_bits16(c), oracle.scale_cast(c32.cpu().numpy(), 1.0, 1.0, kind))
+    _status_ok(q)
+
+
+@pytest.mark.parametrize("tile_n,pair", [(256, -1), (128, -1), (64, -1), (256, 1)])
+def test_row_major_b_in_place_every_tile_shape(qlib, oracle, dev, tile_n, pair):
+    """The in-place (MN-major) B path under every tile configuration, bf16, ragged N and K."""
+    q = qlib
+    M, N, K = 384, 1112, 456
+    a_bits, a_val = oracle.round_bf16(datagen.normal((M, K), seed=13, stream=0))
+    b_bits, b_val = oracle.round_bf16(datagen.normal((K, N), seed=13, stream=1))
+    a, b = _to_dev16(a_bits, torch.bfloat16, dev), _to_dev16(b_bits, torch.bfloat16, dev)
+    c = torch.zeros((M, N), dtype=torch.float32, device=dev)
+    q.gemm(a, b, c, b_kmajor=False, tuning=q.Tuning(tile_n, 1, 0, 0, pair, 0))
+    assert oracle.rel_l2(c.cpu().numpy(), oracle.gemm_f32(a_val, b_val, False)) <= REL_L2_TOL
+    _status_ok(q)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 528, 400), (1024, 1024, 2048)])
+@pytest.mark.parametrize("relayout", [0, 1])
+def test_int8_and_fp8_row_major_b(qlib, oracle, dev, M, N, K, relayout):
+    """8-bit operands with B [K,N] row-major: in place (128-column chunks) and through the relayout."""
+    q = qlib
+    tuning = q.Tuning(0, 0, 0, 0, 0, relayout)
+    ai = datagen.int8_uniform((M, K), seed=K + 3, stream=0)
+    bi = datagen.int8_uniform((K, N), seed=K + 3, stream=1)
+    acc = torch.zeros((M, N), dtype=torch.int32, device=dev)
+    q.gemm(torch.from_numpy(ai).to(dev), torch.from_numpy(bi).to(dev), acc, b_kmajor=False, tuning=tuning)
+    assert np.array_equal(acc.cpu().numpy(), oracle.gemm_i8(ai, bi, False))
+    a32 = datagen.normal((M, K), seed=K, stream=0)
+    b32 = datagen.normal((K, N), seed=K, stream=1)
+    a_bits, a_val, sa = oracle.quantize_e4m3(a32)
+    b_bits, b_val, sb = oracle.quantize_e4m3(b32)
+    a = torch.from_numpy(a_bits).to(dev).view(torch.float8_e4m3fn)
+    b = torch.from_numpy(b_bits).to(dev).view(torch.float8_e4m3fn)
+    c = torch.zeros((M, N), dtype=torch.bfloat16, device=dev)
+    q.mix_gemm(a, b, torch.tensor([sa], device=dev), torch.tensor([sb], device=dev), c, b_kmajor=False, tuning=tuning)
+    ref = oracle.gemm_f32(a_val, b_val, False) * (np.float32(sa) * np.float32(sb))
+    assert oracle.max_rel(c.float().cpu().numpy(), ref) <= FP8_MAX_REL_TOL
     _status_ok(q)
 
 
