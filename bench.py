@@ -56,6 +56,18 @@ WORKLOADS = {
 }
 
 
+_REAL_STDOUT = None
+
+
+def emit(line: dict) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    if _REAL_STDOUT is not None:
+        os.write(_REAL_STDOUT, data)
+    else:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -215,7 +227,7 @@ def run_reference_arm(args):
         "e2e": {"value": value, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ------------------------------------------------------------------------------------ GPU arm
@@ -257,6 +269,12 @@ def make_operands(workload, seed, rank, world, torch, dev):
 
 def main():
     args = parse_args()
+    # The contract is ONE JSON line on stdout: libraries that print there (NCCL's version banner does) are sent
+    # to stderr for the duration of the run, and the line is written to the real stdout at the end.
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference_arm(args)
         return
@@ -532,7 +550,7 @@ def main():
             line["direct_b"] = direct_b
         if gather is not None:
             line["all_gather"] = gather
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
