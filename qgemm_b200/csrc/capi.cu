@@ -395,6 +395,7 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     p.idesc = ptx::make_idesc(plan.ti.cfmt, plan.ti.fmt, plan.ti.fmt, static_cast<uint32_t>(tile_m),
                               static_cast<uint32_t>(cfg.bn), b_direct ? 1u : 0u);
     p.b_mn_major = b_direct ? 1 : 0;
+    p.test_skip_kb = std::getenv("QGEMM_TEST_SKIP_LOAD") ? env_int("QGEMM_TEST_SKIP_LOAD") : -1;
     p.status = st->status;
 
     int launch_out = plan.out_kind;

@@ -50,6 +50,8 @@ struct GemmParams {
     int c_vec_ok;  // C base and ldc allow 16-byte vector stores
     int c_tma_ok;  // the C tensor map is valid: the epilogue stores through shared memory + TMA
     int b_mn_major;  // B is read in place as [K,N] row-major (N contiguous): tmap_b is over [K rows, N cols]
+    int test_skip_kb;  // failure-detection test hook: the producer leaves out the loads of this K block (-1 = none),
+                       // so the consumer's bounded wait runs out and the kernel returns through its error path
 };
 
 constexpr int kBM = 128;
@@ -74,12 +76,15 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
     for (int i = 0; i < 128; ++i)
         if (ptx::mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
+    // An epilogue warp legitimately waits for a whole mainloop, and when a load or an MMA goes missing its wait
+    // starts before the wait that is really stuck: give it twice the limit so the report names the stuck role.
+    const long long limit = (role == ROLE_EPILOGUE) ? 2 * kWaitLimitCycles : kWaitLimitCycles;
     uint32_t it = 0;
 #pragma unroll 1
     while (!ptx::mbar_try_wait(bar, parity)) {
         if ((++it & 0xffu) == 0) {
             if (*abort_flag != 0) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > limit) {
                 *abort_flag = 1;
                 record_error(status, DEV_ERR_WAIT_TIMEOUT, role, where);
                 return false;
@@ -327,9 +332,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         break;
                     }
                     const uint32_t full = bar_full + stage * 8;
-                    ptx::mbar_arrive_expect_tx(full, L::kAStage + L::kBStage);
-                    ptx::tma_load_2d(smem_a + stage * L::kAStage, &tmap_a, full, kb * BK, t.m_blk * kBM);
-                    if (p.b_mn_major) {
+                    if (kb == p.test_skip_kb) {
+                        // test hook: this slot is never filled, so the MMA issuer's wait on it runs out
+                    } else if (p.b_mn_major) {
+                        ptx::mbar_arrive_expect_tx(full, L::kAStage + L::kBStage);
+                        ptx::tma_load_2d(smem_a + stage * L::kAStage, &tmap_a, full, kb * BK, t.m_blk * kBM);
                         // one box per 128-byte chunk of N: [BK rows of K] x [CHUNK columns]
                         constexpr int CHUNK = 128 / ELT;
 #pragma unroll
@@ -337,6 +344,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                             ptx::tma_load_2d(smem_b + stage * L::kBStage + j * (BK * 128), &tmap_b, full,
                                              t.n_blk * BN + j * CHUNK, kb * BK);
                     } else {
+                        ptx::mbar_arrive_expect_tx(full, L::kAStage + L::kBStage);
+                        ptx::tma_load_2d(smem_a + stage * L::kAStage, &tmap_a, full, kb * BK, t.m_blk * kBM);
                         ptx::tma_load_2d(smem_b + stage * L::kBStage, &tmap_b, full, kb * BK, t.n_blk * BN);
                     }
                     if (++stage == STAGES) {
