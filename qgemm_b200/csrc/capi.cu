@@ -177,6 +177,7 @@ int make_output_map(void* ptr, uint64_t M, uint64_t N, uint64_t ld, uint64_t spl
 struct Config {
     int bn, splits, kb_per_split, group_m;
     bool pair;  // two CTAs per 256x256 tile (bn is then 256 and tiles are counted in 256-row units)
+    int am;     // rows of A loaded per stage (128; 64 or 32 with the 64-wide tile when M is that small)
 };
 
 int env_int(const char* name) {
@@ -221,7 +222,7 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
     if (!want_group) want_group = env_int("QGEMM_GROUP_M");
     if (!want_pair) want_pair = env_int("QGEMM_CTA_PAIR");
 
-    Config best{256, 1, kb_total, 16, false};
+    Config best{256, 1, kb_total, 16, false, kBM};
     double best_t = 1e300;
     struct Cand { int bn; bool pair; };
     const Cand cands[] = {{256, true}, {256, false}, {128, false}, {64, false}};
@@ -251,6 +252,10 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
         best.splits = 1;
         best.kb_per_split = kb_total;
     }
+    // Small M with the narrow tile: load only the rows of A that exist, which leaves room for up to 16 stages so
+    // that a short K is wholly in flight at once.
+    best.am = kBM;
+    if (!best.pair && best.bn == 64 && env_int("QGEMM_FULL_A_TILE") == 0) best.am = M <= 32 ? 32 : (M <= 64 ? 64 : kBM);
     // Tile rows per scheduling group: as many as keep the group's A panel (rows x K bytes) near 32 MiB, so that
     // it stays in L2 while the B panels stream past it.
     const long long panel_rows = (32ll << 20) / (static_cast<long long>(kb_total) * 128);
@@ -372,7 +377,7 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
 
     const Config& cfg = plan.cfg;
     CUtensorMap ta, tb;
-    rc = make_operand_map(A, M, K, lda, in_dtype, kBM, &ta);
+    rc = make_operand_map(A, M, K, lda, in_dtype, static_cast<uint32_t>(cfg.am), &ta);
     if (rc != QGEMM_OK) return rc;
     if (b_direct)  // [K rows, N columns]; one box = 128 bytes of N x one 128-byte K block of rows
         rc = make_operand_map(B, K, N, ldb, in_dtype, 128u / static_cast<uint32_t>(es), &tb);
@@ -442,9 +447,9 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
         }
     } else {
         switch (plan.ti.kind) {
-            case ptx::KIND_F16: e = launch_gemm_f16(cfg.bn, launch_out, ta, tb, tc, p, grid, stream); break;
-            case ptx::KIND_I8: e = launch_gemm_i8(cfg.bn, launch_out, ta, tb, tc, p, grid, stream); break;
-            default: e = launch_gemm_f8(cfg.bn, launch_out, ta, tb, tc, p, grid, stream); break;
+            case ptx::KIND_F16: e = launch_gemm_f16(cfg.bn, launch_out, cfg.am, ta, tb, tc, p, grid, stream); break;
+            case ptx::KIND_I8: e = launch_gemm_i8(cfg.bn, launch_out, cfg.am, ta, tb, tc, p, grid, stream); break;
+            default: e = launch_gemm_f8(cfg.bn, launch_out, cfg.am, ta, tb, tc, p, grid, stream); break;
         }
     }
     if (e != cudaSuccess) return QGEMM_ERR_CUDA;

@@ -266,7 +266,7 @@ fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 }
             }
         }
-        if (lane == 0) ptx::tma_store_wait_all<0>();
+        if (lane == 0) ptx::tma_store_wait_read<0>();
     }
 
     // ---------------------------------------------------------------- teardown

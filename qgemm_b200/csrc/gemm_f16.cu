@@ -2,9 +2,9 @@
 #include "gemm_launch.cuh"
 
 namespace qgemm {
-cudaError_t launch_gemm_f16(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+cudaError_t launch_gemm_f16(int bn, int out, int am, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                            int grid, cudaStream_t stream) {
-    return launch_kind<ptx::KIND_F16>(bn, out, ta, tb, tc, p, grid, stream);
+    return launch_kind<ptx::KIND_F16>(bn, out, am, ta, tb, tc, p, grid, stream);
 }
 cudaError_t launch_gemm_pair_f16(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                                  int clusters, cudaStream_t stream) {

@@ -35,17 +35,19 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
 }
 
 // Stages per tile width: a stage holds a 128x128-byte A tile and a BNx128-byte B tile.
-template <int BN>
+template <int BN, int AM = kBM>
 struct StagesFor {
-    static constexpr int value = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
+    // as many as fit in 192 KB, capped at 16
+    static constexpr int kFit = (192 * 1024) / ((AM + BN) * 128);
+    static constexpr int value = kFit > 16 ? 16 : kFit;
 };
 
-template <int KIND, int BN, int OUT>
+template <int KIND, int BN, int OUT, int AM = kBM>
 cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
                        cudaStream_t stream) {
-    constexpr int STAGES = StagesFor<BN>::value;
-    auto kernel = gemm_tcgen05_kernel<KIND, BN, STAGES, OUT>;
-    constexpr int smem = GemmSmem<BN, STAGES>::kDynamicBytes;
+    constexpr int STAGES = StagesFor<BN, AM>::value;
+    auto kernel = gemm_tcgen05_kernel<KIND, BN, STAGES, OUT, AM>;
+    constexpr int smem = GemmSmem<BN, STAGES, AM>::kDynamicBytes;
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -59,23 +61,23 @@ cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     return launch_pdl(kernel, dim3(grid), dim3(kGemmThreads), smem, stream, ta, tb, tc, p);
 }
 
+// `am` = rows of A loaded per stage: 128, or 64 / 32 with the 64-wide tile for small M.
 template <int KIND>
-cudaError_t launch_kind(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
-                        cudaStream_t stream) {
-#define QGEMM_CASE(BN_, OUT_) \
-    if (bn == BN_ && out == OUT_) return launch_one<KIND, BN_, OUT_>(ta, tb, tc, p, grid, stream);
-    QGEMM_CASE(256, OUT_F32)
-    QGEMM_CASE(256, OUT_BF16)
-    QGEMM_CASE(256, OUT_F16)
-    QGEMM_CASE(256, OUT_RAW32)
-    QGEMM_CASE(128, OUT_F32)
-    QGEMM_CASE(128, OUT_BF16)
-    QGEMM_CASE(128, OUT_F16)
-    QGEMM_CASE(128, OUT_RAW32)
-    QGEMM_CASE(64, OUT_F32)
-    QGEMM_CASE(64, OUT_BF16)
-    QGEMM_CASE(64, OUT_F16)
-    QGEMM_CASE(64, OUT_RAW32)
+cudaError_t launch_kind(int bn, int out, int am, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                        const GemmParams& p, int grid, cudaStream_t stream) {
+#define QGEMM_CASE(BN_, OUT_, AM_) \
+    if (bn == BN_ && out == OUT_ && am == AM_) return launch_one<KIND, BN_, OUT_, AM_>(ta, tb, tc, p, grid, stream);
+#define QGEMM_CASES(BN_, AM_)        \
+    QGEMM_CASE(BN_, OUT_F32, AM_)   \
+    QGEMM_CASE(BN_, OUT_BF16, AM_)  \
+    QGEMM_CASE(BN_, OUT_F16, AM_)   \
+    QGEMM_CASE(BN_, OUT_RAW32, AM_)
+    QGEMM_CASES(256, 128)
+    QGEMM_CASES(128, 128)
+    QGEMM_CASES(64, 128)
+    QGEMM_CASES(64, 64)
+    QGEMM_CASES(64, 32)
+#undef QGEMM_CASES
 #undef QGEMM_CASE
     return cudaErrorInvalidValue;
 }
@@ -158,11 +160,11 @@ cudaError_t launch_fp8_blockscale(int out_kind, const CUtensorMap& ta, const CUt
                                   const BlockScaleParams& p, int grid, cudaStream_t stream);
 
 // Defined one per translation unit so the kinds compile in parallel.
-cudaError_t launch_gemm_f16(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+cudaError_t launch_gemm_f16(int bn, int out, int am, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                             int grid, cudaStream_t stream);
-cudaError_t launch_gemm_i8(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+cudaError_t launch_gemm_i8(int bn, int out, int am, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                            int grid, cudaStream_t stream);
-cudaError_t launch_gemm_f8(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+cudaError_t launch_gemm_f8(int bn, int out, int am, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                            int grid, cudaStream_t stream);
 
 }  // namespace qgemm

@@ -247,9 +247,11 @@ __device__ __forceinline__ void epilogue_tma(const CUtensorMap* tmap_c, uint32_t
     }
 }
 
-template <int BN, int STAGES>
+// AM = rows of A actually loaded per stage (128, or 64 / 32 when M is that small: the MMA still reads 128 rows,
+// the rest being whatever follows in shared memory, which only reaches accumulator rows that are never stored).
+template <int BN, int STAGES, int AM = kBM>
 struct GemmSmem {
-    static constexpr int kAStage = kBM * 128;
+    static constexpr int kAStage = AM * 128;
     static constexpr int kBStage = BN * 128;
     static constexpr int kTiles = STAGES * (kAStage + kBStage);
     static constexpr int kOutOffset = kTiles;                    // epilogue staging: 4 warps x 2 buffers x 4 KB
@@ -259,11 +261,12 @@ struct GemmSmem {
     static constexpr int kDynamicBytes = kTotal + 1024;          // slack for the 1024-byte alignment
 };
 
-template <int KIND, int BN, int STAGES, int OUT>
+template <int KIND, int BN, int STAGES, int OUT, int AM = kBM>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
-    using L = GemmSmem<BN, STAGES>;
+    using L = GemmSmem<BN, STAGES, AM>;
+    static_assert(STAGES * L::kAStage + (kBM - AM) * 128 <= L::kTiles, "the MMA's 128-row read of A stays inside the tile area");
     constexpr int ELT = (KIND == ptx::KIND_F16) ? 2 : 1;
     constexpr int BK = 128 / ELT;  // elements per 128-byte K block
     constexpr uint32_t TMEM_COLS = 2 * BN;
@@ -436,8 +439,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bar_tempty + acc * 8);
         }
-        // every TMA store of this warp must have completed before the CTA may exit
-        if (lane == 0) ptx::tma_store_wait_all<0>();
+        // the staging buffers must have been read by every TMA store before the CTA (and its shared memory) goes away;
+        // the global writes themselves complete with the grid
+        if (lane == 0) ptx::tma_store_wait_read<0>();
     }
 
     // ---------------------------------------------------------------- teardown

@@ -214,7 +214,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa_shared(bar_tempty + acc * 8, 0));
         }
-        if (lane == 0) ptx::tma_store_wait_all<0>();
+        if (lane == 0) ptx::tma_store_wait_read<0>();
     }
 
     // ---------------------------------------------------------------- teardown

@@ -202,9 +202,9 @@ extern "C" int qgemm_mix_gemm_splitk_static(int in_dtype, int out_dtype, const v
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     cudaError_t e;
     switch (kind) {
-        case ptx::KIND_F16: e = launch_gemm_f16(kTileN, OUT_RAW32, ta, tb, tc, p, grid, s); break;
-        case ptx::KIND_I8: e = launch_gemm_i8(kTileN, OUT_RAW32, ta, tb, tc, p, grid, s); break;
-        default: e = launch_gemm_f8(kTileN, OUT_RAW32, ta, tb, tc, p, grid, s); break;
+        case ptx::KIND_F16: e = launch_gemm_f16(kTileN, OUT_RAW32, kBM, ta, tb, tc, p, grid, s); break;
+        case ptx::KIND_I8: e = launch_gemm_i8(kTileN, OUT_RAW32, kBM, ta, tb, tc, p, grid, s); break;
+        default: e = launch_gemm_f8(kTileN, OUT_RAW32, kBM, ta, tb, tc, p, grid, s); break;
     }
     if (e != cudaSuccess) return QGEMM_ERR_CUDA;
     return splitk_reduce_launch(st->scratch, p.split_stride, p.ldc, splits, acc_int, C, static_cast<long long>(ldc),
