@@ -51,6 +51,9 @@ WORKLOADS = {
     "c4_fp8_256": ("fp8", "bf16", 256, 7168, 2048, True, "FP8 e4m3 M=256 N=7168 K=2048"),
     "c4_fp8_1024": ("fp8", "bf16", 1024, 7168, 2048, True, "FP8 e4m3 M=1024 N=7168 K=2048"),
     "c4_fp8_6144": ("fp8", "bf16", 6144, 7168, 2048, True, "FP8 e4m3 M=6144 N=7168 K=2048"),
+    "f1_fp8_blockscale": ("fp8", "bf16", 4096, 7168, 7168, True,
+                          "FP8 e4m3 GEMM with block scales (per row x 128-K block of A, per 128x128 block of B), "
+                          "M=4096 N=K=7168, bf16 out: the reference's fp8_mm semantics"),
     "c5_int8_sharded": ("int8", "bf16", 32768, 32768, 8192, True,
                         "int8 mixed GEMM 32768x32768x8192, B/C column-sharded over the ranks (strong scaling)"),
 }
@@ -256,6 +259,10 @@ def make_operands(workload, seed, rank, world, torch, dev):
         a_h = (a32 / s0).to(torch.float8_e4m3fn)
         b_h = (b32 / s1).to(torch.float8_e4m3fn)
         sa, sb = s0.reshape(1).to(dev), s1.reshape(1).to(dev)
+        if workload == "f1_fp8_blockscale":  # one scale per (row, 128-K block) of A and per 128x128 block of B
+            kbs, nbs = -(-K // 128), -(-N // 128)
+            sa = (torch.rand((kbs, M)) * 0.5 + 0.75).mul_(float(s0)).to(dev)
+            sb = (torch.rand((kbs, nbs)) * 0.5 + 0.75).mul_(float(s1)).to(dev)
     else:
         gen = datagen.uniform if workload == "c1_fp16_1024" else datagen.normal
         a_h = torch.from_numpy(gen((M, K), seed, 0)).to(tdt)
@@ -302,6 +309,13 @@ def main():
     # library's own default for an aligned row-major B (reading it in place) is timed separately below.
     tuning = q.Tuning(args.tile_n, args.split_k, args.group_m, 0, 0, 0 if ops["b_kmajor"] else 1)
     mixed = ops["sa"] is not None
+    blockscale = args.workload == "f1_fp8_blockscale"
+
+    def gemm_call(a_, b_, c_, b_kmajor, tun):
+        if blockscale:
+            q.fp8_block_mm(a_, b_, ops["sa"], ops["sb"], c_, reference_layout=False)
+        else:
+            q._gemm(a_, b_, ops["sa"], ops["sb"], c_, b_kmajor, tun, mixed)
 
     # Operands smaller than L2 would be served from L2 on every repeat: rotate through enough copies of
     # (A, B, C) that consecutive steps never find their inputs cached.
@@ -316,7 +330,7 @@ def main():
     def call_device():
         a_, b_, c_ = sets[step_counter[0] % nsets]
         step_counter[0] += 1
-        q._gemm(a_, b_, ops["sa"], ops["sb"], c_, ops["b_kmajor"], tuning, mixed)
+        gemm_call(a_, b_, c_, ops["b_kmajor"], tuning)
 
     # scratch is reserved before any timed region
     q.workspace_reserve(q.workspace_query({"bf16": q.BF16, "fp16": q.FP16, "int8": q.INT8, "fp8": q.FP8_E4M3}[in_name],
@@ -404,7 +418,7 @@ def main():
     def call_kernel():
         a_, b_, c_ = ksets[kcount[0] % nsets]
         kcount[0] += 1
-        q._gemm(a_, b_, ops["sa"], ops["sb"], c_, True, tuning, mixed)
+        gemm_call(a_, b_, c_, True, tuning)
 
     for _ in range(3):
         call_kernel()
@@ -451,7 +465,9 @@ def main():
         gbs = alg_bytes / (gemm_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
                     "peak_source": hbm_src + " copy bandwidth"}
-    roofline.update({"kernel": "gemm_tcgen05_pair_kernel" if M > 256 and not (args.tile_n or args.split_k) else "gemm_tcgen05_kernel",
+    roofline.update({"kernel": "fp8_blockscale_kernel" if blockscale else (
+                         "gemm_tcgen05_pair_kernel" if M > 256 and not (args.tile_n or args.split_k)
+                         else "gemm_tcgen05_kernel"),
                      "kernel_ms": gemm_ms, "algorithmic_flop": flop_per_step_rank,
                      "algorithmic_bytes": alg_bytes, "traffic": NCU_TRAFFIC_BYTES.get(args.workload)})
 
@@ -476,7 +492,7 @@ def main():
 
     # ---------------- e2e: host buffers through the host-level call, copies inside the timed region
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and not blockscale:
         from qgemm_b200.host_api import HostGemm
         hg = HostGemm(M, N, K, ops["in_dtype"], ops["out_dtype"], ops["b_kmajor"], dev)
         e2e_steps = max(3, min(args.steps, 20))

@@ -183,11 +183,16 @@ fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             float acc[CPW];
 #pragma unroll
             for (int j = 0; j < CPW; ++j) acc[j] = 0.0f;
+            // scales are fetched one K block ahead so that their latency never sits between a partial and its FMAs
+            float sa_next = row_ok ? __ldg(p.a_scale + row) : 0.0f;
+            float sb_next = __ldg(p.b_scale + n_blk);
             for (int kb = 0; kb < p.kb_total; ++kb, ++blk) {
                 const uint32_t buf = blk & PMASK;
-                // scales of this block: issued before the wait so the loads overlap it
-                const float sa = row_ok ? __ldg(p.a_scale + static_cast<long long>(kb) * p.M + row) : 0.0f;
-                const float sb = __ldg(p.b_scale + static_cast<long long>(kb) * p.n_scale_blocks + n_blk);
+                const float sa = sa_next, sb = sb_next;
+                if (kb + 1 < p.kb_total) {
+                    sa_next = row_ok ? __ldg(p.a_scale + static_cast<long long>(kb + 1) * p.M + row) : 0.0f;
+                    sb_next = __ldg(p.b_scale + static_cast<long long>(kb + 1) * p.n_scale_blocks + n_blk);
+                }
                 if (!wait_bounded(bar_pfull + buf * 8, (blk >> PSHIFT) & 1u, abort_flag, p.status, ROLE_EPILOGUE, kb)) {
                     ok = false;
                     break;
