@@ -377,6 +377,30 @@ def test_linearity_at_full_size_int8(qlib, oracle, dev):
     _status_ok(q)
 
 
+def test_output_larger_than_4_gib_uses_64_bit_addressing(qlib, oracle, dev):
+    """M x N x sizeof(C) beyond 2^32 bytes: row offsets must be computed in 64 bits on every store path."""
+    q = qlib
+    M, N, K = 70000, 32768, 64
+    ai = datagen.int8_uniform((M, K), seed=77, stream=0)
+    bi = datagen.int8_uniform((N, K), seed=77, stream=1)
+    a, b = torch.from_numpy(ai).to(dev), torch.from_numpy(bi).to(dev)
+    one = torch.ones(1, device=dev)
+    c = torch.empty((M, N), dtype=torch.bfloat16, device=dev)  # 4.6 GB
+    assert c.numel() * 2 > 2 ** 32
+    for tuning in (None, q.Tuning(128, 1, 0, 0, -1, 0)):  # CTA pairs, and the lone-CTA kernel
+        c.fill_(-7.0)
+        q.mix_gemm(a, b, one, one, c, b_kmajor=True, tuning=tuning)
+        for m0 in (0, 32767, 65530, M - 5):
+            got = c[m0:m0 + 5].float().cpu().numpy()
+            ref = oracle.gemm_i8_rows(ai, bi, m0, m0 + 5).astype(np.float32)
+            ref_bits = oracle.round_bf16(ref)[0]
+            assert np.array_equal(c[m0:m0 + 5].view(torch.int16).cpu().numpy().view(np.uint16), ref_bits), m0
+            assert np.isfinite(got).all()
+    del c
+    torch.cuda.empty_cache()
+    _status_ok(q)
+
+
 def test_config2_bf16_8192_row_major_b_sampled(qlib, oracle, dev):
     """BF16 8192^3, A and B row-major, bf16 out: sampled row bands against the oracle (rel-L2)."""
     q = qlib
