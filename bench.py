@@ -201,6 +201,38 @@ class CpuArm:
         return min(rows, self.a.shape[0])
 
 
+def reference_gpu_kernel(M, N, K):
+    """Side figure for the reference arm (not the baseline of record, which is the CPU port): the reference's OWN
+    GPU kernel, GEMM_kernel_v3<bf16,float> (its fastest published one), compiled unmodified from its sources
+    to compute_89 PTX (oracle/build_ref.sh; the reference has no sm_100 code path) and JIT-run on this GPU on the
+    same problem, timed the way its harness does (5 warm-ups, 10 back-to-back launches, CUDA events)."""
+    try:
+        import torch
+        from oracle import ref_gpu
+        if not (torch.cuda.is_available() and ref_gpu.available()):
+            return None
+        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        torch.cuda.set_device(dev)
+        a = torch.randn((M, K), device=dev).to(torch.bfloat16)
+        b = torch.randn((K, N), device=dev).to(torch.bfloat16)
+        c = torch.empty((M, N), dtype=torch.float32, device=dev)
+        for _ in range(5):
+            ref_gpu.gemm("v3", a, b, c)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        fn = ref_gpu.launcher("v3")
+        torch.cuda.synchronize()
+        e0.record(torch.cuda.default_stream())
+        for _ in range(10):
+            fn(a.data_ptr(), K, b.data_ptr(), N, c.data_ptr(), N, M, N, K)
+        e1.record(torch.cuda.default_stream())
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / 10
+        return {"kernel": "GEMM_kernel_v3<__nv_bfloat16,float> (reference sm89 source, compute_89 PTX JIT)",
+                "ms": ms, "tflops": 2.0 * M * N * K / (ms * 1e-3) / 1e12, "output": "fp32"}
+    except Exception as exc:  # the side figure must never break the arm
+        return {"unavailable": repr(exc)[:200]}
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -217,6 +249,9 @@ def run_reference_arm(args):
         t_total += dt
         flops += fl
     value = flops / t_total / 1e12
+    ref_gpu_line = None
+    if args.workload == "c2_bf16_8192":
+        ref_gpu_line = reference_gpu_kernel(M, N, K)
     sample = (f"rows 0..{rows} x {arm.N} columns x K={K} of the workload per step, blocked OpenMP "
               f"{'int32' if in_name == 'int8' else 'fp32'} GEMM")
     line = {
@@ -230,6 +265,8 @@ def run_reference_arm(args):
         "e2e": {"value": value, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    if ref_gpu_line is not None:
+        line["reference_gpu_kernel"] = ref_gpu_line
     emit(line)
 
 

@@ -47,6 +47,16 @@ def check_shape(M: int, N: int, K: int) -> None:
         raise ValueError("reference kernels need M % 512 == 0, N % 128 == 0, K % 64 == 0")
 
 
+def launcher(version: str):
+    """The raw entry point GEMM_kernel_<version><bf16,float>(A, ldA, B, ldB, C, ldC, M, N, K) (legacy default
+    stream, asynchronous), for timing loops. Shapes must satisfy check_shape."""
+    fn = getattr(lib(), _GEMM_SYMBOLS[version])
+    fn.restype = None
+    fn.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
+                   C.c_size_t]
+    return fn
+
+
 def gemm(version: str, a, b, c) -> None:
     """Run the reference's GEMM_kernel_<version><bf16,float> on torch CUDA tensors (default stream).
     a [M,K] bf16; b [K,N] bf16 (or [N,K] for v3_1); c [M,N] fp32, all contiguous."""
