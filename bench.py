@@ -577,6 +577,35 @@ def main():
         gms = max_over_ranks(g0.elapsed_time(g1)) / 5
         gather = {"ms": gms, "bytes_received_per_rank": ops["c"].numel() * ops["c"].element_size() * (world - 1)}
 
+    # ---------------- c5: the same gathered result with no separate collective: every rank's GEMM epilogue
+    # stores its tiles into all ranks' full matrices over NVLink (one launch per rank per step)
+    fused = None
+    if args.gather and world > 1 and args.workload == "c5_int8_sharded":
+        from qgemm_b200 import sharding
+        out = sharding.GatheredOutput(M, N * world, ops["c"].dtype, dev)
+        barrier()
+        for _ in range(2):
+            sharding.sharded_mix_gemm_gather(ops["a"], ops["b"], ops["sa"], ops["sb"], out)
+        torch.cuda.synchronize()
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for _ in range(5):
+            sharding.sharded_mix_gemm_gather(ops["a"], ops["b"], ops["sa"], ops["sb"], out)
+        f1.record()
+        torch.cuda.synchronize()
+        barrier()
+        fms = max_over_ranks(f0.elapsed_time(f1)) / 5
+        # what the separate all-gather assembles must be what the epilogues left behind
+        gemm_call(ops["a"], ops["b"], ops["c"], True, None)
+        full = sharding.slabs_to_matrix(sharding.all_gather_slabs(ops["c"]))
+        same = bool(torch.equal(full.view(torch.int16), out.local.view(torch.int16)))
+        del full
+        out.close()
+        fused = {"ms": fms, "equals_all_gather": same, "launches_per_rank_per_step": 1,
+                 "bytes_stored_to_peers_per_rank": ops["c"].numel() * ops["c"].element_size() * (world - 1),
+                 "whole_job_tops": 2.0 * M * (N * world) * K / (fms * 1e-3) / 1e12}
+
     sampler.stop()
     rc, st = q.device_status()
 
@@ -611,6 +640,8 @@ def main():
             line["direct_b"] = direct_b
         if gather is not None:
             line["all_gather"] = gather
+        if fused is not None:
+            line["gemm_with_fused_gather"] = fused
         emit(line)
     if world > 1:
         dist.destroy_process_group()

@@ -178,6 +178,39 @@ int qgemm_mix_gemm_splitk_static(int in_dtype, int out_dtype, const void* A, siz
                                  const float* scale_a, const float* scale_b, void* C, size_t ldc, size_t M, size_t N,
                                  size_t K, int split_k, qgemm_stream_t stream);
 
+/*
+ * GEMM whose result is stored to several buffers by the same kernel: C_dsts[0..n_dsts-1] each receive the
+ * identical M x N block (same ldc, same out_dtype). No counterpart in the reference, which is single-GPU; it
+ * serves the column-sharded configuration: rank r passes, for every GPU of the box, the address of columns
+ * [n0, n1) of that GPU's full [M, N_total] matrix (its own first, the others mapped with qgemm_peer_open), and
+ * when all ranks' calls have completed every GPU holds the whole C -- the all-gather happens as tile stores
+ * over NVLink from the GEMM's epilogue while later tiles are still being multiplied. Only stores cross to other
+ * GPUs; nothing is loaded from them. Arguments as qgemm_mix_gemm (scales may be NULL; INT8 -> INT32 with both
+ * NULL); 1 <= n_dsts <= QGEMM_MAX_DSTS; every destination 16-byte aligned and ldc * sizeof(out) a multiple of
+ * 16 (QGEMM_ERR_ALIGNMENT otherwise). The call only enqueues work on `stream`; a destination on another GPU is
+ * complete once this call's stream work has finished, and the ranks still need their own barrier before they
+ * read what the others wrote.
+ */
+#define QGEMM_MAX_DSTS 8
+int qgemm_gemm_multi_dst(int in_dtype, int out_dtype, int b_layout, const void* A, size_t lda, const void* B,
+                         size_t ldb, const float* scale_a, const float* scale_b, void* const* C_dsts, int n_dsts,
+                         size_t ldc, size_t M, size_t N, size_t K, qgemm_stream_t stream);
+
+/*
+ * Inter-process sharing of a device buffer between the ranks of one box (CUDA IPC memory handles), so that
+ * qgemm_gemm_multi_dst can be given the other ranks' matrices. No counterpart in the reference.
+ *   qgemm_peer_export  fills handle_out[QGEMM_PEER_HANDLE_BYTES] for the device allocation that contains ptr
+ *                      and *offset_out with ptr's byte offset inside it; the allocation must come from
+ *                      cudaMalloc (not from a virtual-memory pool). Send both to the other processes by any means.
+ *   qgemm_peer_open    maps an exported allocation into this process (a different process from the exporter)
+ *                      and enables peer access; *base_out + offset is the buffer.
+ *   qgemm_peer_close   unmaps it; call before the exporting process frees the allocation.
+ */
+#define QGEMM_PEER_HANDLE_BYTES 64
+int qgemm_peer_export(const void* ptr, void* handle_out, size_t* offset_out);
+int qgemm_peer_open(const void* handle, void** base_out);
+int qgemm_peer_close(void* base);
+
 /* Frees the scratch and cached descriptors of every device (blas::blas_destroy() calls this). */
 int qgemm_shutdown(void);
 

@@ -27,7 +27,8 @@ C_ABI_SYMBOLS = (
     "qgemm_gemm", "qgemm_mix_gemm", "qgemm_gemm_ex", "qgemm_transpose", "qgemm_workspace_reserve",
     "qgemm_workspace_bytes", "qgemm_workspace_query", "qgemm_device_status", "qgemm_shutdown",
     "qgemm_status_string", "qgemm_version", "qgemm_mix_gemm_splitk_static",
-    "qgemm_fp8_block_scaled_gemm", "qgemm_quantize",
+    "qgemm_fp8_block_scaled_gemm", "qgemm_quantize", "qgemm_gemm_multi_dst", "qgemm_peer_export",
+    "qgemm_peer_open", "qgemm_peer_close",
 )
 
 
@@ -72,6 +73,14 @@ def lib() -> C.CDLL:
         L.qgemm_fp8_block_scaled_gemm.restype = i
         L.qgemm_quantize.argtypes = [i, i, vp, sz, vp, sz, fp, fp, sz, sz, vp]
         L.qgemm_quantize.restype = i
+        L.qgemm_gemm_multi_dst.argtypes = [i, i, i, vp, sz, vp, sz, fp, fp, C.POINTER(C.c_void_p), i, sz, sz, sz, sz, vp]
+        L.qgemm_gemm_multi_dst.restype = i
+        L.qgemm_peer_export.argtypes = [vp, vp, C.POINTER(sz)]
+        L.qgemm_peer_export.restype = i
+        L.qgemm_peer_open.argtypes = [vp, C.POINTER(C.c_void_p)]
+        L.qgemm_peer_open.restype = i
+        L.qgemm_peer_close.argtypes = [vp]
+        L.qgemm_peer_close.restype = i
         for name in ("qgemm_gemm", "qgemm_mix_gemm", "qgemm_gemm_ex", "qgemm_transpose", "qgemm_workspace_reserve",
                      "qgemm_device_status", "qgemm_shutdown", "qgemm_version"):
             getattr(L, name).restype = i
@@ -229,6 +238,64 @@ def fp8_block_mm(a, b, a_scale, b_scale, c, reference_layout: bool = True) -> No
             max(b.stride(0), b.shape[1]), a_scale.data_ptr(), b_scale.data_ptr(), c.data_ptr(), max(c.stride(0), N),
             M, N, K, _stream_ptr(a))
     _check(rc, "qgemm_fp8_block_scaled_gemm")
+
+
+MAX_DSTS = 8  # QGEMM_MAX_DSTS
+PEER_HANDLE_BYTES = 64  # QGEMM_PEER_HANDLE_BYTES
+
+
+def gemm_multi_dst(a, b, scale_a, scale_b, dst_ptrs, ldc: int, out_dtype, n_cols: int, b_kmajor: bool = True) -> None:
+    """One GEMM whose [M, n_cols] result is stored to every address of ``dst_ptrs`` (device addresses, this
+    GPU's or mapped from other GPUs with :func:`peer_open`), all with leading dimension ``ldc`` elements of
+    ``out_dtype``. The column-sharded configuration uses it to leave the gathered C on every GPU from the
+    GEMM's own epilogue. Enqueues on the current stream of ``a``'s device; the caller synchronises and lets
+    the ranks meet before anybody reads."""
+    torch = _torch()
+    _require_cuda_2d("a", a)
+    _require_cuda_2d("b", b)
+    M, K = a.shape
+    N, Kb = (b.shape[0], b.shape[1]) if b_kmajor else (b.shape[1], b.shape[0])
+    if Kb != K or N != n_cols or a.dtype != b.dtype:
+        raise QgemmError(ERR_INVALID_ARG, "shape or dtype mismatch")
+    if not (1 <= len(dst_ptrs) <= MAX_DSTS):
+        raise QgemmError(ERR_INVALID_ARG, f"between 1 and {MAX_DSTS} destinations")
+    codes = {torch.bfloat16: BF16, torch.float16: FP16, torch.float32: FP32, torch.int32: INT32}
+    if out_dtype not in codes:
+        raise QgemmError(ERR_UNSUPPORTED, f"output dtype {out_dtype}")
+    arr = (C.c_void_p * len(dst_ptrs))(*[int(p) for p in dst_ptrs])
+    sa = scale_a.data_ptr() if scale_a is not None else None
+    sb = scale_b.data_ptr() if scale_b is not None else None
+    with torch.cuda.device(a.device):
+        rc = lib().qgemm_gemm_multi_dst(
+            _dtype_code(a), codes[out_dtype], B_K_MAJOR if b_kmajor else B_ROW_MAJOR, a.data_ptr(),
+            max(a.stride(0), K), b.data_ptr(), max(b.stride(0), b.shape[1]), sa, sb, arr, len(dst_ptrs), int(ldc),
+            M, N, K, _stream_ptr(a))
+    _check(rc, "qgemm_gemm_multi_dst")
+
+
+def peer_export(t):
+    """(handle bytes, byte offset) of a CUDA tensor's storage for another process of this box to map."""
+    torch = _torch()
+    handle = C.create_string_buffer(PEER_HANDLE_BYTES)
+    offset = C.c_size_t(0)
+    with torch.cuda.device(t.device):
+        _check(lib().qgemm_peer_export(t.data_ptr(), handle, C.byref(offset)), "qgemm_peer_export")
+    return handle.raw, int(offset.value)
+
+
+def peer_open(handle: bytes, device) -> int:
+    """Maps an exported allocation into this process on ``device``; returns its base address."""
+    torch = _torch()
+    base = C.c_void_p(0)
+    buf = C.create_string_buffer(bytes(handle), PEER_HANDLE_BYTES)
+    with torch.cuda.device(device):
+        _check(lib().qgemm_peer_open(buf, C.byref(base)), "qgemm_peer_open")
+    return int(base.value)
+
+
+def peer_close(base: int, device) -> None:
+    with _torch().cuda.device(device):
+        _check(lib().qgemm_peer_close(C.c_void_p(base)), "qgemm_peer_close")
 
 
 STATIC_SCRATCH_BYTES = 32 << 20  # QGEMM_STATIC_SCRATCH_BYTES

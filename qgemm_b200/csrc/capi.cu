@@ -329,9 +329,24 @@ int make_plan(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, siz
 
 int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size_t lda, const void* B, size_t ldb,
                   const float* scale_a, const float* scale_b, void* C, size_t ldc, size_t M, size_t N, size_t K,
-                  const qgemm_tuning_t* tuning, cudaStream_t stream) {
+                  const qgemm_tuning_t* tuning, cudaStream_t stream, void* const* extra_dsts = nullptr,
+                  int n_extra = 0) {
+    if (n_extra < 0 || n_extra > kMaxExtraDst || (n_extra > 0 && extra_dsts == nullptr)) return QGEMM_ERR_INVALID_ARG;
     if (M == 0 || N == 0) return QGEMM_OK;
     if (C == nullptr || ldc < N) return QGEMM_ERR_INVALID_ARG;
+    for (int d = 0; d < n_extra; ++d)
+        if (extra_dsts[d] == nullptr) return QGEMM_ERR_INVALID_ARG;
+    // Several destinations: the CTA-pair kernel's shared-memory + TMA-store epilogue is the one that fans a
+    // tile out, one K pass per tile.
+    qgemm_tuning_t multi_tuning;
+    if (n_extra > 0) {
+        std::memset(&multi_tuning, 0, sizeof(multi_tuning));
+        if (tuning) multi_tuning = *tuning;
+        multi_tuning.tile_n = 0;
+        multi_tuning.split_k = 1;
+        multi_tuning.cta_pair = 1;
+        tuning = &multi_tuning;
+    }
     if (K > 0 && (A == nullptr || B == nullptr || lda < K)) return QGEMM_ERR_INVALID_ARG;
     if (K > 0 && ldb < (b_layout == QGEMM_B_K_MAJOR ? K : N)) return QGEMM_ERR_INVALID_ARG;
 
@@ -353,8 +368,17 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     const int out_bytes = (plan.out_kind == OUT_BF16 || plan.out_kind == OUT_F16) ? 2 : 4;
 
     if (K == 0) {  // empty sum: C = 0
+        for (int d = 0; d < n_extra; ++d)
+            if (cudaMemset2DAsync(extra_dsts[d], ldc * out_bytes, 0, N * out_bytes, M, stream) != cudaSuccess)
+                return QGEMM_ERR_CUDA;
         return cudaMemset2DAsync(C, ldc * out_bytes, 0, N * out_bytes, M, stream) == cudaSuccess ? QGEMM_OK
                                                                                                   : QGEMM_ERR_CUDA;
+    }
+    if (n_extra > 0) {
+        if (!plan.cfg.pair || plan.cfg.splits != 1) return QGEMM_ERR_UNSUPPORTED;
+        if ((ldc * out_bytes) % 16 != 0 || reinterpret_cast<uintptr_t>(C) % 16 != 0) return QGEMM_ERR_ALIGNMENT;
+        for (int d = 0; d < n_extra; ++d)
+            if (reinterpret_cast<uintptr_t>(extra_dsts[d]) % 16 != 0) return QGEMM_ERR_ALIGNMENT;
     }
 
     const int es = plan.ti.elem_bytes;
@@ -423,11 +447,22 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     // The epilogue goes through shared memory + TMA stores when the destination qualifies for a tensor map.
     CUtensorMap tc;
     std::memset(&tc, 0, sizeof(tc));
-    if (p.c_vec_ok && env_int("QGEMM_DIRECT_STORE") == 0) {
+    if (p.c_vec_ok && (n_extra > 0 || env_int("QGEMM_DIRECT_STORE") == 0)) {
         const int map_rc = make_output_map(p.C, M, N, static_cast<uint64_t>(p.ldc), static_cast<uint64_t>(cfg.splits),
                                            launch_out, &tc);
         p.c_tma_ok = (map_rc == QGEMM_OK) ? 1 : 0;
     }
+    ExtraDst extra;
+    if (n_extra > 0) {
+        if (!p.c_tma_ok) return QGEMM_ERR_CUDA;
+        std::memset(&extra, 0, sizeof(extra));
+        for (int d = 0; d < n_extra; ++d) {
+            rc = make_output_map(extra_dsts[d], M, N, static_cast<uint64_t>(ldc), 1, launch_out, &extra.map[d]);
+            if (rc != QGEMM_OK) return rc;
+        }
+        p.n_extra_dst = n_extra;
+    }
+    const ExtraDst* extra_arg = n_extra > 0 ? &extra : nullptr;
 
     const long long work = static_cast<long long>(p.m_tiles) * p.n_tiles * p.splits;
     if (work > 0x7fffffffLL) return QGEMM_ERR_UNSUPPORTED;
@@ -441,9 +476,9 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
         int clusters = static_cast<int>(std::min<long long>(work, st->sm_count / 2));
         if (cap > 0) clusters = std::min(clusters, std::max(1, cap / 2));
         switch (plan.ti.kind) {
-            case ptx::KIND_F16: e = launch_gemm_pair_f16(launch_out, ta, tb, tc, p, clusters, stream); break;
-            case ptx::KIND_I8: e = launch_gemm_pair_i8(launch_out, ta, tb, tc, p, clusters, stream); break;
-            default: e = launch_gemm_pair_f8(launch_out, ta, tb, tc, p, clusters, stream); break;
+            case ptx::KIND_F16: e = launch_gemm_pair_f16(launch_out, ta, tb, tc, extra_arg, p, clusters, stream); break;
+            case ptx::KIND_I8: e = launch_gemm_pair_i8(launch_out, ta, tb, tc, extra_arg, p, clusters, stream); break;
+            default: e = launch_gemm_pair_f8(launch_out, ta, tb, tc, extra_arg, p, clusters, stream); break;
         }
     } else {
         switch (plan.ti.kind) {
@@ -578,6 +613,18 @@ int qgemm_mix_gemm(int in_dtype, int out_dtype, int b_layout, const void* A, siz
         return QGEMM_ERR_UNSUPPORTED;
     return gemm_dispatch(in_dtype, out_dtype, b_layout, A, lda, B, ldb, scale_a, scale_b, C, ldc, M, N, K, nullptr,
                          reinterpret_cast<cudaStream_t>(stream));
+}
+
+int qgemm_gemm_multi_dst(int in_dtype, int out_dtype, int b_layout, const void* A, size_t lda, const void* B,
+                         size_t ldb, const float* scale_a, const float* scale_b, void* const* C_dsts, int n_dsts,
+                         size_t ldc, size_t M, size_t N, size_t K, qgemm_stream_t stream) {
+    if (C_dsts == nullptr || n_dsts < 1 || n_dsts > QGEMM_MAX_DSTS) return QGEMM_ERR_INVALID_ARG;
+    static_assert(QGEMM_MAX_DSTS == kMaxExtraDst + 1, "destination limit");
+    if (n_dsts == 1)
+        return gemm_dispatch(in_dtype, out_dtype, b_layout, A, lda, B, ldb, scale_a, scale_b, C_dsts[0], ldc, M, N, K,
+                             nullptr, static_cast<cudaStream_t>(stream));
+    return gemm_dispatch(in_dtype, out_dtype, b_layout, A, lda, B, ldb, scale_a, scale_b, C_dsts[0], ldc, M, N, K,
+                         nullptr, static_cast<cudaStream_t>(stream), C_dsts + 1, n_dsts - 1);
 }
 
 int qgemm_fp8_block_scaled_gemm(int out_dtype, int a_layout, int b_layout, const void* A, size_t lda, const void* B,

@@ -82,12 +82,14 @@ cudaError_t launch_kind(int bn, int out, int am, const CUtensorMap& ta, const CU
     return cudaErrorInvalidValue;
 }
 
-// CTA-pair kernel (256 x 256 tiles, clusters of two). `max_clusters_out`, when non-null, receives how many
-// clusters the device can keep resident at once (queried once per device).
-template <int KIND, int OUT>
-cudaError_t launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int clusters,
+// CTA-pair kernel (256 x 256 tiles, clusters of two); the number of clusters is clamped to what the device can
+// keep resident at once (queried once per device). `extra` non-null selects the variant whose epilogue also
+// stores every tile to p.n_extra_dst further destinations.
+template <int KIND, int OUT, bool GATHER>
+cudaError_t launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                            const typename ExtraDstParam<GATHER>::type& extra, const GemmParams& p, int clusters,
                             cudaStream_t stream) {
-    auto kernel = gemm_tcgen05_pair_kernel<KIND, OUT>;
+    auto kernel = gemm_tcgen05_pair_kernel<KIND, OUT, GATHER>;
     constexpr int smem = PairSmem::kDynamicBytes;
     static bool configured[64] = {};
     static int max_clusters[64] = {};
@@ -119,26 +121,32 @@ cudaError_t launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const 
     }
     if (clusters > max_clusters[dev]) clusters = max_clusters[dev];
     if (clusters < 1) clusters = 1;
-    return launch_pdl(kernel, dim3(2 * clusters), dim3(kGemmThreads), smem, stream, ta, tb, tc, p);
+    return launch_pdl(kernel, dim3(2 * clusters), dim3(kGemmThreads), smem, stream, ta, tb, tc, extra, p);
 }
 
 template <int KIND>
-cudaError_t launch_pair_kind(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int clusters,
-                             cudaStream_t stream) {
+cudaError_t launch_pair_kind(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                             const ExtraDst* extra, const GemmParams& p, int clusters, cudaStream_t stream) {
+    const NoExtraDst none = {0};
+#define QGEMM_PAIR_CASE(OUT_)                                                                            \
+    case OUT_:                                                                                           \
+        return extra ? launch_pair_one<KIND, OUT_, true>(ta, tb, tc, *extra, p, clusters, stream)        \
+                     : launch_pair_one<KIND, OUT_, false>(ta, tb, tc, none, p, clusters, stream);
     switch (out) {
-        case OUT_F32: return launch_pair_one<KIND, OUT_F32>(ta, tb, tc, p, clusters, stream);
-        case OUT_BF16: return launch_pair_one<KIND, OUT_BF16>(ta, tb, tc, p, clusters, stream);
-        case OUT_F16: return launch_pair_one<KIND, OUT_F16>(ta, tb, tc, p, clusters, stream);
-        case OUT_RAW32: return launch_pair_one<KIND, OUT_RAW32>(ta, tb, tc, p, clusters, stream);
+        QGEMM_PAIR_CASE(OUT_F32)
+        QGEMM_PAIR_CASE(OUT_BF16)
+        QGEMM_PAIR_CASE(OUT_F16)
+        QGEMM_PAIR_CASE(OUT_RAW32)
         default: return cudaErrorInvalidValue;
     }
+#undef QGEMM_PAIR_CASE
 }
 
-cudaError_t launch_gemm_pair_f16(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+cudaError_t launch_gemm_pair_f16(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const ExtraDst* extra, const GemmParams& p,
                                  int clusters, cudaStream_t stream);
-cudaError_t launch_gemm_pair_i8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+cudaError_t launch_gemm_pair_i8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const ExtraDst* extra, const GemmParams& p,
                                 int clusters, cudaStream_t stream);
-cudaError_t launch_gemm_pair_f8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+cudaError_t launch_gemm_pair_f8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const ExtraDst* extra, const GemmParams& p,
                                 int clusters, cudaStream_t stream);
 
 // Block-scaled FP8 GEMM (gemm_blockscale.cu): 128 x 128 tiles, one partial accumulator per 128-wide K block.

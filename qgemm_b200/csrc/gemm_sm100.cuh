@@ -50,8 +50,21 @@ struct GemmParams {
     int c_vec_ok;  // C base and ldc allow 16-byte vector stores
     int c_tma_ok;  // the C tensor map is valid: the epilogue stores through shared memory + TMA
     int b_mn_major;  // B is read in place as [K,N] row-major (N contiguous): tmap_b is over [K rows, N cols]
+    int n_extra_dst;  // further copies of C written by the same epilogue (CTA-pair kernel only, see ExtraDst)
     int test_skip_kb;  // failure-detection test hook: the producer leaves out the loads of this K block (-1 = none),
                        // so the consumer's bounded wait runs out and the kernel returns through its error path
+};
+
+// Tensor maps of further destinations that receive the same output tiles as C: the same [M, N] block at the
+// same leading dimension in other buffers, typically the matching column block of every peer GPU's full
+// matrix, so that a column-sharded GEMM leaves the gathered matrix on every GPU without a separate all-gather.
+// Only stores go there; nothing is ever loaded from a peer.
+constexpr int kMaxExtraDst = 7;
+struct ExtraDst {
+    CUtensorMap map[kMaxExtraDst];
+};
+struct NoExtraDst {
+    int unused;
 };
 
 constexpr int kBM = 128;
@@ -190,7 +203,8 @@ constexpr int kEpilogueStagingBytes = 4 * 2 * 4096;
 template <int KIND, int OUT, int BN>
 __device__ __forceinline__ void epilogue_tma(const CUtensorMap* tmap_c, uint32_t t_addr, int row0, int m_total,
                                              int n_base, int n_total, int split, uint32_t stage_base, int lane,
-                                             float alpha, uint32_t& buf) {
+                                             float alpha, uint32_t& buf, const CUtensorMap* extra = nullptr,
+                                             int n_extra = 0) {
     constexpr int OB = OutBytes<OUT>::value;
     constexpr int CW = 128 / OB;  // columns per chunk: 64 (16-bit out) or 32 (32-bit out)
     if (row0 >= m_total) return;  // this warp's 32 rows are all padding (warp-uniform)
@@ -241,6 +255,8 @@ __device__ __forceinline__ void epilogue_tma(const CUtensorMap* tmap_c, uint32_t
         __syncwarp();
         if (lane == 0) {
             ptx::tma_store_3d(tmap_c, stage_base + buf * 4096u, n0, row0, split);
+            // the same staged box goes to every further destination; one bulk group covers them all
+            for (int d = 0; d < n_extra; ++d) ptx::tma_store_3d(extra + d, stage_base + buf * 4096u, n0, row0, split);
             ptx::tma_store_commit();
         }
         buf ^= 1u;

@@ -34,11 +34,23 @@ struct PairSmem {
     static constexpr int kDynamicBytes = kTotal + 1024;
 };
 
+template <bool GATHER>
+struct ExtraDstParam {
+    using type = NoExtraDst;
+};
+template <>
+struct ExtraDstParam<true> {
+    using type = ExtraDst;
+};
+
 // p.m_tiles / p.n_tiles count 256 x 256 pair tiles; the grid is 2 * (number of clusters).
-template <int KIND, int OUT>
+// GATHER: the epilogue also stores every tile to the p.n_extra_dst destinations of `extra` (see ExtraDst).
+
+template <int KIND, int OUT, bool GATHER = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                         const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
+                         const __grid_constant__ CUtensorMap tmap_c,
+                         const __grid_constant__ typename ExtraDstParam<GATHER>::type extra, const GemmParams p) {
     using L = PairSmem;
     constexpr int STAGES = kPairStages;
     constexpr int ELT = (KIND == ptx::KIND_F16) ? 2 : 1;
@@ -83,6 +95,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         ptx::prefetch_tensormap(&tmap_a);
         ptx::prefetch_tensormap(&tmap_b);
         if (p.c_tma_ok) ptx::prefetch_tensormap(&tmap_c);
+        if constexpr (GATHER)
+            for (int d = 0; d < p.n_extra_dst; ++d) ptx::prefetch_tensormap(&extra.map[d]);
     }
     if (warp == 1) {
         ptx::tmem_alloc_pair(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
@@ -194,7 +208,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             uint8_t* c_base = reinterpret_cast<uint8_t*>(p.C) +
                               static_cast<long long>(t.split) * p.split_stride * OutBytes<OUT>::value;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
-            if (p.c_tma_ok) {
+            if constexpr (GATHER) {
+                // the host only launches this variant with valid tensor maps for C and every further destination
+                epilogue_tma<KIND, OUT, BN>(&tmap_c, t_addr, (t.m_blk * 2 + static_cast<int>(rank)) * 128 + quad * 32,
+                                            p.M, t.n_blk * BN, p.N, t.split,
+                                            smem_base + L::kOutOffset + (warp - 2) * 8192, lane, alpha, out_buf,
+                                            &extra.map[0], p.n_extra_dst);
+            } else if (p.c_tma_ok) {
                 epilogue_tma<KIND, OUT, BN>(&tmap_c, t_addr, (t.m_blk * 2 + static_cast<int>(rank)) * 128 + quad * 32,
                                             p.M, t.n_blk * BN, p.N, t.split,
                                             smem_base + L::kOutOffset + (warp - 2) * 8192, lane, alpha, out_buf);
@@ -214,7 +234,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa_shared(bar_tempty + acc * 8, 0));
         }
-        if (lane == 0) ptx::tma_store_wait_read<0>();
+        if (lane == 0) {
+            // stores to another GPU are waited for to completion, not just until shared memory was read
+            if constexpr (GATHER) ptx::tma_store_wait_all<0>();
+            else ptx::tma_store_wait_read<0>();
+        }
     }
 
     // ---------------------------------------------------------------- teardown
