@@ -179,6 +179,26 @@ int qgemm_mix_gemm_splitk_static(int in_dtype, int out_dtype, const void* A, siz
                                  size_t K, int split_k, qgemm_stream_t stream);
 
 /*
+ * C = cast(scale_a * scale_b * (A x B)) with A, B and C in HOST memory: what the reference's harness does around
+ * every kernel -- copy the operands to the device, launch, copy C back (tests/includes/test_config.h:239-286) --
+ * as one pipelined call. A goes up in row bands and B in column bands, alternately; each arriving band is
+ * followed by one GEMM over the blocks of C it completes and by their download on a second copy engine, so the
+ * PCIe link stays busy in both directions and only a thin strip is left after the last byte has arrived.
+ *   A_host [M,K], B_host ([K,N] row-major or [N,K] K-major), C_host [M,N]; leading dimensions in elements, no
+ *   alignment requirement on the host side. Pin the host buffers (cudaHostAlloc / cudaHostRegister): with
+ *   pageable memory the copies still work but do not overlap.
+ *   scale_a_host / scale_b_host: HOST pointers to one float each, read during the call; NULL = 1.0.
+ *   dtypes as qgemm_gemm_ex (BF16/FP16 -> FP32/BF16/FP16; INT8 -> INT32 exact, or scaled; FP8 scaled).
+ * Device buffers for the three matrices are kept inside the library between calls (freed by qgemm_shutdown).
+ * The work is ordered after everything already enqueued on `stream`, and on return `stream` has been made to
+ * wait for the last download: C_host is complete once `stream` is synchronised. Calls on one device are
+ * serialised against each other.
+ */
+int qgemm_gemm_host(int in_dtype, int out_dtype, int b_layout, const void* A_host, size_t lda, const void* B_host,
+                    size_t ldb, const float* scale_a_host, const float* scale_b_host, void* C_host, size_t ldc,
+                    size_t M, size_t N, size_t K, qgemm_stream_t stream);
+
+/*
  * GEMM whose result is stored to several buffers by the same kernel: C_dsts[0..n_dsts-1] each receive the
  * identical M x N block (same ldc, same out_dtype). No counterpart in the reference, which is single-GPU; it
  * serves the column-sharded configuration: rank r passes, for every GPU of the box, the address of columns

@@ -28,7 +28,7 @@ C_ABI_SYMBOLS = (
     "qgemm_workspace_bytes", "qgemm_workspace_query", "qgemm_device_status", "qgemm_shutdown",
     "qgemm_status_string", "qgemm_version", "qgemm_mix_gemm_splitk_static",
     "qgemm_fp8_block_scaled_gemm", "qgemm_quantize", "qgemm_gemm_multi_dst", "qgemm_peer_export",
-    "qgemm_peer_open", "qgemm_peer_close",
+    "qgemm_peer_open", "qgemm_peer_close", "qgemm_gemm_host",
 )
 
 
@@ -75,6 +75,9 @@ def lib() -> C.CDLL:
         L.qgemm_quantize.restype = i
         L.qgemm_gemm_multi_dst.argtypes = [i, i, i, vp, sz, vp, sz, fp, fp, C.POINTER(C.c_void_p), i, sz, sz, sz, sz, vp]
         L.qgemm_gemm_multi_dst.restype = i
+        L.qgemm_gemm_host.argtypes = [i, i, i, vp, sz, vp, sz, C.POINTER(C.c_float), C.POINTER(C.c_float), vp, sz, sz,
+                                      sz, sz, vp]
+        L.qgemm_gemm_host.restype = i
         L.qgemm_peer_export.argtypes = [vp, vp, C.POINTER(sz)]
         L.qgemm_peer_export.restype = i
         L.qgemm_peer_open.argtypes = [vp, C.POINTER(C.c_void_p)]

@@ -689,6 +689,7 @@ int qgemm_device_status(int* out4) {
 }
 
 int qgemm_shutdown(void) {
+    host_path_shutdown();
     std::lock_guard<std::mutex> lock(g_mutex);
     int cur = 0;
     if (cudaGetDevice(&cur) != cudaSuccess) return QGEMM_ERR_CUDA;

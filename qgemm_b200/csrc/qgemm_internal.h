@@ -22,4 +22,7 @@ int splitk_reduce_launch(const void* partials, long long split_stride, long long
 int quantize_launch(int in_dtype, int out_dtype, const void* in, size_t ld_in, void* out, size_t ld_out,
                     float* scale_out, float* amax_out, size_t rows, size_t cols, cudaStream_t stream);
 
+// Frees the streams, events and device buffers of the host-operand path (host_gemm.cu).
+void host_path_shutdown();
+
 }  // namespace qgemm

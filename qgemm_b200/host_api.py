@@ -2,85 +2,95 @@
 buffers in, host result out (tests/includes/test_config.h:239-286 allocates on the host, copies to
 the device, runs the kernel and copies C back).
 
-``HostGemm`` owns the device buffers for one problem shape and overlaps the three legs on three
-streams: B is uploaded (and relaid out to K-major if it arrives row-major) first, then A is
-uploaded in row bands; each band's GEMM starts as soon as its rows have landed and its C rows are
-downloaded while later bands are still uploading, so a step costs about max(upload, download)
-instead of their sum. All device work goes through the C-ABI kernels; nothing here computes.
+``HostGemm`` is a thin wrapper over the C-ABI entry ``qgemm_gemm_host``, which owns the device
+buffers and overlaps the three legs itself: A goes up in row bands and B in column bands,
+alternately, each arriving band is followed by one GEMM over the blocks of C it completes and by
+their download while later bands are still uploading, so a step costs about the upload time plus a
+thin last strip instead of upload + GEMM + download. Nothing here computes or copies.
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 
-from . import gemm as _gemm_call
-from . import mix_gemm as _mix_call
-from . import transpose as _transpose_call
+from . import B_K_MAJOR, B_ROW_MAJOR, QgemmError, ERR_INVALID_ARG, _check, _dtype_code, lib
+
+
+def band_schedule(extent: int, bands: int = 8):
+    """The bands [lo, hi) ``qgemm_gemm_host`` cuts an extent of rows (of A) or columns (of B) into: about
+    ``bands`` equal ones made of whole 256-wide tiles, the last of them halved repeatedly down to 256, so that
+    what is left after the final upload is a thin strip's GEMM and download."""
+    if extent <= 0:
+        return []
+    bands = max(1, bands)
+    rows = -(-extent // bands)
+    rows = -(-rows // 256) * 256
+    sizes = []
+    left = extent
+    while left > 0:
+        sizes.append(min(rows, left))
+        left -= sizes[-1]
+    last = sizes.pop()
+    while last > 256:
+        half = -(-(last // 2) // 256) * 256
+        if half >= last:
+            break
+        sizes.append(half)
+        last -= half
+    sizes.append(last)
+    edges, r = [], 0
+    for sz in sizes:
+        edges.append((r, r + sz))
+        r += sz
+    return edges
+
+
+def gemm_host(a_host, b_host, c_host, scale_a=None, scale_b=None, b_kmajor: bool = False, device=None) -> None:
+    """c_host[M,N] = cast(scale_a*scale_b*(a_host[M,K] x B)) with all three tensors in (pinned) host memory;
+    B = b_host[K,N], or b_host[N,K] with ``b_kmajor``. ``scale_a`` / ``scale_b`` are Python floats or None.
+    Enqueues on the current stream of ``device`` (default: the current device); synchronise that stream
+    before reading ``c_host``."""
+    for name, t in (("a_host", a_host), ("b_host", b_host), ("c_host", c_host)):
+        if t.is_cuda or t.dim() != 2 or (t.stride(1) != 1 and t.shape[1] > 1):
+            raise QgemmError(ERR_INVALID_ARG, f"{name} must be a 2-D host tensor with unit inner stride")
+    M, K = a_host.shape
+    N, Kb = (b_host.shape[0], b_host.shape[1]) if b_kmajor else (b_host.shape[1], b_host.shape[0])
+    if Kb != K or tuple(c_host.shape) != (M, N) or a_host.dtype != b_host.dtype:
+        raise QgemmError(ERR_INVALID_ARG, "shape or dtype mismatch")
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    sa = C.byref(C.c_float(float(scale_a))) if scale_a is not None else None
+    sb = C.byref(C.c_float(float(scale_b))) if scale_b is not None else None
+    with torch.cuda.device(dev):
+        rc = lib().qgemm_gemm_host(
+            _dtype_code(a_host), _dtype_code(c_host), B_K_MAJOR if b_kmajor else B_ROW_MAJOR,
+            a_host.data_ptr(), max(a_host.stride(0), K), b_host.data_ptr(), max(b_host.stride(0), b_host.shape[1]),
+            sa, sb, c_host.data_ptr(), max(c_host.stride(0), N), M, N, K,
+            torch.cuda.current_stream(dev).cuda_stream)
+    _check(rc, "qgemm_gemm_host")
 
 
 class HostGemm:
+    """One problem shape on host operands. Kept as a class so that callers can query the traffic and the
+    launch count of a call; the device buffers live inside the library."""
+
     def __init__(self, M: int, N: int, K: int, in_dtype, out_dtype, b_kmajor: bool, device, bands: int = 8):
         self.M, self.N, self.K = M, N, K
         self.b_kmajor = b_kmajor
         self.device = torch.device(device)
-        self.bands = max(1, min(bands, (M + 127) // 128))
-        rows = (M + self.bands - 1) // self.bands
-        rows = (rows + 127) // 128 * 128  # whole output tiles per band
-        self.band_rows = rows
-        self.bands = (M + rows - 1) // rows
-        with torch.cuda.device(self.device):
-            self.a = torch.empty((M, K), dtype=in_dtype, device=self.device)
-            self.b = torch.empty((N, K) if b_kmajor else (K, N), dtype=in_dtype, device=self.device)
-            self.bt = None if b_kmajor else torch.empty((N, K), dtype=in_dtype, device=self.device)
-            self.c = torch.empty((M, N), dtype=out_dtype, device=self.device)
-            self.s_in = torch.cuda.Stream(self.device)
-            self.s_compute = torch.cuda.Stream(self.device)
-            self.s_out = torch.cuda.Stream(self.device)
-        self.kernel_launches_per_call = self.bands + (0 if b_kmajor else 1)
-        self.h2d_bytes = self.a.numel() * self.a.element_size() + self.b.numel() * self.b.element_size()
-        self.d2h_bytes = self.c.numel() * self.c.element_size()
+        self.in_dtype, self.out_dtype = in_dtype, out_dtype
+        es = torch.empty((), dtype=in_dtype).element_size()
+        osz = torch.empty((), dtype=out_dtype).element_size()
+        self.h2d_bytes = (M * K + N * K) * es
+        self.d2h_bytes = M * N * osz
+        # one GEMM per arriving band except the very first (nothing to multiply it with yet)
+        self.kernel_launches_per_call = max(1, len(band_schedule(M, bands)) + len(band_schedule(N, bands)) - 1)
 
     def __call__(self, a_host, b_host, c_host, scale_a=None, scale_b=None) -> None:
-        """Enqueue one C = A x B with pinned host tensors; returns once everything is enqueued on the
-        current stream's dependency chain (synchronise the current stream to wait for c_host)."""
-        cur = torch.cuda.current_stream(self.device)
-        start = torch.cuda.Event()
-        start.record(cur)
-        for s in (self.s_in, self.s_compute, self.s_out):
-            s.wait_event(start)
-
-        with torch.cuda.stream(self.s_in):
-            self.b.copy_(b_host, non_blocking=True)
-            ev_b = torch.cuda.Event()
-            ev_b.record(self.s_in)
-        with torch.cuda.stream(self.s_compute):
-            self.s_compute.wait_event(ev_b)
-            if self.b_kmajor:
-                b_k = self.b
-            else:
-                _transpose_call(self.b, self.bt)
-                b_k = self.bt
-
-        for i in range(self.bands):
-            r0 = i * self.band_rows
-            r1 = min(self.M, r0 + self.band_rows)
-            with torch.cuda.stream(self.s_in):
-                self.a[r0:r1].copy_(a_host[r0:r1], non_blocking=True)
-                ev_a = torch.cuda.Event()
-                ev_a.record(self.s_in)
-            with torch.cuda.stream(self.s_compute):
-                self.s_compute.wait_event(ev_a)
-                if scale_a is None and scale_b is None:
-                    _gemm_call(self.a[r0:r1], b_k, self.c[r0:r1], b_kmajor=True)
-                else:
-                    _mix_call(self.a[r0:r1], b_k, scale_a, scale_b, self.c[r0:r1], b_kmajor=True)
-                ev_c = torch.cuda.Event()
-                ev_c.record(self.s_compute)
-            with torch.cuda.stream(self.s_out):
-                self.s_out.wait_event(ev_c)
-                c_host[r0:r1].copy_(self.c[r0:r1], non_blocking=True)
-
-        done_in, done_out = torch.cuda.Event(), torch.cuda.Event()
-        done_in.record(self.s_in)
-        done_out.record(self.s_out)
-        cur.wait_event(done_in)
-        cur.wait_event(done_out)
+        """Enqueue one C = A x B with pinned host tensors on the current stream's dependency chain
+        (synchronise the current stream to wait for c_host). Scales: floats, 1-element tensors or None."""
+        def as_float(s):
+            if s is None:
+                return None
+            return float(s.item()) if hasattr(s, "item") else float(s)
+        gemm_host(a_host, b_host, c_host, as_float(scale_a), as_float(scale_b), self.b_kmajor, self.device)

@@ -1,11 +1,11 @@
-"""The host-buffer call (qgemm_b200.host_api.HostGemm: pinned host operands in, host result out, upload /
-compute / download overlapped on three streams) and the library's scratch life cycle."""
+"""The host-buffer call (qgemm_gemm_host through qgemm_b200.host_api: host operands in, host result out, upload /
+compute / download overlapped inside the library) and the library's scratch life cycle."""
 import numpy as np
 import pytest
 import torch
 
 from qgemm_b200 import datagen
-from qgemm_b200.host_api import HostGemm
+from qgemm_b200.host_api import HostGemm, band_schedule, gemm_host
 
 pytestmark = pytest.mark.gpu
 
@@ -41,6 +41,62 @@ def test_host_gemm_int8_scaled(qlib, oracle, dev):
     torch.cuda.synchronize()
     ref_bits = oracle.scale_cast(oracle.gemm_i8(ai, bi, True), float(sa), float(sb), oracle.OUT_BF16)
     assert oracle.bf16_ulp_distance(c_h.view(torch.int16).numpy().view(np.uint16), ref_bits) <= 1
+
+
+def test_host_gemm_pageable_memory_strided_buffers_and_int32(qlib, oracle, dev):
+    """Pageable (unpinned) host memory still gives the right answer; host leading dimensions larger than the
+    matrix are honoured; INT8 -> INT32 is exact; several column bands and row bands, the last ones ragged."""
+    M, N, K = 777, 1300, 400
+    ai = datagen.int8_uniform((M, K + 16), seed=4, stream=0)[:, :K]       # lda = K + 16
+    bi = datagen.int8_uniform((K, N + 24), seed=4, stream=1)[:, :N]       # row-major B, ldb = N + 24
+    a_h, b_h = torch.from_numpy(ai), torch.from_numpy(bi)
+    c_full = torch.full((M, N + 8), -7, dtype=torch.int32)
+    c_h = c_full[:, :N]                                                    # ldc = N + 8
+    assert not a_h.is_contiguous() and not c_h.is_contiguous()
+    gemm_host(a_h, b_h, c_h, b_kmajor=False, device=dev)
+    torch.cuda.synchronize()
+    assert np.array_equal(c_h.numpy(), oracle.gemm_i8(np.ascontiguousarray(ai), np.ascontiguousarray(bi), False))
+    assert bool((c_full[:, N:] == -7).all())
+    assert qlib.device_status()[0] == qlib.OK
+
+
+def test_host_gemm_back_to_back_calls_with_different_shapes(qlib, oracle, dev):
+    """Calls are enqueued without a host synchronisation in between: the second must not overwrite device
+    buffers the first is still using, and a larger problem regrows them."""
+    outs = []
+    for M, N, K in [(512, 768, 256), (300, 264, 128), (1536, 1024, 512)]:
+        a_bits, a_val = oracle.round_bf16(datagen.normal((M, K), seed=K, stream=0))
+        b_bits, b_val = oracle.round_bf16(datagen.normal((N, K), seed=K, stream=1))
+        a_h = torch.from_numpy(a_bits.view(np.int16)).view(torch.bfloat16).pin_memory()
+        b_h = torch.from_numpy(b_bits.view(np.int16)).view(torch.bfloat16).pin_memory()
+        c_h = torch.zeros((M, N), dtype=torch.float32).pin_memory()
+        gemm_host(a_h, b_h, c_h, b_kmajor=True, device=dev)
+        outs.append((c_h, a_val, b_val, a_h, b_h))
+    torch.cuda.synchronize()
+    for c_h, a_val, b_val, _, _ in outs:
+        assert oracle.rel_l2(c_h.numpy(), oracle.gemm_f32(a_val, b_val, True)) <= 1e-3
+
+
+def test_host_gemm_empty_and_bad_arguments(qlib, dev):
+    z = torch.zeros((0, 8), dtype=torch.int8)
+    gemm_host(z, torch.zeros((8, 16), dtype=torch.int8), torch.zeros((0, 16), dtype=torch.int32), device=dev)  # M = 0
+    c_h = torch.full((4, 16), 5, dtype=torch.int32)
+    gemm_host(torch.zeros((4, 0), dtype=torch.int8), torch.zeros((0, 16), dtype=torch.int8), c_h, device=dev)  # K = 0
+    torch.cuda.synchronize()
+    assert bool((c_h == 0).all())
+    with pytest.raises(qlib.QgemmError):
+        gemm_host(torch.zeros((4, 8), dtype=torch.int8), torch.zeros((9, 16), dtype=torch.int8), c_h, device=dev)
+    with pytest.raises(qlib.QgemmError):
+        gemm_host(torch.zeros((4, 8), dtype=torch.float32), torch.zeros((8, 16), dtype=torch.float32),
+                  torch.zeros((4, 16), dtype=torch.float32), device=dev)
+
+
+def test_band_schedule_tiles_the_extent():
+    for extent in (1, 200, 256, 257, 1000, 8192, 32768):
+        edges = band_schedule(extent, 8)
+        assert edges[0][0] == 0 and edges[-1][1] == extent
+        assert all(a[1] == b[0] for a, b in zip(edges, edges[1:])) and all(hi > lo for lo, hi in edges)
+        assert edges[-1][1] - edges[-1][0] <= 256 or len(edges) == 1
 
 
 def test_scratch_grows_on_demand_and_survives_shutdown(qlib, oracle, dev):
