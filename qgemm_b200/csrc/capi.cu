@@ -185,9 +185,35 @@ int env_int(const char* name) {
     return v ? std::atoi(v) : 0;
 }
 
+// Last-wave split of the CTA-pair kernel. T tiles on S clusters run as T / S full waves plus a last wave of
+// R = T % S tiles that keeps only R clusters busy for a whole tile's duration. When R is at most half of S, the
+// K range of each of those R tiles is cut into `slices` pieces so that R * slices <= S clusters share them: the
+// last wave then lasts about 1 / slices of a tile, at the price of a second, short launch that stores 32-bit
+// partial sums into 256 x 256 scratch slots and a small pass that adds them up in slice order (a fixed order, so
+// results are reproducible; int8 stays exact). The extra launch, its pipeline fill, the 32-bit partial sums and
+// the sum pass cost 17-27 us as measured on B200 (kTailOverhead, in the units of estimate()), so the split is
+// taken only where the K blocks it saves are worth more than that: deep K and few waves (2560 x 2048 x 8192 bf16,
+// 80 tiles on 74 clusters: 123 -> 93 us), never 4096^3 (94 -> 99 us). Returns false when it does not apply.
+constexpr double kPairTimePerKb = 0.93;
+constexpr double kTailOverhead = 50.0;
+bool tail_split(long long tiles, int clusters, int kb_total, int* tail_tiles, int* slices, int* kb_per_slice) {
+    if (clusters <= 0 || tiles <= clusters) return false;
+    const int r = static_cast<int>(tiles % clusters);
+    if (r == 0 || 2 * r > clusters) return false;
+    const int want = std::min(clusters / r, std::min(kb_total / 4, 16));  // at least 4 K blocks per slice
+    if (want < 2) return false;
+    const int kbps = (kb_total + want - 1) / want;
+    if ((kb_total - kbps) * kPairTimePerKb <= kTailOverhead) return false;
+    *tail_tiles = r;
+    *kb_per_slice = kbps;
+    *slices = (kb_total + kbps - 1) / kbps;
+    return *slices >= 2;
+}
+
 // Estimated duration in units of "one 128-byte K block of a 128x256 tile" (about 0.27 us at peak).
 // `pair` = CTA pairs on 256x256 tiles (half as many schedulable units, a third fewer bytes per flop).
-double estimate(int bn, bool pair, int splits, size_t M, size_t N, int kb_total, int sms, int* kbps_out) {
+double estimate(int bn, bool pair, int splits, size_t M, size_t N, int kb_total, int sms, int* kbps_out,
+                bool allow_tail = false) {
     const int tile_m = pair ? kPairTileM : kBM;
     const int mt = static_cast<int>((M + tile_m - 1) / tile_m);
     const int nt = static_cast<int>((N + bn - 1) / bn);
@@ -198,11 +224,14 @@ double estimate(int bn, bool pair, int splits, size_t M, size_t N, int kb_total,
     const long long waves = (units + slots - 1) / slots;
     // time per K block of one unit, and pipeline fill + epilogue drain per unit
     double t_kb, fill;
-    if (pair) { t_kb = 0.93; fill = 6.0; }
+    if (pair) { t_kb = kPairTimePerKb; fill = 6.0; }
     else if (bn == 256) { t_kb = 1.0; fill = 6.0; }
     else if (bn == 128) { t_kb = 0.56; fill = 4.5; }   // narrower tiles re-read A relatively more often
     else { t_kb = 0.33; fill = 4.0; }
     double t = static_cast<double>(waves) * (kbps * t_kb + fill);
+    int tt = 0, ts = 0, tk = 0;
+    if (pair && real_splits == 1 && allow_tail && tail_split(units, slots, kb_total, &tt, &ts, &tk))
+        t = static_cast<double>(waves - 1) * (kbps * t_kb + fill) + (tk * t_kb + fill) + kTailOverhead;
     if (real_splits > 1) {
         // partial slabs are written once and read once by the second pass (~1.75 MB per unit of time)
         const double slab_bytes = static_cast<double>(real_splits) * M * N * 4.0;
@@ -212,7 +241,8 @@ double estimate(int bn, bool pair, int splits, size_t M, size_t N, int kb_total,
     return t;
 }
 
-Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuning_t* tuning, int min_bn = 64) {
+Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuning_t* tuning, int min_bn = 64,
+                     bool allow_tail = false) {
     int want_bn = tuning ? tuning->tile_n : 0;
     int want_split = tuning ? tuning->split_k : 0;
     int want_group = tuning ? tuning->group_m : 0;
@@ -235,7 +265,7 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
         for (int s = want_split ? want_split : 1; s <= max_split; ++s) {
             if (s > kb_total) break;
             int kbps = 0;
-            const double t = estimate(c.bn, c.pair, s, M, N, kb_total, sms, &kbps);
+            const double t = estimate(c.bn, c.pair, s, M, N, kb_total, sms, &kbps, allow_tail && !want_split);
             if (!want_split && s > 1 && kbps < 2) continue;
             if (t < best_t) {
                 best_t = t;
@@ -303,11 +333,14 @@ struct Plan {
     size_t ld_relayout;     // elements; leading dimension of the relaid-out B
     size_t relayout_bytes;  // 0 when B is already K-major
     size_t ldw;             // leading dimension of split-K partial slabs (elements)
-    size_t partial_bytes;   // 0 when splits == 1
+    size_t partial_bytes;   // 0 when splits == 1 and there is no last-wave split
+    int tail_tiles;         // last-wave split (see tail_split): tiles of the last wave, 0 = off
+    int tail_slices;
+    int tail_kb_per_slice;
 };
 
 int make_plan(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, size_t K, int sms,
-              const qgemm_tuning_t* tuning, Plan* p, bool b_direct = false) {
+              const qgemm_tuning_t* tuning, Plan* p, bool b_direct = false, bool allow_tail = true) {
     if (!type_info(in_dtype, &p->ti)) return QGEMM_ERR_UNSUPPORTED;
     p->out_kind = out_kind_of(out_dtype);
     if (p->out_kind < 0) return QGEMM_ERR_UNSUPPORTED;
@@ -317,13 +350,28 @@ int make_plan(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, siz
     const size_t kblk = 128 / p->ti.elem_bytes;
     p->kb_total = static_cast<int>((K + kblk - 1) / kblk);
     // an 8-bit B read in place comes in 128-column chunks: no 64-wide tiles then
+    // The last-wave split is the library's own choice: any explicit split-K, CTA cap or store-path override
+    // (argument or environment) turns it off, and so does QGEMM_TAIL_SPLIT=0.
+    const char* tail_env = std::getenv("QGEMM_TAIL_SPLIT");
+    allow_tail = allow_tail && !(tuning && (tuning->split_k != 0 || tuning->max_ctas != 0)) &&
+                 env_int("QGEMM_SPLIT_K") == 0 && env_int("QGEMM_MAX_CTAS") == 0 &&
+                 env_int("QGEMM_DIRECT_STORE") == 0 && !(tail_env != nullptr && tail_env[0] == '0');
     p->cfg = choose_config(M, N, std::max(p->kb_total, 1), sms, tuning,
-                           (b_direct && p->ti.elem_bytes == 1) ? 128 : 64);
+                           (b_direct && p->ti.elem_bytes == 1) ? 128 : 64, allow_tail);
     p->ld_relayout = round_up(K, 16 / p->ti.elem_bytes);
     p->relayout_bytes =
         (b_layout == QGEMM_B_ROW_MAJOR && !b_direct) ? round_up(N * p->ld_relayout * p->ti.elem_bytes, 256) : 0;
     p->ldw = round_up(N, 4);
     p->partial_bytes = p->cfg.splits > 1 ? static_cast<size_t>(p->cfg.splits) * M * p->ldw * 4 : 0;
+    p->tail_tiles = p->tail_slices = p->tail_kb_per_slice = 0;
+    if (allow_tail && p->cfg.pair && p->cfg.splits == 1) {
+        const long long tiles = static_cast<long long>((M + kPairTileM - 1) / kPairTileM) *
+                                static_cast<long long>((N + kPairTileN - 1) / kPairTileN);
+        if (tail_split(tiles, sms / 2, p->kb_total, &p->tail_tiles, &p->tail_slices, &p->tail_kb_per_slice))
+            p->partial_bytes = static_cast<size_t>(p->tail_slices) * p->tail_tiles * kPairTileM * kPairTileN * 4;
+        else
+            p->tail_tiles = 0;
+    }
     return QGEMM_OK;
 }
 
@@ -362,7 +410,7 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     const bool b_direct = b_layout == QGEMM_B_ROW_MAJOR && !want_relayout && K > 0 &&
                           reinterpret_cast<uintptr_t>(B) % 16 == 0 && (ldb * ti0.elem_bytes) % 16 == 0;
     Plan plan;
-    rc = make_plan(in_dtype, out_dtype, b_layout, M, N, K, st->sm_count, tuning, &plan, b_direct);
+    rc = make_plan(in_dtype, out_dtype, b_layout, M, N, K, st->sm_count, tuning, &plan, b_direct, n_extra == 0);
     if (rc != QGEMM_OK) return rc;
     if (plan.out_kind == OUT_RAW32 && (scale_a != nullptr || scale_b != nullptr)) return QGEMM_ERR_INVALID_ARG;
     const int out_bytes = (plan.out_kind == OUT_BF16 || plan.out_kind == OUT_F16) ? 2 : 4;
@@ -475,6 +523,8 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     if (cfg.pair) {
         int clusters = static_cast<int>(std::min<long long>(work, st->sm_count / 2));
         if (cap > 0) clusters = std::min(clusters, std::max(1, cap / 2));
+        const bool tail = plan.tail_tiles > 0 && p.c_tma_ok;
+        if (tail) p.work_end = static_cast<int>(work) - plan.tail_tiles;  // this launch: the full waves only
         switch (plan.ti.kind) {
             case ptx::KIND_F16: e = launch_gemm_pair_f16(launch_out, ta, tb, tc, extra_arg, p, clusters, stream); break;
             case ptx::KIND_I8: e = launch_gemm_pair_i8(launch_out, ta, tb, tc, extra_arg, p, clusters, stream); break;
@@ -488,6 +538,39 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
         }
     }
     if (e != cudaSuccess) return QGEMM_ERR_CUDA;
+
+    if (cfg.pair && plan.tail_tiles > 0 && p.c_tma_ok) {
+        // Last wave: every tile's K range in slices over all clusters, partial sums into scratch slots, then the sum.
+        GemmParams pt = p;
+        pt.C = partials;
+        pt.ldc = kPairTileN;
+        pt.split_stride = 0;
+        pt.scale_a = pt.scale_b = nullptr;
+        pt.splits = plan.tail_slices;
+        pt.kb_per_split = plan.tail_kb_per_slice;
+        pt.tile_offset = static_cast<int>(work) - plan.tail_tiles;
+        pt.work_end = plan.tail_tiles * plan.tail_slices;
+        pt.compact_store = 1;
+        pt.c_vec_ok = 1;
+        CUtensorMap tct;
+        rc = make_output_map(partials, static_cast<uint64_t>(plan.tail_tiles) * kPairTileM, kPairTileN, kPairTileN,
+                             static_cast<uint64_t>(plan.tail_slices), OUT_RAW32, &tct);
+        if (rc != QGEMM_OK) return rc;
+        const int tail_clusters = std::min(pt.work_end, st->sm_count / 2);
+        switch (plan.ti.kind) {
+            case ptx::KIND_F16: e = launch_gemm_pair_f16(OUT_RAW32, ta, tb, tct, nullptr, pt, tail_clusters, stream); break;
+            case ptx::KIND_I8: e = launch_gemm_pair_i8(OUT_RAW32, ta, tb, tct, nullptr, pt, tail_clusters, stream); break;
+            default: e = launch_gemm_pair_f8(OUT_RAW32, ta, tb, tct, nullptr, pt, tail_clusters, stream); break;
+        }
+        if (e != cudaSuccess) return QGEMM_ERR_CUDA;
+        GemmParams tiles = p;
+        tiles.splits = 1;
+        tiles.tile_offset = pt.tile_offset;
+        rc = splitk_reduce_tiles_launch(partials, plan.tail_tiles, plan.tail_slices, plan.ti.acc_int, C,
+                                        static_cast<long long>(ldc), p.M, p.N, plan.out_kind, scale_a, scale_b, tiles,
+                                        stream);
+        if (rc != QGEMM_OK) return rc;
+    }
 
     if (cfg.splits > 1) {
         rc = splitk_reduce_launch(partials, p.split_stride, p.ldc, cfg.splits, plan.ti.acc_int, C,

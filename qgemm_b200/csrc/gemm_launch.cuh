@@ -167,6 +167,13 @@ struct BlockScaleParams {
 cudaError_t launch_fp8_blockscale(int out_kind, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
                                   const BlockScaleParams& p, int grid, cudaStream_t stream);
 
+// Adds up the K slices of the last-wave tiles (splitk_reduce.cu): `slots` tiles stored as
+// [splits][slots * 256][256] 32-bit partial sums; `tiles` locates slot i in C (m_tiles, n_tiles, group_m,
+// tile_offset; splits = 1).
+int splitk_reduce_tiles_launch(const void* partials, int slots, int splits, bool acc_is_int, void* C, long long ldc,
+                               int M, int N, int out_kind, const float* scale_a, const float* scale_b,
+                               const GemmParams& tiles, cudaStream_t stream);
+
 // Defined one per translation unit so the kinds compile in parallel.
 cudaError_t launch_gemm_f16(int bn, int out, int am, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                             int grid, cudaStream_t stream);

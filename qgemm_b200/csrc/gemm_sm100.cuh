@@ -51,6 +51,13 @@ struct GemmParams {
     int c_tma_ok;  // the C tensor map is valid: the epilogue stores through shared memory + TMA
     int b_mn_major;  // B is read in place as [K,N] row-major (N contiguous): tmap_b is over [K rows, N cols]
     int n_extra_dst;  // further copies of C written by the same epilogue (CTA-pair kernel only, see ExtraDst)
+    // A launch may cover only part of the tile list (CTA-pair kernel): work items [0, work_end) when work_end > 0,
+    // tile numbers shifted by tile_offset. With compact_store the tile computed by work item w is stored, not at
+    // its place in C, but as 256 x 256 slot number (w / splits) of a [splits][slots * 256][256] scratch array:
+    // that is how the last, partial wave of tiles is cut along K over all the SMs (see tail_split in capi.cu).
+    int work_end;
+    int tile_offset;
+    int compact_store;
     int test_skip_kb;  // failure-detection test hook: the producer leaves out the loads of this K block (-1 = none),
                        // so the consumer's bounded wait runs out and the kernel returns through its error path
 };
@@ -109,6 +116,7 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
 
 struct TileCoord {
     int m_blk, n_blk, split;
+    int slot;  // tile number within this launch (before tile_offset is added)
 };
 
 // Work item -> tile. Splits of one tile are adjacent; tiles are grouped `group_m` tile-rows at a
@@ -118,6 +126,8 @@ __device__ __forceinline__ TileCoord decode_tile(int w, const GemmParams& p) {
     TileCoord t;
     int tile = w / p.splits;
     t.split = w - tile * p.splits;
+    t.slot = tile;
+    tile += p.tile_offset;
     int group_sz = p.group_m * p.n_tiles;
     int g = tile / group_sz;
     int first_m = g * p.group_m;

@@ -77,7 +77,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const uint32_t rank = ptx::cluster_ctarank();  // 0 = leader
     const int cluster_id = static_cast<int>(blockIdx.x) >> 1;
     const int n_clusters = static_cast<int>(gridDim.x) >> 1;
-    const int total_work = p.m_tiles * p.n_tiles * p.splits;
+    const int total_work = p.work_end > 0 ? p.work_end : p.m_tiles * p.n_tiles * p.splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -208,16 +208,26 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             uint8_t* c_base = reinterpret_cast<uint8_t*>(p.C) +
                               static_cast<long long>(t.split) * p.split_stride * OutBytes<OUT>::value;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
-            if constexpr (GATHER) {
-                // the host only launches this variant with valid tensor maps for C and every further destination
-                epilogue_tma<KIND, OUT, BN>(&tmap_c, t_addr, (t.m_blk * 2 + static_cast<int>(rank)) * 128 + quad * 32,
-                                            p.M, t.n_blk * BN, p.N, t.split,
+            // Where this tile goes: its place in C, or (compact_store: partial sums of a K slice of a last-wave
+            // tile) a whole 256 x 256 slot of the scratch array, where nothing needs clipping.
+            int row0 = (t.m_blk * 2 + static_cast<int>(rank)) * 128 + quad * 32;
+            int m_total = p.M, n_base = t.n_blk * BN, n_total = p.N;
+            if (p.compact_store) {
+                row0 = (t.slot * 2 + static_cast<int>(rank)) * 128 + quad * 32;
+                m_total = 0x7fffffff;
+                n_base = 0;
+                n_total = BN;
+            }
+            const CUtensorMap* extra_maps = nullptr;
+            int n_extra = 0;
+            if constexpr (GATHER) {  // launched only with valid tensor maps for C and every further destination
+                extra_maps = &extra.map[0];
+                n_extra = p.n_extra_dst;
+            }
+            if (GATHER || p.c_tma_ok) {
+                epilogue_tma<KIND, OUT, BN>(&tmap_c, t_addr, row0, m_total, n_base, n_total, t.split,
                                             smem_base + L::kOutOffset + (warp - 2) * 8192, lane, alpha, out_buf,
-                                            &extra.map[0], p.n_extra_dst);
-            } else if (p.c_tma_ok) {
-                epilogue_tma<KIND, OUT, BN>(&tmap_c, t_addr, (t.m_blk * 2 + static_cast<int>(rank)) * 128 + quad * 32,
-                                            p.M, t.n_blk * BN, p.N, t.split,
-                                            smem_base + L::kOutOffset + (warp - 2) * 8192, lane, alpha, out_buf);
+                                            extra_maps, n_extra);
             } else {
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {

@@ -12,21 +12,13 @@ namespace qgemm {
 
 namespace {
 
+// Sums four consecutive columns over the splits (src, src + split_stride, ...) in split order and writes
+// cast(scale_a * scale_b * sum), or the raw 32-bit sum, to C[row, col .. col+3] (columns >= N left alone).
 template <bool ACC_INT>
-__global__ void __launch_bounds__(256)
-splitk_reduce_kernel(const uint32_t* __restrict__ partials, long long split_stride, long long ldw, int splits,
-                     void* __restrict__ C, long long ldc, int M, int N, int out_kind,
-                     const float* __restrict__ scale_a, const float* __restrict__ scale_b, int c_vec_ok) {
-    ptx::pdl_launch_dependents();
-    ptx::pdl_wait();
-    const long long quads_per_row = ldw >> 2;
-    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (idx >= quads_per_row * M) return;
-    const long long row = idx / quads_per_row;
-    const int col = static_cast<int>(idx - row * quads_per_row) * 4;
-    if (col >= N) return;
-
-    const uint32_t* src = partials + row * ldw + col;
+__device__ __forceinline__ void reduce_quad(const uint32_t* __restrict__ src, long long split_stride, int splits,
+                                            void* __restrict__ C, long long ldc, long long row, int col, int N,
+                                            int out_kind, const float* __restrict__ scale_a,
+                                            const float* __restrict__ scale_b, int c_vec_ok) {
     uint32_t raw[4];
     float f[4];
     if constexpr (ACC_INT) {
@@ -103,7 +95,66 @@ splitk_reduce_kernel(const uint32_t* __restrict__ partials, long long split_stri
     }
 }
 
+template <bool ACC_INT>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const uint32_t* __restrict__ partials, long long split_stride, long long ldw, int splits,
+                     void* __restrict__ C, long long ldc, int M, int N, int out_kind,
+                     const float* __restrict__ scale_a, const float* __restrict__ scale_b, int c_vec_ok) {
+    ptx::pdl_launch_dependents();
+    ptx::pdl_wait();
+    const long long quads_per_row = ldw >> 2;
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= quads_per_row * M) return;
+    const long long row = idx / quads_per_row;
+    const int col = static_cast<int>(idx - row * quads_per_row) * 4;
+    if (col >= N) return;
+    reduce_quad<ACC_INT>(partials + row * ldw + col, split_stride, splits, C, ldc, row, col, N, out_kind, scale_a,
+                         scale_b, c_vec_ok);
+}
+
+// The same sum for tiles whose K slices were stored as compact 256 x 256 slots ([splits][slots * 256][256]):
+// blockIdx.y = slot; the tile's place in C comes from the GEMM's own tile order (`tiles` carries m_tiles, n_tiles,
+// group_m and tile_offset, with splits = 1).
+template <bool ACC_INT>
+__global__ void __launch_bounds__(256)
+splitk_reduce_tiles_kernel(const uint32_t* __restrict__ partials, long long split_stride, int splits,
+                           void* __restrict__ C, long long ldc, int M, int N, int out_kind,
+                           const float* __restrict__ scale_a, const float* __restrict__ scale_b, int c_vec_ok,
+                           const GemmParams tiles) {
+    ptx::pdl_launch_dependents();
+    ptx::pdl_wait();
+    const int slot = static_cast<int>(blockIdx.y);
+    const TileCoord t = decode_tile(slot, tiles);
+    const int idx = static_cast<int>(blockIdx.x) * 256 + static_cast<int>(threadIdx.x);  // 256 rows x 64 quads
+    const int r = idx >> 6;
+    const int c = (idx & 63) * 4;
+    const long long row = static_cast<long long>(t.m_blk) * kPairTileM + r;
+    const int col = t.n_blk * kPairTileN + c;
+    if (r >= kPairTileM || row >= M || col >= N) return;
+    const uint32_t* src = partials + (static_cast<long long>(slot) * kPairTileM + r) * kPairTileN + c;
+    reduce_quad<ACC_INT>(src, split_stride, splits, C, ldc, row, col, N, out_kind, scale_a, scale_b, c_vec_ok);
+}
+
 }  // namespace
+
+int splitk_reduce_tiles_launch(const void* partials, int slots, int splits, bool acc_is_int, void* C, long long ldc,
+                               int M, int N, int out_kind, const float* scale_a, const float* scale_b,
+                               const GemmParams& tiles, cudaStream_t stream) {
+    if (slots <= 0) return QGEMM_OK;
+    const int out_bytes = (out_kind == OUT_BF16 || out_kind == OUT_F16) ? 2 : 4;
+    const int c_vec_ok = (reinterpret_cast<uintptr_t>(C) % 16 == 0) && ((ldc * out_bytes) % 16 == 0);
+    const long long split_stride = static_cast<long long>(slots) * kPairTileM * kPairTileN;
+    const uint32_t* p = reinterpret_cast<const uint32_t*>(partials);
+    const dim3 grid(kPairTileM * (kPairTileN / 4) / 256, static_cast<unsigned>(slots));
+    cudaError_t e;
+    if (acc_is_int)
+        e = launch_pdl(splitk_reduce_tiles_kernel<true>, grid, dim3(256), 0, stream, p, split_stride, splits, C, ldc, M,
+                       N, out_kind, scale_a, scale_b, c_vec_ok, tiles);
+    else
+        e = launch_pdl(splitk_reduce_tiles_kernel<false>, grid, dim3(256), 0, stream, p, split_stride, splits, C, ldc,
+                       M, N, out_kind, scale_a, scale_b, c_vec_ok, tiles);
+    return e == cudaSuccess ? QGEMM_OK : QGEMM_ERR_CUDA;
+}
 
 int splitk_reduce_launch(const void* partials, long long split_stride, long long ldw, int splits, bool acc_is_int,
                          void* C, long long ldc, int M, int N, int out_kind, const float* scale_a,
