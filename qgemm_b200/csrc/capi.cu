@@ -186,20 +186,21 @@ int env_int(const char* name) {
 }
 
 // Last-wave split of the CTA-pair kernel. T tiles on S clusters run as T / S full waves plus a last wave of
-// R = T % S tiles that keeps only R clusters busy for a whole tile's duration. When R is at most half of S, the
-// K range of each of those R tiles is cut into `slices` pieces so that R * slices <= S clusters share them: the
-// last wave then lasts about 1 / slices of a tile, at the price of a second, short launch that stores 32-bit
-// partial sums into 256 x 256 scratch slots and a small pass that adds them up in slice order (a fixed order, so
-// results are reproducible; int8 stays exact). The extra launch, its pipeline fill, the 32-bit partial sums and
-// the sum pass cost 17-27 us as measured on B200 (kTailOverhead, in the units of estimate()), so the split is
-// taken only where the K blocks it saves are worth more than that: deep K and few waves (2560 x 2048 x 8192 bf16,
-// 80 tiles on 74 clusters: 123 -> 93 us), never 4096^3 (94 -> 99 us). Returns false when it does not apply.
+// R = T % S tiles that keeps only R clusters busy for a whole tile's duration. When R is small, the K range of
+// each of those R tiles is cut into `slices` pieces so that R * slices <= S clusters share them: the last wave
+// then lasts about 1 / slices of a tile. The slices are further work items of the same persistent launch; their
+// 32-bit partial sums go to 256 x 256 scratch slots, and a small second kernel adds them up in slice order (a
+// fixed order, so results are reproducible; int8 stays exact), scales and casts.
+// Taken only when few clusters would be busy in the last wave (R <= S / 4) and the K blocks saved outweigh the
+// partial-sum traffic and the second kernel (kTailOverhead, in the units of estimate()). Measured on B200: bf16
+// 2560 x 2048 x 4096 (80 tiles on 74 clusters) 61 -> 51 us; with R = 34 (4096^3) the split gains nothing, because
+// the part runs at its power cap and a half-empty last wave simply runs at a higher clock.
 constexpr double kPairTimePerKb = 0.93;
-constexpr double kTailOverhead = 50.0;
+constexpr double kTailOverhead = 16.0;
 bool tail_split(long long tiles, int clusters, int kb_total, int* tail_tiles, int* slices, int* kb_per_slice) {
     if (clusters <= 0 || tiles <= clusters) return false;
     const int r = static_cast<int>(tiles % clusters);
-    if (r == 0 || 2 * r > clusters) return false;
+    if (r == 0 || 4 * r > clusters) return false;
     const int want = std::min(clusters / r, std::min(kb_total / 4, 16));  // at least 4 K blocks per slice
     if (want < 2) return false;
     const int kbps = (kb_total + want - 1) / want;
@@ -520,15 +521,27 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     if (cap > 0) grid = std::min(grid, cap);
 
     cudaError_t e;
+    const bool tail = cfg.pair && plan.tail_tiles > 0 && p.c_tma_ok && n_extra == 0;
+    p.total_work = static_cast<int>(work);
     if (cfg.pair) {
-        int clusters = static_cast<int>(std::min<long long>(work, st->sm_count / 2));
+        CUtensorMap tws;
+        std::memset(&tws, 0, sizeof(tws));
+        if (tail) {
+            // whole tiles first, then the last wave's tiles as K slices whose partial sums go to scratch slots
+            p.tail_begin = static_cast<int>(work) - plan.tail_tiles;
+            p.tail_slices = plan.tail_slices;
+            p.tail_kb_per_slice = plan.tail_kb_per_slice;
+            p.total_work = p.tail_begin + plan.tail_tiles * plan.tail_slices;
+            rc = make_output_map(partials, static_cast<uint64_t>(plan.tail_tiles) * kPairTileM, kPairTileN, kPairTileN,
+                                 static_cast<uint64_t>(plan.tail_slices), OUT_RAW32, &tws);
+            if (rc != QGEMM_OK) return rc;
+        }
+        int clusters = static_cast<int>(std::min<long long>(p.total_work, st->sm_count / 2));
         if (cap > 0) clusters = std::min(clusters, std::max(1, cap / 2));
-        const bool tail = plan.tail_tiles > 0 && p.c_tma_ok;
-        if (tail) p.work_end = static_cast<int>(work) - plan.tail_tiles;  // this launch: the full waves only
         switch (plan.ti.kind) {
-            case ptx::KIND_F16: e = launch_gemm_pair_f16(launch_out, ta, tb, tc, extra_arg, p, clusters, stream); break;
-            case ptx::KIND_I8: e = launch_gemm_pair_i8(launch_out, ta, tb, tc, extra_arg, p, clusters, stream); break;
-            default: e = launch_gemm_pair_f8(launch_out, ta, tb, tc, extra_arg, p, clusters, stream); break;
+            case ptx::KIND_F16: e = launch_gemm_pair_f16(launch_out, ta, tb, tc, tws, extra_arg, p, clusters, stream); break;
+            case ptx::KIND_I8: e = launch_gemm_pair_i8(launch_out, ta, tb, tc, tws, extra_arg, p, clusters, stream); break;
+            default: e = launch_gemm_pair_f8(launch_out, ta, tb, tc, tws, extra_arg, p, clusters, stream); break;
         }
     } else {
         switch (plan.ti.kind) {
@@ -539,33 +552,10 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     }
     if (e != cudaSuccess) return QGEMM_ERR_CUDA;
 
-    if (cfg.pair && plan.tail_tiles > 0 && p.c_tma_ok) {
-        // Last wave: every tile's K range in slices over all clusters, partial sums into scratch slots, then the sum.
-        GemmParams pt = p;
-        pt.C = partials;
-        pt.ldc = kPairTileN;
-        pt.split_stride = 0;
-        pt.scale_a = pt.scale_b = nullptr;
-        pt.splits = plan.tail_slices;
-        pt.kb_per_split = plan.tail_kb_per_slice;
-        pt.tile_offset = static_cast<int>(work) - plan.tail_tiles;
-        pt.work_end = plan.tail_tiles * plan.tail_slices;
-        pt.compact_store = 1;
-        pt.c_vec_ok = 1;
-        CUtensorMap tct;
-        rc = make_output_map(partials, static_cast<uint64_t>(plan.tail_tiles) * kPairTileM, kPairTileN, kPairTileN,
-                             static_cast<uint64_t>(plan.tail_slices), OUT_RAW32, &tct);
-        if (rc != QGEMM_OK) return rc;
-        const int tail_clusters = std::min(pt.work_end, st->sm_count / 2);
-        switch (plan.ti.kind) {
-            case ptx::KIND_F16: e = launch_gemm_pair_f16(OUT_RAW32, ta, tb, tct, nullptr, pt, tail_clusters, stream); break;
-            case ptx::KIND_I8: e = launch_gemm_pair_i8(OUT_RAW32, ta, tb, tct, nullptr, pt, tail_clusters, stream); break;
-            default: e = launch_gemm_pair_f8(OUT_RAW32, ta, tb, tct, nullptr, pt, tail_clusters, stream); break;
-        }
-        if (e != cudaSuccess) return QGEMM_ERR_CUDA;
+    if (tail) {
+        // the K slices of the last-wave tiles are in scratch: add them up in slice order, scale, cast, store
         GemmParams tiles = p;
-        tiles.splits = 1;
-        tiles.tile_offset = pt.tile_offset;
+        tiles.tile_offset = p.tail_begin;
         rc = splitk_reduce_tiles_launch(partials, plan.tail_tiles, plan.tail_slices, plan.ti.acc_int, C,
                                         static_cast<long long>(ldc), p.M, p.N, plan.out_kind, scale_a, scale_b, tiles,
                                         stream);

@@ -84,9 +84,10 @@ cudaError_t launch_kind(int bn, int out, int am, const CUtensorMap& ta, const CU
 
 // CTA-pair kernel (256 x 256 tiles, clusters of two); the number of clusters is clamped to what the device can
 // keep resident at once (queried once per device). `extra` non-null selects the variant whose epilogue also
-// stores every tile to p.n_extra_dst further destinations.
+// stores every tile to p.n_extra_dst further destinations; `tws` is the tensor map of the last-wave scratch slots
+// (read only when p.tail_begin > 0).
 template <int KIND, int OUT, bool GATHER>
-cudaError_t launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+cudaError_t launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tws,
                             const typename ExtraDstParam<GATHER>::type& extra, const GemmParams& p, int clusters,
                             cudaStream_t stream) {
     auto kernel = gemm_tcgen05_pair_kernel<KIND, OUT, GATHER>;
@@ -121,17 +122,18 @@ cudaError_t launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const 
     }
     if (clusters > max_clusters[dev]) clusters = max_clusters[dev];
     if (clusters < 1) clusters = 1;
-    return launch_pdl(kernel, dim3(2 * clusters), dim3(kGemmThreads), smem, stream, ta, tb, tc, extra, p);
+    return launch_pdl(kernel, dim3(2 * clusters), dim3(kGemmThreads), smem, stream, ta, tb, tc, tws, extra, p);
 }
 
 template <int KIND>
 cudaError_t launch_pair_kind(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
-                             const ExtraDst* extra, const GemmParams& p, int clusters, cudaStream_t stream) {
+                             const CUtensorMap& tws, const ExtraDst* extra, const GemmParams& p, int clusters,
+                             cudaStream_t stream) {
     const NoExtraDst none = {0};
 #define QGEMM_PAIR_CASE(OUT_)                                                                            \
     case OUT_:                                                                                           \
-        return extra ? launch_pair_one<KIND, OUT_, true>(ta, tb, tc, *extra, p, clusters, stream)        \
-                     : launch_pair_one<KIND, OUT_, false>(ta, tb, tc, none, p, clusters, stream);
+        return extra ? launch_pair_one<KIND, OUT_, true>(ta, tb, tc, tws, *extra, p, clusters, stream)        \
+                     : launch_pair_one<KIND, OUT_, false>(ta, tb, tc, tws, none, p, clusters, stream);
     switch (out) {
         QGEMM_PAIR_CASE(OUT_F32)
         QGEMM_PAIR_CASE(OUT_BF16)
@@ -142,11 +144,14 @@ cudaError_t launch_pair_kind(int out, const CUtensorMap& ta, const CUtensorMap& 
 #undef QGEMM_PAIR_CASE
 }
 
-cudaError_t launch_gemm_pair_f16(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const ExtraDst* extra, const GemmParams& p,
+cudaError_t launch_gemm_pair_f16(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tws,
+                                 const ExtraDst* extra, const GemmParams& p,
                                  int clusters, cudaStream_t stream);
-cudaError_t launch_gemm_pair_i8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const ExtraDst* extra, const GemmParams& p,
+cudaError_t launch_gemm_pair_i8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tws,
+                                 const ExtraDst* extra, const GemmParams& p,
                                 int clusters, cudaStream_t stream);
-cudaError_t launch_gemm_pair_f8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const ExtraDst* extra, const GemmParams& p,
+cudaError_t launch_gemm_pair_f8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tws,
+                                 const ExtraDst* extra, const GemmParams& p,
                                 int clusters, cudaStream_t stream);
 
 // Block-scaled FP8 GEMM (gemm_blockscale.cu): 128 x 128 tiles, one partial accumulator per 128-wide K block.

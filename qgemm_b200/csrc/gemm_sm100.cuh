@@ -51,13 +51,15 @@ struct GemmParams {
     int c_tma_ok;  // the C tensor map is valid: the epilogue stores through shared memory + TMA
     int b_mn_major;  // B is read in place as [K,N] row-major (N contiguous): tmap_b is over [K rows, N cols]
     int n_extra_dst;  // further copies of C written by the same epilogue (CTA-pair kernel only, see ExtraDst)
-    // A launch may cover only part of the tile list (CTA-pair kernel): work items [0, work_end) when work_end > 0,
-    // tile numbers shifted by tile_offset. With compact_store the tile computed by work item w is stored, not at
-    // its place in C, but as 256 x 256 slot number (w / splits) of a [splits][slots * 256][256] scratch array:
-    // that is how the last, partial wave of tiles is cut along K over all the SMs (see tail_split in capi.cu).
-    int work_end;
-    int tile_offset;
-    int compact_store;
+    // Last-wave split (CTA-pair kernel, splits == 1): work items [0, tail_begin) are whole tiles; item
+    // tail_begin + u is K slice (u % tail_slices) of tile number tail_begin + u / tail_slices, whose 32-bit partial
+    // sums go to 256 x 256 slot (u / tail_slices) of a [tail_slices][slots * 256][256] scratch array instead of C
+    // (see tail_split in capi.cu). tail_begin == 0: no such items. total_work counts both kinds.
+    int tail_begin;
+    int tail_slices;
+    int tail_kb_per_slice;
+    int total_work;
+    int tile_offset;  // added to the tile number by decode_tile (the pass that sums the slices locates slot i with it)
     int test_skip_kb;  // failure-detection test hook: the producer leaves out the loads of this K block (-1 = none),
                        // so the consumer's bounded wait runs out and the kernel returns through its error path
 };
@@ -116,7 +118,6 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
 
 struct TileCoord {
     int m_blk, n_blk, split;
-    int slot;  // tile number within this launch (before tile_offset is added)
 };
 
 // Work item -> tile. Splits of one tile are adjacent; tiles are grouped `group_m` tile-rows at a
@@ -126,7 +127,6 @@ __device__ __forceinline__ TileCoord decode_tile(int w, const GemmParams& p) {
     TileCoord t;
     int tile = w / p.splits;
     t.split = w - tile * p.splits;
-    t.slot = tile;
     tile += p.tile_offset;
     int group_sz = p.group_m * p.n_tiles;
     int g = tile / group_sz;
@@ -136,6 +136,32 @@ __device__ __forceinline__ TileCoord decode_tile(int w, const GemmParams& p) {
     t.n_blk = r / gm;
     t.m_blk = first_m + (r - t.n_blk * gm);
     return t;
+}
+
+// One work item of the CTA-pair kernel: a whole tile, or one K slice of a last-wave tile.
+struct WorkItem {
+    TileCoord t;
+    int kb0, kb1;  // K blocks [kb0, kb1)
+    int slot;      // >= 0: partial sums of slice t.split go to this scratch slot; -1: an ordinary tile
+};
+
+__device__ __forceinline__ WorkItem decode_work(int w, const GemmParams& p) {
+    WorkItem it;
+    if (p.tail_begin > 0 && w >= p.tail_begin) {
+        const int u = w - p.tail_begin;
+        it.slot = u / p.tail_slices;
+        const int slice = u - it.slot * p.tail_slices;
+        it.t = decode_tile(p.tail_begin + it.slot, p);  // splits == 1 here: work item number == tile number
+        it.t.split = slice;
+        it.kb0 = slice * p.tail_kb_per_slice;
+        it.kb1 = min(p.kb_total, it.kb0 + p.tail_kb_per_slice);
+    } else {
+        it.t = decode_tile(w, p);
+        it.slot = -1;
+        it.kb0 = it.t.split * p.kb_per_split;
+        it.kb1 = min(p.kb_total, it.kb0 + p.kb_per_split);
+    }
+    return it;
 }
 
 template <int OUT>

@@ -49,7 +49,7 @@ struct ExtraDstParam<true> {
 template <int KIND, int OUT, bool GATHER = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                         const __grid_constant__ CUtensorMap tmap_c,
+                         const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_ws,
                          const __grid_constant__ typename ExtraDstParam<GATHER>::type extra, const GemmParams p) {
     using L = PairSmem;
     constexpr int STAGES = kPairStages;
@@ -77,7 +77,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const uint32_t rank = ptx::cluster_ctarank();  // 0 = leader
     const int cluster_id = static_cast<int>(blockIdx.x) >> 1;
     const int n_clusters = static_cast<int>(gridDim.x) >> 1;
-    const int total_work = p.work_end > 0 ? p.work_end : p.m_tiles * p.n_tiles * p.splits;
+    const int total_work = p.total_work;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -95,6 +95,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         ptx::prefetch_tensormap(&tmap_a);
         ptx::prefetch_tensormap(&tmap_b);
         if (p.c_tma_ok) ptx::prefetch_tensormap(&tmap_c);
+        if (p.tail_begin > 0) ptx::prefetch_tensormap(&tmap_ws);
         if constexpr (GATHER)
             for (int d = 0; d < p.n_extra_dst; ++d) ptx::prefetch_tensormap(&extra.map[d]);
     }
@@ -118,9 +119,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (int w = cluster_id; ok && w < total_work; w += n_clusters) {
-                const TileCoord t = decode_tile(w, p);
-                const int kb0 = t.split * p.kb_per_split;
-                const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                const WorkItem item = decode_work(w, p);
+                const TileCoord t = item.t;
+                const int kb0 = item.kb0, kb1 = item.kb1;
                 const int row_a = (t.m_blk * 2 + static_cast<int>(rank)) * 128;
                 const int row_b = t.n_blk * BN + static_cast<int>(rank) * 128;
                 for (int kb = kb0; kb < kb1; ++kb) {
@@ -154,9 +155,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             uint32_t it = 0;
             bool ok = true;
             for (int w = cluster_id; ok && w < total_work; w += n_clusters, ++it) {
-                const TileCoord t = decode_tile(w, p);
-                const int kb0 = t.split * p.kb_per_split;
-                const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                const WorkItem item = decode_work(w, p);
+                const int kb0 = item.kb0, kb1 = item.kb1;
                 const uint32_t acc = it & 1u;
                 const uint32_t acc_phase = (it >> 1) & 1u;
                 if (!wait_bounded(bar_tempty + acc * 8, acc_phase ^ 1u, abort_flag, p.status, ROLE_MMA, -1)) break;
@@ -198,7 +198,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         uint32_t it = 0;
         uint32_t out_buf = 0;
         for (int w = cluster_id; w < total_work; w += n_clusters, ++it) {
-            const TileCoord t = decode_tile(w, p);
+            const WorkItem item = decode_work(w, p);
+            const TileCoord t = item.t;
             const uint32_t acc = it & 1u;
             const uint32_t acc_phase = (it >> 1) & 1u;
             if (!wait_bounded(bar_tfull + acc * 8, acc_phase, abort_flag, p.status, ROLE_EPILOGUE, w)) break;
@@ -208,24 +209,21 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             uint8_t* c_base = reinterpret_cast<uint8_t*>(p.C) +
                               static_cast<long long>(t.split) * p.split_stride * OutBytes<OUT>::value;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
-            // Where this tile goes: its place in C, or (compact_store: partial sums of a K slice of a last-wave
-            // tile) a whole 256 x 256 slot of the scratch array, where nothing needs clipping.
-            int row0 = (t.m_blk * 2 + static_cast<int>(rank)) * 128 + quad * 32;
-            int m_total = p.M, n_base = t.n_blk * BN, n_total = p.N;
-            if (p.compact_store) {
-                row0 = (t.slot * 2 + static_cast<int>(rank)) * 128 + quad * 32;
-                m_total = 0x7fffffff;
-                n_base = 0;
-                n_total = BN;
-            }
+            const int row0 = (t.m_blk * 2 + static_cast<int>(rank)) * 128 + quad * 32;
             const CUtensorMap* extra_maps = nullptr;
             int n_extra = 0;
             if constexpr (GATHER) {  // launched only with valid tensor maps for C and every further destination
                 extra_maps = &extra.map[0];
                 n_extra = p.n_extra_dst;
             }
-            if (GATHER || p.c_tma_ok) {
-                epilogue_tma<KIND, OUT, BN>(&tmap_c, t_addr, row0, m_total, n_base, n_total, t.split,
+            if (item.slot >= 0) {
+                // K slice of a last-wave tile: raw 32-bit partial sums into a whole scratch slot, nothing to clip
+                epilogue_tma<KIND, OUT_RAW32, BN>(&tmap_ws, t_addr,
+                                                  (item.slot * 2 + static_cast<int>(rank)) * 128 + quad * 32, 0x7fffffff,
+                                                  0, BN, t.split, smem_base + L::kOutOffset + (warp - 2) * 8192, lane,
+                                                  1.0f, out_buf);
+            } else if (GATHER || p.c_tma_ok) {
+                epilogue_tma<KIND, OUT, BN>(&tmap_c, t_addr, row0, p.M, t.n_blk * BN, p.N, t.split,
                                             smem_base + L::kOutOffset + (warp - 2) * 8192, lane, alpha, out_buf,
                                             extra_maps, n_extra);
             } else {
