@@ -37,7 +37,13 @@ typedef enum {
     QGEMM_DTYPE_INT8 = 2,
     QGEMM_DTYPE_FP8_E4M3 = 3, /* OCP e4m3 (max 448), the CUDA-side FP8 type of include/gpu_type.h:7 */
     QGEMM_DTYPE_FP32 = 4,
-    QGEMM_DTYPE_INT32 = 5
+    QGEMM_DTYPE_INT32 = 5,
+    QGEMM_DTYPE_INT4 = 6 /* signed 4-bit (-8..7), two per byte, element 2i in the low nibble of byte i: the "Int4" of
+                            the reference's roadmap (develop.md:9-12), which has no code for it. Input type of the
+                            GEMM entry points (A [M,K] and B [N,K], K-major only, K and the leading dimensions even
+                            and counted in elements) and output type of qgemm_quantize. The tensor cores have no
+                            4-bit integer kind: the operands are widened to int8 in scratch and multiplied by the
+                            int8 kernel, so results are the exact int32 sums, as for INT8. */
 } qgemm_dtype_t;
 
 /* How the K x N operand B is laid out in memory. */
@@ -125,9 +131,9 @@ int qgemm_transpose(const void* in, void* out, size_t rows, size_t cols, size_t 
 /*
  * Per-matrix quantisation, the step in front of qgemm_mix_gemm (the reference's roadmap names it,
  * develop.md:9-12, README.md:1, but has no kernel for it):
- *   *amax_out = max |in|;  *scale_out = amax / qmax (qmax = 448 for FP8_E4M3, 127 for INT8; 1 if amax == 0);
- *   out[r*ld_out + c] = round_to_nearest_even(in[r*ld_in + c] / scale), saturated to +-qmax.
- * in: FP32 or BF16 [rows, cols]; out: FP8_E4M3 or INT8, same shape. scale_out and amax_out are DEVICE pointers
+ *   *amax_out = max |in|;  *scale_out = amax / qmax (qmax = 448 for FP8_E4M3, 127 for INT8, 7 for INT4; 1 if
+ *   amax == 0);  out[r*ld_out + c] = round_to_nearest_even(in[r*ld_in + c] / scale), saturated to +-qmax.
+ * in: FP32 or BF16 [rows, cols]; out: FP8_E4M3, INT8 or INT4 (packed, cols and ld_out even), same shape. scale_out and amax_out are DEVICE pointers
  * to one float each (amax_out doubles as the reduction's scratch); pass scale_out as scale_a / scale_b of
  * qgemm_mix_gemm. Everything stays on `stream`; nothing is read back to the host.
  */

@@ -38,6 +38,7 @@ def lib() -> C.CDLL:
         _lib = C.CDLL(_LIB_PATH)
         _lib.oracle_quantize_e4m3.restype = C.c_float
         _lib.oracle_quantize_int8.restype = C.c_float
+        _lib.oracle_quantize_int4.restype = C.c_float
         _lib.oracle_num_threads.restype = C.c_int
     return _lib
 
@@ -91,6 +92,28 @@ def quantize_int8(x: np.ndarray):
     q = np.empty(x.shape, np.int8)
     scale = lib().oracle_quantize_int8(_p(x), _p(q), _sz(x.size))
     return q, float(scale)
+
+
+def unpack_int4(packed: np.ndarray) -> np.ndarray:
+    """Packed signed 4-bit [rows, cols/2] (two per byte, low nibble first) -> int8 [rows, cols]."""
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    out = np.empty(packed.shape[:-1] + (packed.shape[-1] * 2,), np.int8)
+    lib().oracle_unpack_int4(_p(packed), _p(out), _sz(out.size))
+    return out
+
+
+def quantize_int4(x: np.ndarray):
+    """Per-matrix int4 quantisation (scale = amax/7): returns (packed uint8 [rows, cols/2], scale)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    assert x.shape[-1] % 2 == 0
+    q = np.empty(x.shape[:-1] + (x.shape[-1] // 2,), np.uint8)
+    scale = lib().oracle_quantize_int4(_p(x), _p(q), _sz(x.size))
+    return q, float(scale)
+
+
+def gemm_i4(A_packed: np.ndarray, Bt_packed: np.ndarray) -> np.ndarray:
+    """Exact int32 product of packed int4 A [M, K/2] and K-major B [N, K/2]."""
+    return gemm_i8(unpack_int4(A_packed), unpack_int4(Bt_packed), True)
 
 
 def e4m3_decode(bits: np.ndarray) -> np.ndarray:

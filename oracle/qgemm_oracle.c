@@ -169,6 +169,34 @@ float oracle_quantize_int8(const float* in, int8_t* out, size_t n) {
     return scale;
 }
 
+/* Packed signed 4-bit values (the roadmap's "Int4", develop.md:9-12; the reference has no code for it): two per
+ * byte, element 2i in the low nibble of byte i, two's complement. */
+void oracle_unpack_int4(const uint8_t* in, int8_t* out, size_t n_elems) {
+    for (size_t i = 0; i < n_elems; ++i) {
+        int nib = (i & 1) ? (in[i >> 1] >> 4) : (in[i >> 1] & 0x0f);
+        out[i] = (int8_t)((nib ^ 8) - 8);
+    }
+}
+
+/* Per-matrix int4 quantisation: scale = amax / 7, q = clamp(round_to_nearest_even(x / scale), -7, 7), packed as
+ * above (n_elems even). Returns the scale. */
+float oracle_quantize_int4(const float* in, uint8_t* out_packed, size_t n_elems) {
+    float amax = 0.0f;
+    for (size_t i = 0; i < n_elems; ++i) { float a = fabsf(in[i]); if (a > amax) amax = a; }
+    float scale = amax > 0.0f ? amax / 7.0f : 1.0f;
+    for (size_t i = 0; i < n_elems; i += 2) {
+        int q[2];
+        for (int e = 0; e < 2; ++e) {
+            float r = rintf(in[i + e] / scale);
+            if (r > 7.0f) r = 7.0f;
+            if (r < -7.0f) r = -7.0f;
+            q[e] = (int)r;
+        }
+        out_packed[i >> 1] = (uint8_t)((q[0] & 0xf) | ((q[1] & 0xf) << 4));
+    }
+    return scale;
+}
+
 void oracle_e4m3_decode(const uint8_t* in, float* out, size_t n) {
     for (size_t i = 0; i < n; ++i) out[i] = oracle_e4m3_to_f32(in[i]);
 }

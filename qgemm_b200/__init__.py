@@ -18,7 +18,7 @@ LIB_PATH = os.path.join(HERE, "libqgemm.so")
 # qgemm_status_t
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_CUDA, ERR_WORKSPACE, ERR_DEVICE_TIMEOUT = range(7)
 # qgemm_dtype_t
-BF16, FP16, INT8, FP8_E4M3, FP32, INT32 = range(6)
+BF16, FP16, INT8, FP8_E4M3, FP32, INT32, INT4 = range(7)
 # qgemm_b_layout_t
 B_ROW_MAJOR, B_K_MAJOR = 0, 1
 
@@ -186,6 +186,53 @@ def fp8_mm(a, b, a_scale, b_scale, c) -> None:
 
 
 A_ROW_MAJOR, A_COL_MAJOR = 0, 1
+
+
+def int4_mm(a_packed, b_packed, a_scale, b_scale, c, tuning: Tuning | None = None) -> None:
+    """Int4 mixed GEMM (the "Int4" precision of the reference's roadmap, develop.md:9-12): ``a_packed`` [m, k/2] and
+    ``b_packed`` [n, k/2] are uint8 / int8 tensors holding two signed 4-bit values per byte (element 2i in the low
+    nibble), K-major. ``c`` [m, n]: int32 (exact sums, both scales None) or bf16 / fp16 / fp32 =
+    cast(a_scale * b_scale * sum). The operands are widened to int8 on the device and multiplied by the int8 kernel."""
+    torch = _torch()
+    for name, t in (("a_packed", a_packed), ("b_packed", b_packed), ("c", c)):
+        _require_cuda_2d(name, t)
+    if a_packed.element_size() != 1 or b_packed.element_size() != 1:
+        raise QgemmError(ERR_INVALID_ARG, "packed int4 operands are 1-byte tensors (two values per byte)")
+    M, Kh = a_packed.shape
+    N = b_packed.shape[0]
+    if b_packed.shape[1] != Kh or tuple(c.shape) != (M, N):
+        raise QgemmError(ERR_INVALID_ARG, "shape mismatch")
+    sa = a_scale.data_ptr() if a_scale is not None else None
+    sb = b_scale.data_ptr() if b_scale is not None else None
+    with torch.cuda.device(a_packed.device):
+        rc = lib().qgemm_gemm_ex(INT4, _dtype_code(c), B_K_MAJOR, a_packed.data_ptr(), 2 * max(a_packed.stride(0), Kh),
+                                 b_packed.data_ptr(), 2 * max(b_packed.stride(0), Kh), sa, sb, c.data_ptr(),
+                                 max(c.stride(0), N), M, N, 2 * Kh, C.byref(tuning) if tuning is not None else None,
+                                 _stream_ptr(a_packed))
+    _check(rc, "qgemm_gemm_ex (int4)")
+
+
+def quantize_int4(x, out=None):
+    """Per-matrix int4 quantisation of a float32 / bfloat16 CUDA matrix with an even number of columns. Returns
+    ``(packed, scale)``: ``packed`` uint8 [rows, cols/2] (two values per byte, low nibble first), ``scale`` =
+    amax / 7 as a 1-element float32 CUDA tensor."""
+    torch = _torch()
+    _require_cuda_2d("x", x)
+    rows, cols = x.shape
+    if cols % 2:
+        raise QgemmError(ERR_INVALID_ARG, "int4 packs two values per byte: the number of columns must be even")
+    if out is None:
+        out = torch.empty((rows, cols // 2), dtype=torch.uint8, device=x.device)
+    _require_cuda_2d("out", out)
+    if tuple(out.shape) != (rows, cols // 2) or out.element_size() != 1:
+        raise QgemmError(ERR_INVALID_ARG, "out must be a 1-byte tensor of shape [rows, cols/2]")
+    sc = torch.empty(2, dtype=torch.float32, device=x.device)  # [scale, amax]
+    with torch.cuda.device(x.device):
+        rc = lib().qgemm_quantize(_dtype_code(x), INT4, x.data_ptr(), max(x.stride(0), cols), out.data_ptr(),
+                                  2 * max(out.stride(0), cols // 2), sc.data_ptr(), sc.data_ptr() + 4, rows, cols,
+                                  _stream_ptr(x))
+    _check(rc, "qgemm_quantize (int4)")
+    return out, sc[:1]
 
 
 def quantize(x, out_dtype, out=None):

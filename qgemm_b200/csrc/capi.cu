@@ -30,6 +30,8 @@ struct DeviceState {
     int cc_major = 0;
     void* ws = nullptr;
     size_t ws_bytes = 0;
+    void* ws_i4 = nullptr;  // int4 operands widened to int8: [A | B]
+    size_t ws_i4_bytes = 0;
     int* status = nullptr;
 };
 
@@ -68,21 +70,23 @@ int get_state(DeviceState** out) {
     return QGEMM_OK;
 }
 
-int ensure_workspace(DeviceState& s, size_t bytes) {
-    if (bytes <= s.ws_bytes) return QGEMM_OK;
+int ensure_buffer(void** buf, size_t* cap, size_t bytes) {
+    if (bytes <= *cap) return QGEMM_OK;
     // Growing: earlier launches may still be using the old buffer.
     if (cudaDeviceSynchronize() != cudaSuccess) return QGEMM_ERR_CUDA;
-    if (s.ws != nullptr) cudaFree(s.ws);
-    s.ws = nullptr;
-    s.ws_bytes = 0;
+    if (*buf != nullptr) cudaFree(*buf);
+    *buf = nullptr;
+    *cap = 0;
     const size_t rounded = (bytes + ((size_t)1 << 20) - 1) & ~(((size_t)1 << 20) - 1);
-    if (cudaMalloc(&s.ws, rounded) != cudaSuccess) {
+    if (cudaMalloc(buf, rounded) != cudaSuccess) {
         (void)cudaGetLastError();
         return QGEMM_ERR_WORKSPACE;
     }
-    s.ws_bytes = rounded;
+    *cap = rounded;
     return QGEMM_OK;
 }
+
+int ensure_workspace(DeviceState& s, size_t bytes) { return ensure_buffer(&s.ws, &s.ws_bytes, bytes); }
 
 // ---------------------------------------------------------------- tensor maps
 struct MapKey {
@@ -570,6 +574,37 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     return QGEMM_OK;
 }
 
+// Packed int4 operands: widen both to int8 in their own scratch, then the int8 path (exact int32 sums).
+int int4_dispatch(int out_dtype, int b_layout, const void* A, size_t lda, const void* B, size_t ldb,
+                  const float* scale_a, const float* scale_b, void* C, size_t ldc, size_t M, size_t N, size_t K,
+                  const qgemm_tuning_t* tuning, cudaStream_t stream) {
+    if (b_layout != QGEMM_B_K_MAJOR) return QGEMM_ERR_UNSUPPORTED;  // two values share a byte along K only
+    if (M == 0 || N == 0) return QGEMM_OK;
+    if ((K & 1) || (lda & 1) || (ldb & 1)) return QGEMM_ERR_INVALID_ARG;
+    if (K > 0 && (A == nullptr || B == nullptr || lda < K || ldb < K)) return QGEMM_ERR_INVALID_ARG;
+    if (M > 0x7fffff00ull || N > 0x7fffff00ull || K > 0x7fffff00ull) return QGEMM_ERR_INVALID_ARG;
+    const size_t ldu = round_up(std::max<size_t>(K, 1), 16);
+    const size_t a_bytes = round_up(M * ldu, 256), b_bytes = round_up(N * ldu, 256);
+    void* buf = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        DeviceState* st = nullptr;
+        int rc = get_state(&st);
+        if (rc != QGEMM_OK) return rc;
+        rc = ensure_buffer(&st->ws_i4, &st->ws_i4_bytes, a_bytes + b_bytes);
+        if (rc != QGEMM_OK) return rc;
+        buf = st->ws_i4;
+    }
+    int8_t* a8 = static_cast<int8_t*>(buf);
+    int8_t* b8 = a8 + a_bytes;
+    int rc = unpack_int4_launch(A, lda, a8, ldu, M, K, stream);
+    if (rc != QGEMM_OK) return rc;
+    rc = unpack_int4_launch(B, ldb, b8, ldu, N, K, stream);
+    if (rc != QGEMM_OK) return rc;
+    return gemm_dispatch(QGEMM_DTYPE_INT8, out_dtype, QGEMM_B_K_MAJOR, a8, ldu, b8, ldu, scale_a, scale_b, C, ldc, M, N,
+                         K, tuning, stream);
+}
+
 int blockscale_dispatch(int out_dtype, int a_layout, int b_layout, const void* A, size_t lda, const void* B,
                         size_t ldb, const float* a_scale, const float* b_scale, void* C, size_t ldc, size_t M, size_t N,
                         size_t K, cudaStream_t stream) {
@@ -665,6 +700,9 @@ extern "C" {
 int qgemm_gemm_ex(int in_dtype, int out_dtype, int b_layout, const void* A, size_t lda, const void* B, size_t ldb,
                   const float* scale_a, const float* scale_b, void* C, size_t ldc, size_t M, size_t N, size_t K,
                   const qgemm_tuning_t* tuning, qgemm_stream_t stream) {
+    if (in_dtype == QGEMM_DTYPE_INT4)
+        return int4_dispatch(out_dtype, b_layout, A, lda, B, ldb, scale_a, scale_b, C, ldc, M, N, K, tuning,
+                             static_cast<cudaStream_t>(stream));
     return gemm_dispatch(in_dtype, out_dtype, b_layout, A, lda, B, ldb, scale_a, scale_b, C, ldc, M, N, K, tuning,
                          reinterpret_cast<cudaStream_t>(stream));
 }
@@ -673,10 +711,9 @@ int qgemm_gemm(int in_dtype, int out_dtype, int b_layout, const void* A, size_t 
                void* C, size_t ldc, size_t M, size_t N, size_t K, qgemm_stream_t stream) {
     const bool ok = ((in_dtype == QGEMM_DTYPE_BF16 || in_dtype == QGEMM_DTYPE_FP16) &&
                      (out_dtype == QGEMM_DTYPE_FP32 || out_dtype == QGEMM_DTYPE_BF16 || out_dtype == QGEMM_DTYPE_FP16)) ||
-                    (in_dtype == QGEMM_DTYPE_INT8 && out_dtype == QGEMM_DTYPE_INT32);
+                    ((in_dtype == QGEMM_DTYPE_INT8 || in_dtype == QGEMM_DTYPE_INT4) && out_dtype == QGEMM_DTYPE_INT32);
     if (!ok) return QGEMM_ERR_UNSUPPORTED;
-    return gemm_dispatch(in_dtype, out_dtype, b_layout, A, lda, B, ldb, nullptr, nullptr, C, ldc, M, N, K, nullptr,
-                         reinterpret_cast<cudaStream_t>(stream));
+    return qgemm_gemm_ex(in_dtype, out_dtype, b_layout, A, lda, B, ldb, nullptr, nullptr, C, ldc, M, N, K, nullptr, stream);
 }
 
 int qgemm_mix_gemm(int in_dtype, int out_dtype, int b_layout, const void* A, size_t lda, const void* B, size_t ldb,
@@ -684,8 +721,7 @@ int qgemm_mix_gemm(int in_dtype, int out_dtype, int b_layout, const void* A, siz
                    qgemm_stream_t stream) {
     if (out_dtype != QGEMM_DTYPE_FP32 && out_dtype != QGEMM_DTYPE_BF16 && out_dtype != QGEMM_DTYPE_FP16)
         return QGEMM_ERR_UNSUPPORTED;
-    return gemm_dispatch(in_dtype, out_dtype, b_layout, A, lda, B, ldb, scale_a, scale_b, C, ldc, M, N, K, nullptr,
-                         reinterpret_cast<cudaStream_t>(stream));
+    return qgemm_gemm_ex(in_dtype, out_dtype, b_layout, A, lda, B, ldb, scale_a, scale_b, C, ldc, M, N, K, nullptr, stream);
 }
 
 int qgemm_gemm_multi_dst(int in_dtype, int out_dtype, int b_layout, const void* A, size_t lda, const void* B,
@@ -743,9 +779,15 @@ size_t qgemm_workspace_query(int in_dtype, int b_layout, size_t M, size_t N, siz
             sms = g_dev[dev].sm_count;
     }
     Plan plan;
+    size_t widened = 0;
+    if (in_dtype == QGEMM_DTYPE_INT4) {  // both operands widened to int8, then the int8 path
+        const size_t ldu = round_up(K, 16);
+        widened = round_up(M * ldu, 256) + round_up(N * ldu, 256);
+        in_dtype = QGEMM_DTYPE_INT8;
+    }
     const int out = (in_dtype == QGEMM_DTYPE_INT8) ? QGEMM_DTYPE_INT32 : QGEMM_DTYPE_FP32;
     if (make_plan(in_dtype, out, b_layout, M, N, K, sms, tuning, &plan) != QGEMM_OK) return 0;
-    return plan.relayout_bytes + plan.partial_bytes;
+    return plan.relayout_bytes + plan.partial_bytes + widened;
 }
 
 int qgemm_device_status(int* out4) {
@@ -772,6 +814,7 @@ int qgemm_shutdown(void) {
         cudaSetDevice(d);
         cudaDeviceSynchronize();
         if (s.ws) cudaFree(s.ws);
+        if (s.ws_i4) cudaFree(s.ws_i4);
         if (s.status) cudaFree(s.status);
         s = DeviceState();
     }

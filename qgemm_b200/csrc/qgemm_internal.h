@@ -22,6 +22,11 @@ int splitk_reduce_launch(const void* partials, long long split_stride, long long
 int quantize_launch(int in_dtype, int out_dtype, const void* in, size_t ld_in, void* out, size_t ld_out,
                     float* scale_out, float* amax_out, size_t rows, size_t cols, cudaStream_t stream);
 
+// Widens packed signed 4-bit values (two per byte, low nibble first) to int8: out[r*ld_out + c] for c < cols.
+// ld_in_elems counts 4-bit elements (even); cols even (int4.cu).
+int unpack_int4_launch(const void* in, size_t ld_in_elems, void* out, size_t ld_out, size_t rows, size_t cols,
+                       cudaStream_t stream);
+
 // Frees the streams, events and device buffers of the host-operand path (host_gemm.cu).
 void host_path_shutdown();
 

@@ -1,7 +1,8 @@
 // Per-matrix quantisation pre-pass: the step in front of the mixed GEMM. The reference's roadmap lists
 // it (develop.md:9-12, README.md:1 "The input matrix will be quantized to 8 bits") but ships no kernel;
 // the semantics are those of C = (A o Q_A) x (B o Q_B) (README.md:5-7) with one coefficient per matrix:
-//   amax  = max |x|,  scale = amax / qmax  (qmax = 448 for FP8 e4m3, 127 for int8; scale = 1 if amax == 0)
+//   amax  = max |x|,  scale = amax / qmax  (qmax = 448 for FP8 e4m3, 127 for int8, 7 for packed int4; scale = 1
+//           if amax == 0)
 //   q     = round_to_nearest_even(x / scale), saturated to +-qmax,
 // so that x ~= scale * q and `scale` is what the GEMM epilogue multiplies back in.
 //
@@ -118,6 +119,32 @@ quantize_kernel(const TIn* __restrict__ in, long long ld_in, uint8_t* __restrict
     }
 }
 
+// INT4 output: one thread handles 8 consecutive elements of a row and writes 4 packed bytes.
+template <typename TIn>
+__global__ void __launch_bounds__(kQuantThreads)
+quantize_int4_kernel(const TIn* __restrict__ in, long long ld_in, uint8_t* __restrict__ out, long long ld_out_bytes,
+                     int rows, int cols, const float* __restrict__ amax_in, float* __restrict__ scale_out) {
+    ptx::pdl_launch_dependents();
+    ptx::pdl_wait();
+    const float amax = __ldg(amax_in);
+    const float scale = amax > 0.0f ? __fdiv_rn(amax, 7.0f) : 1.0f;
+    if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
+    const long long octs_per_row = (cols + 7) / 8;
+    const long long total = octs_per_row * rows;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long r = i / octs_per_row;
+        const int c = static_cast<int>(i - r * octs_per_row) * 8;
+        const TIn* src = in + r * ld_in + c;
+        uint8_t* dst = out + r * ld_out_bytes + c / 2;
+        for (int e = 0; e < 8 && c + e < cols; e += 2) {  // cols is even: pairs are whole
+            const float q0 = fminf(fmaxf(rintf(__fdiv_rn(load_as_float(src + e), scale)), -7.0f), 7.0f);
+            const float q1 = fminf(fmaxf(rintf(__fdiv_rn(load_as_float(src + e + 1), scale)), -7.0f), 7.0f);
+            dst[e >> 1] = static_cast<uint8_t>((static_cast<int>(q0) & 0xf) | ((static_cast<int>(q1) & 0xf) << 4));
+        }
+    }
+}
+
 __global__ void zero_float_kernel(float* p) {
     ptx::pdl_launch_dependents();
     ptx::pdl_wait();
@@ -126,13 +153,17 @@ __global__ void zero_float_kernel(float* p) {
 
 template <typename TIn>
 int quantize_typed(const TIn* in, size_t ld_in, void* out, size_t ld_out, float* scale_out, float* amax_out,
-                   size_t rows, size_t cols, bool fp8, int blocks, int vec_ok, cudaStream_t stream) {
+                   size_t rows, size_t cols, bool fp8, bool int4, int blocks, int vec_ok, cudaStream_t stream) {
     cudaError_t e = launch_pdl(zero_float_kernel, dim3(1), dim3(1), 0, stream, amax_out);
     if (e != cudaSuccess) return QGEMM_ERR_CUDA;
     e = launch_pdl(amax_kernel<TIn>, dim3(blocks), dim3(kQuantThreads), 0, stream, in, (long long)ld_in, (int)rows,
                    (int)cols, amax_out, vec_ok);
     if (e != cudaSuccess) return QGEMM_ERR_CUDA;
-    if (fp8)
+    if (int4)
+        e = launch_pdl(quantize_int4_kernel<TIn>, dim3(blocks), dim3(kQuantThreads), 0, stream, in, (long long)ld_in,
+                       static_cast<uint8_t*>(out), (long long)(ld_out / 2), (int)rows, (int)cols,
+                       static_cast<const float*>(amax_out), scale_out);
+    else if (fp8)
         e = launch_pdl(quantize_kernel<TIn, true>, dim3(blocks), dim3(kQuantThreads), 0, stream, in, (long long)ld_in,
                        static_cast<uint8_t*>(out), (long long)ld_out, (int)rows, (int)cols,
                        static_cast<const float*>(amax_out), scale_out, vec_ok);
@@ -148,7 +179,10 @@ int quantize_typed(const TIn* in, size_t ld_in, void* out, size_t ld_out, float*
 int quantize_launch(int in_dtype, int out_dtype, const void* in, size_t ld_in, void* out, size_t ld_out,
                     float* scale_out, float* amax_out, size_t rows, size_t cols, cudaStream_t stream) {
     if (in_dtype != QGEMM_DTYPE_FP32 && in_dtype != QGEMM_DTYPE_BF16) return QGEMM_ERR_UNSUPPORTED;
-    if (out_dtype != QGEMM_DTYPE_FP8_E4M3 && out_dtype != QGEMM_DTYPE_INT8) return QGEMM_ERR_UNSUPPORTED;
+    if (out_dtype != QGEMM_DTYPE_FP8_E4M3 && out_dtype != QGEMM_DTYPE_INT8 && out_dtype != QGEMM_DTYPE_INT4)
+        return QGEMM_ERR_UNSUPPORTED;
+    const bool int4 = out_dtype == QGEMM_DTYPE_INT4;
+    if (int4 && ((cols & 1) || (ld_out & 1))) return QGEMM_ERR_INVALID_ARG;
     if (scale_out == nullptr || amax_out == nullptr) return QGEMM_ERR_INVALID_ARG;
     if (rows > 0x7fffffffull || cols > 0x7fffffffull) return QGEMM_ERR_INVALID_ARG;
     if (rows > 0 && cols > 0 && (in == nullptr || out == nullptr || ld_in < cols || ld_out < cols))
@@ -165,9 +199,9 @@ int quantize_launch(int in_dtype, int out_dtype, const void* in, size_t ld_in, v
     const bool fp8 = out_dtype == QGEMM_DTYPE_FP8_E4M3;
     if (in_dtype == QGEMM_DTYPE_FP32)
         return quantize_typed(static_cast<const float*>(in), ld_in, out, ld_out, scale_out, amax_out, rows, cols, fp8,
-                              static_cast<int>(blocks), vec_ok, stream);
+                              int4, static_cast<int>(blocks), vec_ok, stream);
     return quantize_typed(static_cast<const uint16_t*>(in), ld_in, out, ld_out, scale_out, amax_out, rows, cols, fp8,
-                          static_cast<int>(blocks), vec_ok, stream);
+                          int4, static_cast<int>(blocks), vec_ok, stream);
 }
 
 }  // namespace qgemm

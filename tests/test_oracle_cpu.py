@@ -192,3 +192,17 @@ def test_reference_variants_agree(golden):
 
 def test_oracle_transpose_matches_reference_kernel(oracle, golden):
     assert np.array_equal(oracle.transpose(golden["t_in_bits"]), golden["t_out_bits"])
+
+
+def test_int4_pack_unpack_and_quantise():
+    """Packed signed 4-bit: low nibble first, two's complement; quantisation to +-7 with scale amax/7."""
+    from oracle import oracle as o
+    packed = np.array([[0x10, 0xF8, 0x7F, 0x98]], dtype=np.uint8)
+    assert o.unpack_int4(packed).tolist() == [[0, 1, -8, -1, -1, 7, -8, -7]]
+    x = np.array([[7.0, -7.0, 3.4, 3.6, -0.5, 0.5, 1.5, 2.5]], dtype=np.float32)  # scale = 1: ties go to even
+    q, scale = o.quantize_int4(x)
+    assert scale == 1.0
+    assert o.unpack_int4(q).tolist() == [[7, -7, 3, 4, 0, 0, 2, 2]]
+    a = np.array([[0x21, 0x43]], dtype=np.uint8)   # 1 2 3 4
+    b = np.array([[0xFF, 0x7F], [0x01, 0x00]], dtype=np.uint8)  # -1 -1 -1 7 ; 1 0 0 0
+    assert o.gemm_i4(a, b).tolist() == [[-1 - 2 - 3 + 28, 1]]
