@@ -25,18 +25,16 @@ __device__ __forceinline__ void widen8(uint32_t w, uint32_t& lo4, uint32_t& hi4)
     hi4 = __byte_perm(ls, hs, 0x7362);  // e4 e5 e6 e7
 }
 
-// One thread widens 32 elements (16 packed bytes) of a row; chunks_per_row = ceil(cols / 32).
+// One thread widens 32 elements (16 packed bytes) of a row: blockIdx.x walks along the row, blockIdx.y strides over
+// the rows (no per-thread division).
 __global__ void __launch_bounds__(kUnpackThreads)
 unpack_int4_kernel(const uint8_t* __restrict__ in, long long ld_in_bytes, int8_t* __restrict__ out, long long ld_out,
                    int rows, int cols, int vec_ok) {
     ptx::pdl_launch_dependents();
     ptx::pdl_wait();
-    const long long chunks_per_row = (cols + 31) / 32;
-    const long long total = chunks_per_row * rows;
-    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const long long r = i / chunks_per_row;
-        const int c = static_cast<int>(i - r * chunks_per_row) * 32;
+    const int c = (static_cast<int>(blockIdx.x) * kUnpackThreads + static_cast<int>(threadIdx.x)) * 32;
+    if (c >= cols) return;
+    for (long long r = blockIdx.y; r < rows; r += gridDim.y) {
         const uint8_t* src = in + r * ld_in_bytes + c / 2;
         int8_t* dst = out + r * ld_out + c;
         if (vec_ok && c + 32 <= cols) {
@@ -69,14 +67,10 @@ int unpack_int4_launch(const void* in, size_t ld_in_elems, void* out, size_t ld_
     const size_t ld_in_bytes = ld_in_elems / 2;
     const int vec_ok = (reinterpret_cast<uintptr_t>(in) % 16 == 0) && (ld_in_bytes % 16 == 0) &&
                        (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (ld_out % 16 == 0);
-    const size_t chunks = ((cols + 31) / 32) * rows;
-    int dev = 0, sms = 148;
-    if (cudaGetDevice(&dev) != cudaSuccess) return QGEMM_ERR_CUDA;
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return QGEMM_ERR_CUDA;
-    size_t blocks = (chunks + kUnpackThreads - 1) / kUnpackThreads;
-    blocks = std::max<size_t>(1, std::min<size_t>(blocks, static_cast<size_t>(sms) * 8));
+    const unsigned blocks_x = static_cast<unsigned>(((cols + 31) / 32 + kUnpackThreads - 1) / kUnpackThreads);
+    const unsigned blocks_y = static_cast<unsigned>(std::min<size_t>(rows, 65535));
     const cudaError_t e =
-        launch_pdl(unpack_int4_kernel, dim3(static_cast<unsigned>(blocks)), dim3(kUnpackThreads), 0, stream,
+        launch_pdl(unpack_int4_kernel, dim3(blocks_x, blocks_y), dim3(kUnpackThreads), 0, stream,
                    static_cast<const uint8_t*>(in), static_cast<long long>(ld_in_bytes), static_cast<int8_t*>(out),
                    static_cast<long long>(ld_out), static_cast<int>(rows), static_cast<int>(cols), vec_ok);
     return e == cudaSuccess ? QGEMM_OK : QGEMM_ERR_CUDA;

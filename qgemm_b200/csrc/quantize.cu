@@ -12,6 +12,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
+#include <type_traits>
+
 #include "gemm_launch.cuh"
 #include "qgemm_internal.h"
 
@@ -27,33 +29,70 @@ __device__ __forceinline__ float load_as_float(const TIn* p) {
     else return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(p));
 }
 
-// One thread handles 4 consecutive elements of a row; quads_per_row = ceil(cols / 4).
+// Four consecutive elements of a row as floats (one 16-byte or 8-byte load).
+template <typename TIn>
+struct Quad {
+    using Raw = typename std::conditional<sizeof(TIn) == 4, float4, uint2>::type;
+    static __device__ __forceinline__ Raw load(const TIn* p) { return __ldg(reinterpret_cast<const Raw*>(p)); }
+    static __device__ __forceinline__ void to_float(const Raw& v, float (&x)[4]) {
+        if constexpr (sizeof(TIn) == 4) {
+            x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+        } else {
+            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
+            const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+            x[0] = __low2float(a); x[1] = __high2float(a); x[2] = __low2float(b); x[3] = __high2float(b);
+        }
+    }
+};
+
+// Loads in flight per thread: both passes are plain streams, and with one small load per loop iteration the
+// bytes in flight per SM (2048 threads x 8 or 16 bytes) are too few to cover HBM latency at full bandwidth.
+template <typename TIn>
+struct Unroll {
+    static constexpr int value = sizeof(TIn) == 4 ? 4 : 8;
+};
+
+// Work decomposition of both passes: a block takes one *chunk* of a row at a time -- kQuantThreads x U quads of 4
+// elements, thread t the quads t, t + kQuantThreads, ... of the chunk, so that every load instruction of a warp covers
+// 512 (or 256) contiguous bytes and a thread has U loads in flight. Row and chunk come from one division per block and
+// chunk, not one per element (a 64-bit division costs more than the rest of the per-element work together).
 template <typename TIn>
 __global__ void __launch_bounds__(kQuantThreads)
 amax_kernel(const TIn* __restrict__ in, long long ld, int rows, int cols, float* __restrict__ amax_out, int vec_ok) {
     ptx::pdl_launch_dependents();
     ptx::pdl_wait();
-    const long long quads_per_row = (cols + 3) / 4;
-    const long long total = quads_per_row * rows;
+    constexpr int U = Unroll<TIn>::value;
+    constexpr int kChunkQuads = kQuantThreads * U;
+    const int quads_per_row = (cols + 3) / 4;
+    const int chunks_per_row = (quads_per_row + kChunkQuads - 1) / kChunkQuads;
+    const long long items = static_cast<long long>(chunks_per_row) * rows;
     float m = 0.0f;
-    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const long long r = i / quads_per_row;
-        const int c = static_cast<int>(i - r * quads_per_row) * 4;
-        const TIn* src = in + r * ld + c;
-        if (vec_ok && c + 4 <= cols) {
-            if constexpr (sizeof(TIn) == 4) {
-                const float4 v = __ldg(reinterpret_cast<const float4*>(src));
-                m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-            } else {
-                const uint2 v = __ldg(reinterpret_cast<const uint2*>(src));
-                const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
-                const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
-                m = fmaxf(m, fmaxf(fmaxf(fabsf(__low2float(a)), fabsf(__high2float(a))),
-                                   fmaxf(fabsf(__low2float(b)), fabsf(__high2float(b)))));
+    for (long long item = blockIdx.x; item < items; item += gridDim.x) {
+        const long long r = item / chunks_per_row;
+        const int q0 = static_cast<int>(item - r * chunks_per_row) * kChunkQuads + static_cast<int>(threadIdx.x);
+        const TIn* row = in + r * ld;
+        if (vec_ok && (q0 + (U - 1) * kQuantThreads) * 4 + 4 <= cols) {
+            typename Quad<TIn>::Raw v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) v[u] = Quad<TIn>::load(row + (q0 + u * kQuantThreads) * 4);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                float x[4];
+                Quad<TIn>::to_float(v[u], x);
+                m = fmaxf(m, fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3]))));
             }
-        } else {
-            for (int e = 0; e < 4 && c + e < cols; ++e) m = fmaxf(m, fabsf(load_as_float(src + e)));
+            continue;
+        }
+        for (int u = 0; u < U; ++u) {
+            const int c = (q0 + u * kQuantThreads) * 4;
+            if (c >= cols) break;
+            if (vec_ok && c + 4 <= cols) {
+                float x[4];
+                Quad<TIn>::to_float(Quad<TIn>::load(row + c), x);
+                m = fmaxf(m, fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3]))));
+            } else {
+                for (int e = 0; e < 4 && c + e < cols; ++e) m = fmaxf(m, fabsf(load_as_float(row + c + e)));
+            }
         }
     }
 #pragma unroll
@@ -75,8 +114,25 @@ __device__ __forceinline__ uint8_t quantize_one(float x, float scale) {
     if constexpr (FP8) {
         return static_cast<uint8_t>(__nv_cvt_float_to_fp8(q, __NV_SATFINITE, __NV_E4M3));
     } else {
-        const float r = fminf(fmaxf(rintf(q), -127.0f), 127.0f);
-        return static_cast<uint8_t>(static_cast<int8_t>(static_cast<int>(r)));
+        // round to nearest even straight to an integer (what rintf + cast does), then saturate to +-127
+        const int r = max(-127, min(127, __float2int_rn(q)));
+        return static_cast<uint8_t>(r & 0xff);
+    }
+}
+
+// Four quantised values packed into one 32-bit word.
+template <bool FP8>
+__device__ __forceinline__ uint32_t quantize_quad(const float (&x)[4], float scale) {
+    if constexpr (FP8) {
+        // two values per conversion instruction (same rounding and saturation as the scalar form)
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(x[0], scale), __fdiv_rn(x[1], scale)),
+                                                     __NV_SATFINITE, __NV_E4M3);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(x[2], scale), __fdiv_rn(x[3], scale)),
+                                                     __NV_SATFINITE, __NV_E4M3);
+        return lo | (hi << 16);
+    } else {
+        return quantize_one<FP8>(x[0], scale) | (quantize_one<FP8>(x[1], scale) << 8) |
+               (quantize_one<FP8>(x[2], scale) << 16) | (static_cast<uint32_t>(quantize_one<FP8>(x[3], scale)) << 24);
     }
 }
 
@@ -86,35 +142,43 @@ quantize_kernel(const TIn* __restrict__ in, long long ld_in, uint8_t* __restrict
                 int cols, const float* __restrict__ amax_in, float* __restrict__ scale_out, int vec_ok) {
     ptx::pdl_launch_dependents();
     ptx::pdl_wait();
+    constexpr int U = Unroll<TIn>::value;
+    constexpr int kChunkQuads = kQuantThreads * U;
     const float amax = __ldg(amax_in);
     const float qmax = FP8 ? 448.0f : 127.0f;
     const float scale = amax > 0.0f ? __fdiv_rn(amax, qmax) : 1.0f;
     if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
-    const long long quads_per_row = (cols + 3) / 4;
-    const long long total = quads_per_row * rows;
-    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const long long r = i / quads_per_row;
-        const int c = static_cast<int>(i - r * quads_per_row) * 4;
-        const TIn* src = in + r * ld_in + c;
-        uint8_t* dst = out + r * ld_out + c;
-        if (vec_ok && c + 4 <= cols) {
-            float x[4];
-            if constexpr (sizeof(TIn) == 4) {
-                const float4 v = __ldg(reinterpret_cast<const float4*>(src));
-                x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
-            } else {
-                const uint2 v = __ldg(reinterpret_cast<const uint2*>(src));
-                const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
-                const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
-                x[0] = __low2float(a); x[1] = __high2float(a); x[2] = __low2float(b); x[3] = __high2float(b);
+    const int quads_per_row = (cols + 3) / 4;
+    const int chunks_per_row = (quads_per_row + kChunkQuads - 1) / kChunkQuads;
+    const long long items = static_cast<long long>(chunks_per_row) * rows;
+    for (long long item = blockIdx.x; item < items; item += gridDim.x) {
+        const long long r = item / chunks_per_row;
+        const int q0 = static_cast<int>(item - r * chunks_per_row) * kChunkQuads + static_cast<int>(threadIdx.x);
+        const TIn* src_row = in + r * ld_in;
+        uint8_t* dst_row = out + r * ld_out;
+        if (vec_ok && (q0 + (U - 1) * kQuantThreads) * 4 + 4 <= cols) {
+            typename Quad<TIn>::Raw v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) v[u] = Quad<TIn>::load(src_row + (q0 + u * kQuantThreads) * 4);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                float x[4];
+                Quad<TIn>::to_float(v[u], x);
+                *reinterpret_cast<uint32_t*>(dst_row + (q0 + u * kQuantThreads) * 4) = quantize_quad<FP8>(x, scale);
             }
-            const uint32_t packed = quantize_one<FP8>(x[0], scale) | (quantize_one<FP8>(x[1], scale) << 8) |
-                                    (quantize_one<FP8>(x[2], scale) << 16) |
-                                    (static_cast<uint32_t>(quantize_one<FP8>(x[3], scale)) << 24);
-            *reinterpret_cast<uint32_t*>(dst) = packed;
-        } else {
-            for (int e = 0; e < 4 && c + e < cols; ++e) dst[e] = quantize_one<FP8>(load_as_float(src + e), scale);
+            continue;
+        }
+        for (int u = 0; u < U; ++u) {
+            const int c = (q0 + u * kQuantThreads) * 4;
+            if (c >= cols) break;
+            if (vec_ok && c + 4 <= cols) {
+                float x[4];
+                Quad<TIn>::to_float(Quad<TIn>::load(src_row + c), x);
+                *reinterpret_cast<uint32_t*>(dst_row + c) = quantize_quad<FP8>(x, scale);
+            } else {
+                for (int e = 0; e < 4 && c + e < cols; ++e)
+                    dst_row[c + e] = quantize_one<FP8>(load_as_float(src_row + c + e), scale);
+            }
         }
     }
 }
@@ -190,7 +254,9 @@ int quantize_launch(int in_dtype, int out_dtype, const void* in, size_t ld_in, v
     const size_t es = in_dtype == QGEMM_DTYPE_FP32 ? 4 : 2;
     const int vec_ok = (reinterpret_cast<uintptr_t>(in) % (4 * es) == 0) && (ld_in % 4 == 0) &&
                        (reinterpret_cast<uintptr_t>(out) % 4 == 0) && (ld_out % 4 == 0);
-    const size_t quads = ((cols + 3) / 4) * rows;
+    // blocks walk (row, chunk) items: see amax_kernel
+    const size_t chunk_quads = static_cast<size_t>(kQuantThreads) * (es == 4 ? 4 : 8);
+    const size_t quads = (((cols + 3) / 4 + chunk_quads - 1) / chunk_quads) * rows * kQuantThreads;
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) != cudaSuccess) return QGEMM_ERR_CUDA;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return QGEMM_ERR_CUDA;

@@ -5,6 +5,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <algorithm>
+
 #include "gemm_launch.cuh"
 #include "qgemm_internal.h"
 
@@ -102,14 +104,12 @@ splitk_reduce_kernel(const uint32_t* __restrict__ partials, long long split_stri
                      const float* __restrict__ scale_a, const float* __restrict__ scale_b, int c_vec_ok) {
     ptx::pdl_launch_dependents();
     ptx::pdl_wait();
-    const long long quads_per_row = ldw >> 2;
-    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (idx >= quads_per_row * M) return;
-    const long long row = idx / quads_per_row;
-    const int col = static_cast<int>(idx - row * quads_per_row) * 4;
+    // blockIdx.x walks along a row (four columns per thread), blockIdx.y strides over the rows: no per-thread division
+    const int col = (static_cast<int>(blockIdx.x) * static_cast<int>(blockDim.x) + static_cast<int>(threadIdx.x)) * 4;
     if (col >= N) return;
-    reduce_quad<ACC_INT>(partials + row * ldw + col, split_stride, splits, C, ldc, row, col, N, out_kind, scale_a,
-                         scale_b, c_vec_ok);
+    for (long long row = blockIdx.y; row < M; row += gridDim.y)
+        reduce_quad<ACC_INT>(partials + row * ldw + col, split_stride, splits, C, ldc, row, col, N, out_kind, scale_a,
+                             scale_b, c_vec_ok);
 }
 
 // The same sum for tiles whose K slices were stored as compact 256 x 256 slots ([splits][slots * 256][256]):
@@ -161,19 +161,19 @@ int splitk_reduce_launch(const void* partials, long long split_stride, long long
                          const float* scale_b, cudaStream_t stream) {
     const int out_bytes = (out_kind == OUT_BF16 || out_kind == OUT_F16) ? 2 : 4;
     const int c_vec_ok = (reinterpret_cast<uintptr_t>(C) % 16 == 0) && ((ldc * out_bytes) % 16 == 0);
-    const long long total = (ldw >> 2) * M;
+    if (M <= 0 || N <= 0) return QGEMM_OK;
     const int threads = 256;
-    const long long blocks = (total + threads - 1) / threads;
-    if (blocks <= 0) return QGEMM_OK;
-    if (blocks > 0x7fffffffLL) return QGEMM_ERR_UNSUPPORTED;
+    const unsigned blocks_x = static_cast<unsigned>(((N + 3) / 4 + threads - 1) / threads);
+    const unsigned blocks_y = static_cast<unsigned>(std::min<long long>(M, 65535));
+    const dim3 grid(blocks_x, blocks_y);
     const uint32_t* p = reinterpret_cast<const uint32_t*>(partials);
     cudaError_t e;
     if (acc_is_int)
-        e = launch_pdl(splitk_reduce_kernel<true>, dim3(static_cast<unsigned>(blocks)), dim3(threads), 0, stream, p,
-                       split_stride, ldw, splits, C, ldc, M, N, out_kind, scale_a, scale_b, c_vec_ok);
+        e = launch_pdl(splitk_reduce_kernel<true>, grid, dim3(threads), 0, stream, p, split_stride, ldw, splits, C, ldc, M,
+                       N, out_kind, scale_a, scale_b, c_vec_ok);
     else
-        e = launch_pdl(splitk_reduce_kernel<false>, dim3(static_cast<unsigned>(blocks)), dim3(threads), 0, stream, p,
-                       split_stride, ldw, splits, C, ldc, M, N, out_kind, scale_a, scale_b, c_vec_ok);
+        e = launch_pdl(splitk_reduce_kernel<false>, grid, dim3(threads), 0, stream, p, split_stride, ldw, splits, C, ldc, M,
+                       N, out_kind, scale_a, scale_b, c_vec_ok);
     if (e != cudaSuccess) return QGEMM_ERR_CUDA;
     return cudaGetLastError() == cudaSuccess ? QGEMM_OK : QGEMM_ERR_CUDA;
 }
