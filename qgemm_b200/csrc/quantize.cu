@@ -193,18 +193,16 @@ quantize_int4_kernel(const TIn* __restrict__ in, long long ld_in, uint8_t* __res
     const float amax = __ldg(amax_in);
     const float scale = amax > 0.0f ? __fdiv_rn(amax, 7.0f) : 1.0f;
     if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
-    const long long octs_per_row = (cols + 7) / 8;
-    const long long total = octs_per_row * rows;
-    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const long long r = i / octs_per_row;
-        const int c = static_cast<int>(i - r * octs_per_row) * 8;
+    // blockIdx.x walks along the row (8 elements per thread), blockIdx.y strides over the rows
+    const int c = (static_cast<int>(blockIdx.x) * kQuantThreads + static_cast<int>(threadIdx.x)) * 8;
+    if (c >= cols) return;
+    for (long long r = blockIdx.y; r < rows; r += gridDim.y) {
         const TIn* src = in + r * ld_in + c;
         uint8_t* dst = out + r * ld_out_bytes + c / 2;
         for (int e = 0; e < 8 && c + e < cols; e += 2) {  // cols is even: pairs are whole
-            const float q0 = fminf(fmaxf(rintf(__fdiv_rn(load_as_float(src + e), scale)), -7.0f), 7.0f);
-            const float q1 = fminf(fmaxf(rintf(__fdiv_rn(load_as_float(src + e + 1), scale)), -7.0f), 7.0f);
-            dst[e >> 1] = static_cast<uint8_t>((static_cast<int>(q0) & 0xf) | ((static_cast<int>(q1) & 0xf) << 4));
+            const int q0 = max(-7, min(7, __float2int_rn(__fdiv_rn(load_as_float(src + e), scale))));
+            const int q1 = max(-7, min(7, __float2int_rn(__fdiv_rn(load_as_float(src + e + 1), scale))));
+            dst[e >> 1] = static_cast<uint8_t>((q0 & 0xf) | ((q1 & 0xf) << 4));
         }
     }
 }
@@ -224,7 +222,10 @@ int quantize_typed(const TIn* in, size_t ld_in, void* out, size_t ld_out, float*
                    (int)cols, amax_out, vec_ok);
     if (e != cudaSuccess) return QGEMM_ERR_CUDA;
     if (int4)
-        e = launch_pdl(quantize_int4_kernel<TIn>, dim3(blocks), dim3(kQuantThreads), 0, stream, in, (long long)ld_in,
+        e = launch_pdl(quantize_int4_kernel<TIn>,
+                       dim3(static_cast<unsigned>(((cols + 7) / 8 + kQuantThreads - 1) / kQuantThreads),
+                            static_cast<unsigned>(rows < 65535 ? rows : 65535)),
+                       dim3(kQuantThreads), 0, stream, in, (long long)ld_in,
                        static_cast<uint8_t*>(out), (long long)(ld_out / 2), (int)rows, (int)cols,
                        static_cast<const float*>(amax_out), scale_out);
     else if (fp8)
