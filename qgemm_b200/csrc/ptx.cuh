@@ -41,9 +41,6 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
-__device__ __forceinline__ void mbar_inval(uint32_t bar) {
-    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
 __device__ __forceinline__ void fence_barrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
@@ -85,24 +82,9 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
         : "memory");
 }
 
-// Same with an L2 eviction-priority hint.
-__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst_smem, const CUtensorMap* tmap, uint32_t bar, int x,
-                                                 int y, uint64_t policy) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-        " [%0], [%1, {%3, %4}], [%2], %5;"
-        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "l"(policy)
-        : "memory");
-}
-
-// 2-D tiled store shared -> global (bulk async-group completion). Elements outside the tensor are
-// clipped by the hardware. Never issued with a negative coordinate.
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, uint32_t src_smem, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                 ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src_smem), "r"(x), "r"(y)
-                 : "memory");
-}
-// 3-D form: z selects a slab (split-K partial sums are [split][M][N]); rows beyond M are clipped per slab.
+// 3-D tiled store shared -> global (bulk async-group completion); z selects a slab (split-K partial sums are
+// [split][M][N]). Elements outside the tensor are clipped by the hardware, rows beyond M per slab. Never issued
+// with a negative coordinate.
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* tmap, uint32_t src_smem, int x, int y, int z) {
     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
                  ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src_smem), "r"(x), "r"(y), "r"(z)
@@ -226,10 +208,6 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t nthreads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
 
 // ---------------------------------------------------------------- CTA pairs (cta_group::2)
 // Two CTAs of a 2-CTA cluster cooperate on one MMA: the even-ranked ("leader") CTA issues it, each
