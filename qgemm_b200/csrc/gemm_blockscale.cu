@@ -14,6 +14,10 @@
 // cores already work on the next blocks in the other partials -- the rescale in CUDA cores that the
 // reference does per K tile in registers. After the last block the registers are rounded and leave
 // through the same swizzled-staging + TMA-store path as the plain GEMM.
+//
+// Barriers: full[stage] (TMA bytes landed), done[blk % 12] (one tcgen05.commit per K block: the block has been
+// multiplied, which both frees its stage and publishes its partial), pempty[partial] (all eight rescale warps
+// have the partial in registers). The producer, not the MMA issuer, waits for pempty before it loads a block.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -27,6 +31,7 @@ namespace {
 constexpr int kBsBN = 128;
 constexpr int kBsStages = 6;
 constexpr int kBsPartials = 4;                           // partial accumulators in flight (4 x 128 = all 512 columns)
+constexpr int kBsDone = 12;                              // "K block multiplied" barriers: lcm(stages, partials)
 constexpr int kBsEpilogueWarps = 8;                      // two warps per tensor-memory lane quadrant
 constexpr int kBsThreads = 32 * (2 + kBsEpilogueWarps);  // producer, MMA issuer, 8 rescale warps
 constexpr int kBsColsPerWarp = kBsBN / 2;                // each of the two warps of a quadrant takes 64 columns
@@ -36,8 +41,8 @@ struct BsSmem {
     static constexpr int kBStage = kBsBN * 128;
     static constexpr int kTiles = kBsStages * (kAStage + kBStage);
     static constexpr int kOutOffset = kTiles;
-    static constexpr int kBarOffset = kTiles + kBsEpilogueWarps * 4096;  // full[S], empty[S], pfull[P], pempty[P]
-    static constexpr int kMiscOffset = kBarOffset + (2 * kBsStages + 2 * kBsPartials) * 8;
+    static constexpr int kBarOffset = kTiles + kBsEpilogueWarps * 4096;  // full[S], done[12], pempty[P]
+    static constexpr int kMiscOffset = kBarOffset + (kBsStages + kBsDone + kBsPartials) * 8;
     static constexpr int kTotal = kMiscOffset + 16;
     static constexpr int kDynamicBytes = kTotal + 1024;
 };
@@ -74,10 +79,15 @@ fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const uint32_t smem_base = raw_addr + pad;
     const uint32_t smem_a = smem_base;
     const uint32_t smem_b = smem_base + STAGES * L::kAStage;
+    // One tcgen05.commit per K block: done[i] (i = running K-block count mod 12) says "that block has been multiplied",
+    // which frees its shared-memory stage for the producer and publishes its partial to the rescale warps at once.
+    // The issuing thread is the narrow point of this kernel -- with 128 x 128 x 32 MMAs a K block is 256 cycles of
+    // tensor work, and every wait and commit on that thread costs about as much as an MMA -- so the wait for a free
+    // partial is the producer's (a load is only issued once the partial its block will be multiplied into has been
+    // handed back), and full[stage] then stands for both.
     const uint32_t bar_full = smem_base + L::kBarOffset;
-    const uint32_t bar_empty = bar_full + STAGES * 8;
-    const uint32_t bar_pfull = bar_empty + STAGES * 8;
-    const uint32_t bar_pempty = bar_pfull + kBsPartials * 8;
+    const uint32_t bar_done = bar_full + STAGES * 8;
+    const uint32_t bar_pempty = bar_done + kBsDone * 8;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kMiscOffset);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 4);
 
@@ -86,14 +96,9 @@ fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const int total_work = p.m_tiles * p.n_tiles;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            ptx::mbar_init(bar_full + s * 8, 1);
-            ptx::mbar_init(bar_empty + s * 8, 1);
-        }
-        for (int a = 0; a < kBsPartials; ++a) {
-            ptx::mbar_init(bar_pfull + a * 8, 1);
-            ptx::mbar_init(bar_pempty + a * 8, kBsEpilogueWarps);
-        }
+        for (int s = 0; s < STAGES; ++s) ptx::mbar_init(bar_full + s * 8, 1);
+        for (int d = 0; d < kBsDone; ++d) ptx::mbar_init(bar_done + d * 8, 1);
+        for (int a = 0; a < kBsPartials; ++a) ptx::mbar_init(bar_pempty + a * 8, kBsEpilogueWarps);
         *abort_flag = 0;
         ptx::fence_barrier_init();
     }
@@ -116,24 +121,31 @@ fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (ptx::elect_one()) {
-            uint32_t stage = 0, phase = 0;
+            uint32_t stage = 0;
+            uint32_t blk = 0;               // running K-block count
+            uint32_t prev = kBsDone - STAGES, prev_phase = 1;  // done[] slot of block blk - STAGES and its parity
             bool ok = true;
             for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
                 int m_blk, n_blk;
                 bs_decode(w, p, m_blk, n_blk);
-                for (int kb = 0; kb < p.kb_total; ++kb) {
-                    if (!wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, p.status, ROLE_PRODUCER, kb)) {
+                for (int kb = 0; kb < p.kb_total; ++kb, ++blk) {
+                    // the stage is free once the block that used it last (blk - STAGES) has been multiplied, and the
+                    // partial this block goes into (blk % P) once the rescale warps have drained block blk - P
+                    if (!wait_bounded(bar_done + prev * 8, prev_phase, abort_flag, p.status, ROLE_PRODUCER, kb) ||
+                        !wait_bounded(bar_pempty + (blk & PMASK) * 8, ((blk >> PSHIFT) & 1u) ^ 1u, abort_flag, p.status,
+                                      ROLE_PRODUCER, kb)) {
                         ok = false;
                         break;
+                    }
+                    if (++prev == kBsDone) {
+                        prev = 0;
+                        prev_phase ^= 1u;
                     }
                     const uint32_t full = bar_full + stage * 8;
                     ptx::mbar_arrive_expect_tx(full, L::kAStage + L::kBStage);
                     ptx::tma_load_2d(smem_a + stage * L::kAStage, &tmap_a, full, kb * BK, m_blk * kBM);
                     ptx::tma_load_2d(smem_b + stage * L::kBStage, &tmap_b, full, kb * BK, n_blk * BN);
-                    if (++stage == STAGES) {
-                        stage = 0;
-                        phase ^= 1u;
-                    }
+                    if (++stage == STAGES) stage = 0;
                 }
             }
         }
@@ -141,13 +153,13 @@ fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         // ------------------------------------------------------------ MMA issuer: one partial per K block
         if (ptx::elect_one()) {
             uint32_t stage = 0, phase = 0;
-            uint32_t blk = 0;  // running K-block count: partial buffer blk % P, phase (blk / P) & 1
+            uint32_t blk = 0;   // running K-block count: partial buffer blk % P
+            uint32_t slot = 0;  // blk % 12
             bool ok = true;
             for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
                 for (int kb = 0; kb < p.kb_total; ++kb, ++blk) {
                     const uint32_t buf = blk & PMASK;
-                    if (!wait_bounded(bar_pempty + buf * 8, ((blk >> PSHIFT) & 1u) ^ 1u, abort_flag, p.status, ROLE_MMA, -1) ||
-                        !wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status, ROLE_MMA, kb)) {
+                    if (!wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status, ROLE_MMA, kb)) {
                         ok = false;
                         break;
                     }
@@ -158,8 +170,8 @@ fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
                         ptx::umma_ss<ptx::KIND_F8>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, k > 0 ? 1u : 0u);
-                    ptx::tc_commit(bar_empty + stage * 8);
-                    ptx::tc_commit(bar_pfull + buf * 8);
+                    ptx::tc_commit(bar_done + slot * 8);
+                    if (++slot == kBsDone) slot = 0;
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1u;
@@ -173,6 +185,7 @@ fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const int half = (warp - 2) >> 2;       // which 64 of the tile's 128 columns
         constexpr int CPW = kBsColsPerWarp;
         uint32_t blk = 0;
+        uint32_t slot = 0, slot_phase = 0;  // done[] slot of block blk and its parity
         bool ok = true;
         for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
             int m_blk, n_blk;
@@ -193,9 +206,13 @@ fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                     sa_next = row_ok ? __ldg(p.a_scale + static_cast<long long>(kb + 1) * p.M + row) : 0.0f;
                     sb_next = __ldg(p.b_scale + static_cast<long long>(kb + 1) * p.n_scale_blocks + n_blk);
                 }
-                if (!wait_bounded(bar_pfull + buf * 8, (blk >> PSHIFT) & 1u, abort_flag, p.status, ROLE_EPILOGUE, kb)) {
+                if (!wait_bounded(bar_done + slot * 8, slot_phase, abort_flag, p.status, ROLE_EPILOGUE, kb)) {
                     ok = false;
                     break;
+                }
+                if (++slot == kBsDone) {
+                    slot = 0;
+                    slot_phase ^= 1u;
                 }
                 ptx::tc_fence_after();
                 const float s = sa * sb;
