@@ -18,6 +18,8 @@
 // Barriers: full[stage] (TMA bytes landed), done[blk % 12] (one tcgen05.commit per K block: the block has been
 // multiplied, which both frees its stage and publishes its partial), pempty[partial] (all eight rescale warps
 // have the partial in registers). The producer, not the MMA issuer, waits for pempty before it loads a block.
+// Two warps issue the MMAs, one the even K blocks and one the odd ones: per block the issuing thread's wait, four
+// MMAs and commit take about as long as the block's tensor work, and blocks go into different partials anyway.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -33,7 +35,8 @@ constexpr int kBsStages = 6;
 constexpr int kBsPartials = 4;                           // partial accumulators in flight (4 x 128 = all 512 columns)
 constexpr int kBsDone = 12;                              // "K block multiplied" barriers: lcm(stages, partials)
 constexpr int kBsEpilogueWarps = 8;                      // two warps per tensor-memory lane quadrant
-constexpr int kBsThreads = 32 * (2 + kBsEpilogueWarps);  // producer, MMA issuer, 8 rescale warps
+constexpr int kBsIssuerB = 2 + kBsEpilogueWarps;         // second MMA-issuing warp (odd K blocks), after the rescale warps
+constexpr int kBsThreads = 32 * (3 + kBsEpilogueWarps);  // producer, MMA issuer (even blocks), 8 rescale warps, issuer (odd)
 constexpr int kBsColsPerWarp = kBsBN / 2;                // each of the two warps of a quadrant takes 64 columns
 
 struct BsSmem {
@@ -137,20 +140,23 @@ fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                         ok = false;
                         break;
                     }
-                    if (++prev == kBsDone) {
-                        prev = 0;
-                        prev_phase ^= 1u;
-                    }
                     const uint32_t full = bar_full + stage * 8;
                     ptx::mbar_arrive_expect_tx(full, L::kAStage + L::kBStage);
                     ptx::tma_load_2d(smem_a + stage * L::kAStage, &tmap_a, full, kb * BK, m_blk * kBM);
                     ptx::tma_load_2d(smem_b + stage * L::kBStage, &tmap_b, full, kb * BK, n_blk * BN);
+                    if (++prev == kBsDone) {
+                        prev = 0;
+                        prev_phase ^= 1u;
+                    }
                     if (++stage == STAGES) stage = 0;
                 }
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer: one partial per K block
+    } else if (warp == 1 || warp == kBsIssuerB) {
+        // ------------------------------------------------------------ MMA issuers: one partial per K block; warp 1
+        // takes the even blocks and warp kBsIssuerB the odd ones. Blocks go into different partials, so their MMAs
+        // are independent, and each tcgen05.commit tracks the MMAs of its own thread only.
+        const uint32_t my_parity = warp == 1 ? 0u : 1u;
         if (ptx::elect_one()) {
             uint32_t stage = 0, phase = 0;
             uint32_t blk = 0;   // running K-block count: partial buffer blk % P
@@ -159,18 +165,20 @@ fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
                 for (int kb = 0; kb < p.kb_total; ++kb, ++blk) {
                     const uint32_t buf = blk & PMASK;
-                    if (!wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status, ROLE_MMA, kb)) {
-                        ok = false;
-                        break;
-                    }
-                    ptx::tc_fence_after();
-                    const uint64_t a_desc = ptx::make_kmajor_sw128_desc(smem_a + stage * L::kAStage);
-                    const uint64_t b_desc = ptx::make_kmajor_sw128_desc(smem_b + stage * L::kBStage);
-                    const uint32_t d_tmem = tmem_base + buf * BN;
+                    if ((blk & 1u) == my_parity) {
+                        if (!wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status, ROLE_MMA, kb)) {
+                            ok = false;
+                            break;
+                        }
+                        ptx::tc_fence_after();
+                        const uint64_t a_desc = ptx::make_kmajor_sw128_desc(smem_a + stage * L::kAStage);
+                        const uint64_t b_desc = ptx::make_kmajor_sw128_desc(smem_b + stage * L::kBStage);
+                        const uint32_t d_tmem = tmem_base + buf * BN;
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        ptx::umma_ss<ptx::KIND_F8>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, k > 0 ? 1u : 0u);
-                    ptx::tc_commit(bar_done + slot * 8);
+                        for (int k = 0; k < 4; ++k)
+                            ptx::umma_ss<ptx::KIND_F8>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, k > 0 ? 1u : 0u);
+                        ptx::tc_commit(bar_done + slot * 8);
+                    }
                     if (++slot == kBsDone) slot = 0;
                     if (++stage == STAGES) {
                         stage = 0;
