@@ -3,7 +3,7 @@ buffers in, host result out (tests/includes/test_config.h:239-286 allocates on t
 the device, runs the kernel and copies C back).
 
 ``HostGemm`` is a thin wrapper over the C-ABI entry ``qgemm_gemm_host``, which owns the device
-buffers and overlaps the three legs itself: A goes up in row bands and B in column bands,
+buffers and overlaps the three legs itself: B goes up in column bands and A in row bands,
 alternately, each arriving band is followed by one GEMM over the blocks of C it completes and by
 their download while later bands are still uploading, so a step costs about the upload time plus a
 thin last strip instead of upload + GEMM + download. Nothing here computes or copies.
@@ -17,10 +17,10 @@ import torch
 from . import B_K_MAJOR, B_ROW_MAJOR, QgemmError, ERR_INVALID_ARG, _check, _dtype_code, lib
 
 
-def band_schedule(extent: int, bands: int = 8):
-    """The bands [lo, hi) ``qgemm_gemm_host`` cuts an extent of rows (of A) or columns (of B) into: about
-    ``bands`` equal ones made of whole 256-wide tiles, the last of them halved repeatedly down to 256, so that
-    what is left after the final upload is a thin strip's GEMM and download."""
+def band_schedule(extent: int, bands: int = 8, shrink: bool = True):
+    """The bands [lo, hi) ``qgemm_gemm_host`` cuts an extent into: about ``bands`` equal ones made of whole
+    256-wide tiles; with ``shrink`` (the rows of A) the last of them is halved repeatedly down to 256, so that what
+    is left after the final upload is a thin strip's GEMM and download. The columns of B are cut without it."""
     if extent <= 0:
         return []
     bands = max(1, bands)
@@ -32,7 +32,7 @@ def band_schedule(extent: int, bands: int = 8):
         sizes.append(min(rows, left))
         left -= sizes[-1]
     last = sizes.pop()
-    while last > 256:
+    while shrink and last > 256:
         half = -(-(last // 2) // 256) * 256
         if half >= last:
             break
@@ -84,7 +84,7 @@ class HostGemm:
         self.h2d_bytes = (M * K + N * K) * es
         self.d2h_bytes = M * N * osz
         # one GEMM per arriving band except the very first (nothing to multiply it with yet)
-        self.kernel_launches_per_call = max(1, len(band_schedule(M, bands)) + len(band_schedule(N, bands)) - 1)
+        self.kernel_launches_per_call = max(1, len(band_schedule(M, bands)) + len(band_schedule(N, bands, False)) - 1)
 
     def __call__(self, a_host, b_host, c_host, scale_a=None, scale_b=None) -> None:
         """Enqueue one C = A x B with pinned host tensors on the current stream's dependency chain
