@@ -183,26 +183,61 @@ quantize_kernel(const TIn* __restrict__ in, long long ld_in, uint8_t* __restrict
     }
 }
 
-// INT4 output: one thread handles 8 consecutive elements of a row and writes 4 packed bytes.
+// INT4 output: eight consecutive elements of a row become four packed bytes (one 32-bit store). Same (row, chunk)
+// decomposition as quantize_kernel, a chunk being kQuantThreads x U groups of eight.
+__device__ __forceinline__ uint32_t quantize_nibble(float x, float scale) {
+    return static_cast<uint32_t>(max(-7, min(7, __float2int_rn(__fdiv_rn(x, scale))))) & 0xfu;
+}
+
 template <typename TIn>
 __global__ void __launch_bounds__(kQuantThreads)
 quantize_int4_kernel(const TIn* __restrict__ in, long long ld_in, uint8_t* __restrict__ out, long long ld_out_bytes,
-                     int rows, int cols, const float* __restrict__ amax_in, float* __restrict__ scale_out) {
+                     int rows, int cols, const float* __restrict__ amax_in, float* __restrict__ scale_out, int vec_ok) {
     ptx::pdl_launch_dependents();
     ptx::pdl_wait();
+    constexpr int U = Unroll<TIn>::value / 2;
+    constexpr int kChunkOcts = kQuantThreads * U;
     const float amax = __ldg(amax_in);
     const float scale = amax > 0.0f ? __fdiv_rn(amax, 7.0f) : 1.0f;
     if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
-    // blockIdx.x walks along the row (8 elements per thread), blockIdx.y strides over the rows
-    const int c = (static_cast<int>(blockIdx.x) * kQuantThreads + static_cast<int>(threadIdx.x)) * 8;
-    if (c >= cols) return;
-    for (long long r = blockIdx.y; r < rows; r += gridDim.y) {
-        const TIn* src = in + r * ld_in + c;
-        uint8_t* dst = out + r * ld_out_bytes + c / 2;
-        for (int e = 0; e < 8 && c + e < cols; e += 2) {  // cols is even: pairs are whole
-            const int q0 = max(-7, min(7, __float2int_rn(__fdiv_rn(load_as_float(src + e), scale))));
-            const int q1 = max(-7, min(7, __float2int_rn(__fdiv_rn(load_as_float(src + e + 1), scale))));
-            dst[e >> 1] = static_cast<uint8_t>((q0 & 0xf) | ((q1 & 0xf) << 4));
+    const int octs_per_row = (cols + 7) / 8;
+    const int chunks_per_row = (octs_per_row + kChunkOcts - 1) / kChunkOcts;
+    const long long items = static_cast<long long>(chunks_per_row) * rows;
+    for (long long item = blockIdx.x; item < items; item += gridDim.x) {
+        const long long r = item / chunks_per_row;
+        const int o0 = static_cast<int>(item - r * chunks_per_row) * kChunkOcts + static_cast<int>(threadIdx.x);
+        const TIn* src_row = in + r * ld_in;
+        uint8_t* dst_row = out + r * ld_out_bytes;
+        if (vec_ok && (o0 + (U - 1) * kQuantThreads) * 8 + 8 <= cols) {
+            typename Quad<TIn>::Raw v[2 * U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                v[2 * u] = Quad<TIn>::load(src_row + (o0 + u * kQuantThreads) * 8);
+                v[2 * u + 1] = Quad<TIn>::load(src_row + (o0 + u * kQuantThreads) * 8 + 4);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                float x[4], y[4];
+                Quad<TIn>::to_float(v[2 * u], x);
+                Quad<TIn>::to_float(v[2 * u + 1], y);
+                uint32_t w = 0;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    w |= quantize_nibble(x[e], scale) << (4 * e);
+                    w |= quantize_nibble(y[e], scale) << (16 + 4 * e);
+                }
+                *reinterpret_cast<uint32_t*>(dst_row + (o0 + u * kQuantThreads) * 4) = w;
+            }
+            continue;
+        }
+        for (int u = 0; u < U; ++u) {
+            const int c = (o0 + u * kQuantThreads) * 8;
+            if (c >= cols) break;
+            for (int e = 0; e < 8 && c + e < cols; e += 2) {  // cols is even: pairs are whole
+                const uint32_t q0 = quantize_nibble(load_as_float(src_row + c + e), scale);
+                const uint32_t q1 = quantize_nibble(load_as_float(src_row + c + e + 1), scale);
+                dst_row[(c + e) >> 1] = static_cast<uint8_t>(q0 | (q1 << 4));
+            }
         }
     }
 }
@@ -222,12 +257,9 @@ int quantize_typed(const TIn* in, size_t ld_in, void* out, size_t ld_out, float*
                    (int)cols, amax_out, vec_ok);
     if (e != cudaSuccess) return QGEMM_ERR_CUDA;
     if (int4)
-        e = launch_pdl(quantize_int4_kernel<TIn>,
-                       dim3(static_cast<unsigned>(((cols + 7) / 8 + kQuantThreads - 1) / kQuantThreads),
-                            static_cast<unsigned>(rows < 65535 ? rows : 65535)),
-                       dim3(kQuantThreads), 0, stream, in, (long long)ld_in,
+        e = launch_pdl(quantize_int4_kernel<TIn>, dim3(blocks), dim3(kQuantThreads), 0, stream, in, (long long)ld_in,
                        static_cast<uint8_t*>(out), (long long)(ld_out / 2), (int)rows, (int)cols,
-                       static_cast<const float*>(amax_out), scale_out);
+                       static_cast<const float*>(amax_out), scale_out, vec_ok);
     else if (fp8)
         e = launch_pdl(quantize_kernel<TIn, true>, dim3(blocks), dim3(kQuantThreads), 0, stream, in, (long long)ld_in,
                        static_cast<uint8_t*>(out), (long long)ld_out, (int)rows, (int)cols,
@@ -253,8 +285,9 @@ int quantize_launch(int in_dtype, int out_dtype, const void* in, size_t ld_in, v
     if (rows > 0 && cols > 0 && (in == nullptr || out == nullptr || ld_in < cols || ld_out < cols))
         return QGEMM_ERR_INVALID_ARG;
     const size_t es = in_dtype == QGEMM_DTYPE_FP32 ? 4 : 2;
+    // 4-element loads and 4-byte stores: for packed int4 output four bytes are eight elements
     const int vec_ok = (reinterpret_cast<uintptr_t>(in) % (4 * es) == 0) && (ld_in % 4 == 0) &&
-                       (reinterpret_cast<uintptr_t>(out) % 4 == 0) && (ld_out % 4 == 0);
+                       (reinterpret_cast<uintptr_t>(out) % 4 == 0) && (ld_out % (int4 ? 8 : 4) == 0);
     // blocks walk (row, chunk) items: see amax_kernel
     const size_t chunk_quads = static_cast<size_t>(kQuantThreads) * (es == 4 ? 4 : 8);
     const size_t quads = (((cols + 3) / 4 + chunk_quads - 1) / chunk_quads) * rows * kQuantThreads;
