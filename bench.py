@@ -32,9 +32,13 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 # DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum), from the
-# ncu capture summarised in profiles/gemm_tcgen05_pair_bf16_8192.md. Keyed by workload; None where no
-# capture of that workload exists.
-NCU_TRAFFIC_BYTES = {"c2_bf16_8192": 1.058648e9 + 129.081e6}
+# ncu captures summarised under profiles/ (the BF16 one in gemm_tcgen05_pair_bf16_8192.md). Keyed by workload; None
+# where no capture of that workload exists.
+NCU_TRAFFIC_BYTES = {
+    "c2_bf16_8192": 1.1135e9 + 128.26e6,     # latest capture of the pair kernel (mean of its two launches)
+    "f1_fp8_blockscale": 131.4e6 + 39.6e6,   # profiles/fp8_blockscale_kernel_4096x7168x7168.md
+    "c3_int8_8192": 337.7e6 + 114.2e6,       # profiles/gemm_tcgen05_pair_int8_fp8.md
+}
 
 NOMINAL_PEAK_TFLOPS = {"bf16": 2250.0, "fp16": 2250.0, "int8": 4500.0, "fp8": 4500.0}
 
