@@ -602,9 +602,11 @@ def main():
         like_for_like["sustained"] = su
         like_for_like["library"] = "torch.matmul(A[M,K], B[N,K]^T) -> same dtype as C (cuBLAS), a side figure only"
         roofline["like_for_like"] = like_for_like
-    roofline.update({"kernel": "fp8_blockscale_kernel" if blockscale else (
-                         "gemm_tcgen05_pair_kernel" if M > 256 and not (args.tile_n or args.split_k)
-                         else "gemm_tcgen05_kernel"),
+    plan = q.plan_query({"bf16": q.BF16, "fp16": q.FP16, "int8": q.INT8, "fp8": q.FP8_E4M3}[in_name],
+                        {"bf16": q.BF16, "fp16": q.FP16, "fp32": q.FP32}[out_name], q.B_K_MAJOR, M, N, K, tuning)
+    gemm_kernel_name = ("gemm_tcgen05_wide_pair_kernel" if plan["tile_m"] == 512 else
+                        "gemm_tcgen05_pair_kernel" if plan["ctas_per_tile"] == 2 else "gemm_tcgen05_kernel")
+    roofline.update({"kernel": "fp8_blockscale_kernel" if blockscale else gemm_kernel_name, "plan": plan,
                      "kernel_ms": gemm_ms, "replica_ms_per_step": replica_ms, "algorithmic_flop": flop_per_step_rank,
                      "algorithmic_bytes": alg_bytes, "traffic": NCU_TRAFFIC_BYTES.get(args.workload)})
 

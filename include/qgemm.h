@@ -62,7 +62,8 @@ typedef struct {
     int split_k; /* number of K splits (>= 1) */
     int group_m; /* tile rows per scheduling group */
     int max_ctas; /* cap on the persistent grid (testing) */
-    int cta_pair; /* 1 = pair two CTAs on 256x256 tiles (tcgen05 cta_group::2), -1 = never, 0 = heuristic */
+    int cta_pair; /* 1 = pair two CTAs on 256x256 tiles (tcgen05 cta_group::2), 2 = pair them on 512x256 tiles,
+                     -1 = never, 0 = heuristic */
     int relayout_b; /* row-major B: 1 = always relay it out to K-major with the transpose kernel first,
                        0 = read it in place (MN-major tensor-core operand) when its base and ldb are 16-byte aligned */
 } qgemm_tuning_t;
@@ -151,6 +152,15 @@ size_t qgemm_workspace_bytes(void);
 
 /* Bytes of scratch a call with these arguments would use at most (row-major B counted as relaid out). */
 size_t qgemm_workspace_query(int in_dtype, int b_layout, size_t M, size_t N, size_t K, const qgemm_tuning_t* tuning);
+
+/*
+ * Which kernel configuration a GEMM of this shape would get on the current device (the same planning the entry
+ * points run; alignment-dependent fall-backs, e.g. a C that TMA cannot address, are decided at call time and not
+ * reflected): out6 = { tile rows, tile columns, CTAs per tile (1, or 2 = tcgen05 cta_group::2 pair), K splits,
+ * tiles of the last wave whose K range is sliced (0 = none), slices }. No counterpart in the reference.
+ */
+int qgemm_plan_query(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, size_t K,
+                     const qgemm_tuning_t* tuning, int* out6);
 
 /*
  * Synchronises the current device and copies its four status words to out4:

@@ -28,7 +28,7 @@ C_ABI_SYMBOLS = (
     "qgemm_workspace_bytes", "qgemm_workspace_query", "qgemm_device_status", "qgemm_shutdown",
     "qgemm_status_string", "qgemm_version", "qgemm_mix_gemm_splitk_static",
     "qgemm_fp8_block_scaled_gemm", "qgemm_quantize", "qgemm_gemm_multi_dst", "qgemm_peer_export",
-    "qgemm_peer_open", "qgemm_peer_close", "qgemm_gemm_host",
+    "qgemm_peer_open", "qgemm_peer_close", "qgemm_gemm_host", "qgemm_plan_query",
 )
 
 
@@ -78,6 +78,8 @@ def lib() -> C.CDLL:
         L.qgemm_gemm_host.argtypes = [i, i, i, vp, sz, vp, sz, C.POINTER(C.c_float), C.POINTER(C.c_float), vp, sz, sz,
                                       sz, sz, vp]
         L.qgemm_gemm_host.restype = i
+        L.qgemm_plan_query.argtypes = [i, i, i, sz, sz, sz, C.POINTER(Tuning), C.POINTER(C.c_int)]
+        L.qgemm_plan_query.restype = i
         L.qgemm_peer_export.argtypes = [vp, vp, C.POINTER(sz)]
         L.qgemm_peer_export.restype = i
         L.qgemm_peer_open.argtypes = [vp, C.POINTER(C.c_void_p)]
@@ -399,6 +401,15 @@ def workspace_reserve(nbytes: int) -> None:
 
 def workspace_query(in_dtype: int, b_layout: int, M: int, N: int, K: int, tuning: Tuning | None = None) -> int:
     return int(lib().qgemm_workspace_query(in_dtype, b_layout, M, N, K, C.byref(tuning) if tuning else None))
+
+
+def plan_query(in_dtype: int, out_dtype: int, b_layout: int, M: int, N: int, K: int, tuning: Tuning | None = None):
+    """{tile_m, tile_n, ctas_per_tile, split_k, tail_tiles, tail_slices} the library would use for this shape."""
+    out = (C.c_int * 6)()
+    _check(lib().qgemm_plan_query(in_dtype, out_dtype, b_layout, M, N, K, C.byref(tuning) if tuning else None, out),
+           "qgemm_plan_query")
+    keys = ("tile_m", "tile_n", "ctas_per_tile", "split_k", "tail_tiles", "tail_slices")
+    return dict(zip(keys, list(out)))
 
 
 def device_status():

@@ -181,6 +181,7 @@ int make_output_map(void* ptr, uint64_t M, uint64_t N, uint64_t ld, uint64_t spl
 struct Config {
     int bn, splits, kb_per_split, group_m;
     bool pair;  // two CTAs per 256x256 tile (bn is then 256 and tiles are counted in 256-row units)
+    bool wide;  // pair with 512x256 tiles, both accumulators of a CTA in use (gemm_sm100_2cta_wide.cuh)
     int am;     // rows of A loaded per stage (128; 64 or 32 with the 64-wide tile when M is that small)
 };
 
@@ -247,7 +248,7 @@ double estimate(int bn, bool pair, int splits, size_t M, size_t N, int kb_total,
 }
 
 Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuning_t* tuning, int min_bn = 64,
-                     bool allow_tail = false) {
+                     bool allow_tail = false, int elem_bytes = 1) {
     int want_bn = tuning ? tuning->tile_n : 0;
     int want_split = tuning ? tuning->split_k : 0;
     int want_group = tuning ? tuning->group_m : 0;
@@ -257,7 +258,7 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
     if (!want_group) want_group = env_int("QGEMM_GROUP_M");
     if (!want_pair) want_pair = env_int("QGEMM_CTA_PAIR");
 
-    Config best{256, 1, kb_total, 16, false, kBM};
+    Config best{256, 1, kb_total, 16, false, false, kBM};
     double best_t = 1e300;
     struct Cand { int bn; bool pair; };
     const Cand cands[] = {{256, true}, {256, false}, {128, false}, {64, false}};
@@ -293,8 +294,17 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
     if (!best.pair && best.bn == 64 && env_int("QGEMM_FULL_A_TILE") == 0) best.am = M <= 32 ? 32 : (M <= 64 ? 64 : kBM);
     // Tile rows per scheduling group: as many as keep the group's A panel (rows x K bytes) near 32 MiB, so that
     // it stays in L2 while the B panels stream past it.
+    // 512 x 256 tiles per CTA pair instead of 256 x 256: a quarter fewer operand bytes from L2 per flop (clock, on a
+    // power-capped part) against an epilogue that is no longer hidden behind the next tile. Measured on B200 at 8192^3:
+    // bf16 +5 % sustained (1383 against 1314 TFLOP/s; the library GEMM 1371), int8 and fp8 -3 to -14 % (their
+    // mainloop per tile is half as long, so the exposed epilogue weighs double), bf16 4096^3 -4 % (two waves of 128
+    // tiles). So: 16-bit inputs, at least four waves of wide tiles, K deep enough (96 K blocks = 6144 elements).
+    const long long wide_tiles = static_cast<long long>((M + kWideTileM - 1) / kWideTileM) *
+                                 static_cast<long long>((N + kWideTileN - 1) / kWideTileN);
+    const bool auto_wide = want_pair == 0 && elem_bytes == 2 && kb_total >= 96 && wide_tiles >= 4ll * (sms / 2);
+    best.wide = (want_pair == 2 || auto_wide) && best.pair && best.splits == 1;
     const long long panel_rows = (32ll << 20) / (static_cast<long long>(kb_total) * 128);
-    const int tile_m = best.pair ? kPairTileM : kBM;
+    const int tile_m = best.wide ? kWideTileM : (best.pair ? kPairTileM : kBM);
     const int auto_group = static_cast<int>(std::max<long long>(4, std::min<long long>(4096, panel_rows / tile_m)));
     best.group_m = want_group > 0 ? want_group : auto_group;
     return best;
@@ -362,14 +372,14 @@ int make_plan(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, siz
                  env_int("QGEMM_SPLIT_K") == 0 && env_int("QGEMM_MAX_CTAS") == 0 &&
                  env_int("QGEMM_DIRECT_STORE") == 0 && !(tail_env != nullptr && tail_env[0] == '0');
     p->cfg = choose_config(M, N, std::max(p->kb_total, 1), sms, tuning,
-                           (b_direct && p->ti.elem_bytes == 1) ? 128 : 64, allow_tail);
+                           (b_direct && p->ti.elem_bytes == 1) ? 128 : 64, allow_tail, p->ti.elem_bytes);
     p->ld_relayout = round_up(K, 16 / p->ti.elem_bytes);
     p->relayout_bytes =
         (b_layout == QGEMM_B_ROW_MAJOR && !b_direct) ? round_up(N * p->ld_relayout * p->ti.elem_bytes, 256) : 0;
     p->ldw = round_up(N, 4);
     p->partial_bytes = p->cfg.splits > 1 ? static_cast<size_t>(p->cfg.splits) * M * p->ldw * 4 : 0;
     p->tail_tiles = p->tail_slices = p->tail_kb_per_slice = 0;
-    if (allow_tail && p->cfg.pair && p->cfg.splits == 1) {
+    if (allow_tail && p->cfg.pair && !p->cfg.wide && p->cfg.splits == 1) {
         const long long tiles = static_cast<long long>((M + kPairTileM - 1) / kPairTileM) *
                                 static_cast<long long>((N + kPairTileN - 1) / kPairTileN);
         if (tail_split(tiles, sms / 2, p->kb_total, &p->tail_tiles, &p->tail_slices, &p->tail_kb_per_slice))
@@ -452,9 +462,13 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
         ldb_k = plan.ld_relayout;
     }
 
+    // The wide pair kernel stores through TMA only: without a C it can address that way, take the 256 x 256 pairs.
+    if (plan.cfg.wide && (n_extra > 0 || reinterpret_cast<uintptr_t>(C) % 16 != 0 || (ldc * out_bytes) % 16 != 0 ||
+                          env_int("QGEMM_DIRECT_STORE") != 0))
+        plan.cfg.wide = false;
     const Config& cfg = plan.cfg;
     CUtensorMap ta, tb;
-    rc = make_operand_map(A, M, K, lda, in_dtype, static_cast<uint32_t>(cfg.am), &ta);
+    rc = make_operand_map(A, M, K, lda, in_dtype, cfg.wide ? 256u : static_cast<uint32_t>(cfg.am), &ta);
     if (rc != QGEMM_OK) return rc;
     if (b_direct)  // [K rows, N columns]; one box = 128 bytes of N x one 128-byte K block of rows
         rc = make_operand_map(B, K, N, ldb, in_dtype, 128u / static_cast<uint32_t>(es), &tb);
@@ -467,14 +481,14 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     p.M = static_cast<int>(M);
     p.N = static_cast<int>(N);
     p.K = static_cast<int>(K);
-    const int tile_m = cfg.pair ? kPairTileM : kBM;
+    const int tile_m = cfg.wide ? kWideTileM : (cfg.pair ? kPairTileM : kBM);
     p.m_tiles = static_cast<int>((M + tile_m - 1) / tile_m);
     p.n_tiles = static_cast<int>((N + cfg.bn - 1) / cfg.bn);
     p.splits = cfg.splits;
     p.kb_total = plan.kb_total;
     p.kb_per_split = cfg.kb_per_split;
     p.group_m = cfg.group_m;
-    p.idesc = ptx::make_idesc(plan.ti.cfmt, plan.ti.fmt, plan.ti.fmt, static_cast<uint32_t>(tile_m),
+    p.idesc = ptx::make_idesc(plan.ti.cfmt, plan.ti.fmt, plan.ti.fmt, static_cast<uint32_t>(cfg.wide ? kPairTileM : tile_m),
                               static_cast<uint32_t>(cfg.bn), b_direct ? 1u : 0u);
     p.b_mn_major = b_direct ? 1 : 0;
     p.test_skip_kb = std::getenv("QGEMM_TEST_SKIP_LOAD") ? env_int("QGEMM_TEST_SKIP_LOAD") : -1;
@@ -525,9 +539,18 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     if (cap > 0) grid = std::min(grid, cap);
 
     cudaError_t e;
-    const bool tail = cfg.pair && plan.tail_tiles > 0 && p.c_tma_ok && n_extra == 0;
+    const bool tail = cfg.pair && !cfg.wide && plan.tail_tiles > 0 && p.c_tma_ok && n_extra == 0;
     p.total_work = static_cast<int>(work);
-    if (cfg.pair) {
+    if (cfg.wide) {
+        if (!p.c_tma_ok) return QGEMM_ERR_CUDA;
+        int clusters = static_cast<int>(std::min<long long>(work, st->sm_count / 2));
+        if (cap > 0) clusters = std::min(clusters, std::max(1, cap / 2));
+        switch (plan.ti.kind) {
+            case ptx::KIND_F16: e = launch_gemm_wide_f16(launch_out, ta, tb, tc, p, clusters, stream); break;
+            case ptx::KIND_I8: e = launch_gemm_wide_i8(launch_out, ta, tb, tc, p, clusters, stream); break;
+            default: e = launch_gemm_wide_f8(launch_out, ta, tb, tc, p, clusters, stream); break;
+        }
+    } else if (cfg.pair) {
         CUtensorMap tws;
         std::memset(&tws, 0, sizeof(tws));
         if (tail) {
@@ -788,6 +811,29 @@ size_t qgemm_workspace_query(int in_dtype, int b_layout, size_t M, size_t N, siz
     const int out = (in_dtype == QGEMM_DTYPE_INT8) ? QGEMM_DTYPE_INT32 : QGEMM_DTYPE_FP32;
     if (make_plan(in_dtype, out, b_layout, M, N, K, sms, tuning, &plan) != QGEMM_OK) return 0;
     return plan.relayout_bytes + plan.partial_bytes + widened;
+}
+
+int qgemm_plan_query(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, size_t K,
+                     const qgemm_tuning_t* tuning, int* out6) {
+    if (out6 == nullptr) return QGEMM_ERR_INVALID_ARG;
+    int sms = 148;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_dev[dev].init)
+            sms = g_dev[dev].sm_count;
+    }
+    Plan plan;
+    const int rc = make_plan(in_dtype == QGEMM_DTYPE_INT4 ? QGEMM_DTYPE_INT8 : in_dtype, out_dtype, b_layout, M, N,
+                             std::max<size_t>(K, 1), sms, tuning, &plan);
+    if (rc != QGEMM_OK) return rc;
+    out6[0] = plan.cfg.wide ? kWideTileM : (plan.cfg.pair ? kPairTileM : kBM);
+    out6[1] = plan.cfg.bn;
+    out6[2] = plan.cfg.pair ? 2 : 1;
+    out6[3] = plan.cfg.splits;
+    out6[4] = plan.tail_tiles;
+    out6[5] = plan.tail_slices;
+    return QGEMM_OK;
 }
 
 int qgemm_device_status(int* out4) {

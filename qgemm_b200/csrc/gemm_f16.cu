@@ -11,4 +11,8 @@ cudaError_t launch_gemm_pair_f16(int out, const CUtensorMap& ta, const CUtensorM
                                  const GemmParams& p, int clusters, cudaStream_t stream) {
     return launch_pair_kind<ptx::KIND_F16>(out, ta, tb, tc, tws, extra, p, clusters, stream);
 }
+cudaError_t launch_gemm_wide_f16(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+                                 int clusters, cudaStream_t stream) {
+    return launch_wide_kind<ptx::KIND_F16>(out, ta, tb, tc, p, clusters, stream);
+}
 }  // namespace qgemm

@@ -4,6 +4,7 @@
 
 #include "gemm_sm100.cuh"
 #include "gemm_sm100_2cta.cuh"
+#include "gemm_sm100_2cta_wide.cuh"
 
 namespace qgemm {
 
@@ -143,6 +144,64 @@ cudaError_t launch_pair_kind(int out, const CUtensorMap& ta, const CUtensorMap& 
     }
 #undef QGEMM_PAIR_CASE
 }
+
+// Wide CTA-pair kernel (512 x 256 tiles per cluster of two; gemm_sm100_2cta_wide.cuh).
+template <int KIND, int OUT>
+cudaError_t launch_wide_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+                            int clusters, cudaStream_t stream) {
+    auto kernel = gemm_tcgen05_wide_pair_kernel<KIND, OUT>;
+    constexpr int smem = WideSmem::kDynamicBytes;
+    static bool configured[64] = {};
+    static int max_clusters[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!configured[dev]) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * 74);
+        cfg.blockDim = dim3(kGemmThreads);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
+            (void)cudaGetLastError();
+            n = 74;
+        }
+        max_clusters[dev] = n;
+        configured[dev] = true;
+    }
+    if (clusters > max_clusters[dev]) clusters = max_clusters[dev];
+    if (clusters < 1) clusters = 1;
+    return launch_pdl(kernel, dim3(2 * clusters), dim3(kGemmThreads), smem, stream, ta, tb, tc, p);
+}
+
+template <int KIND>
+cudaError_t launch_wide_kind(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                             const GemmParams& p, int clusters, cudaStream_t stream) {
+    switch (out) {
+        case OUT_F32: return launch_wide_one<KIND, OUT_F32>(ta, tb, tc, p, clusters, stream);
+        case OUT_BF16: return launch_wide_one<KIND, OUT_BF16>(ta, tb, tc, p, clusters, stream);
+        case OUT_F16: return launch_wide_one<KIND, OUT_F16>(ta, tb, tc, p, clusters, stream);
+        case OUT_RAW32: return launch_wide_one<KIND, OUT_RAW32>(ta, tb, tc, p, clusters, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_gemm_wide_f16(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+                                 int clusters, cudaStream_t stream);
+cudaError_t launch_gemm_wide_i8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+                                int clusters, cudaStream_t stream);
+cudaError_t launch_gemm_wide_f8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+                                int clusters, cudaStream_t stream);
 
 cudaError_t launch_gemm_pair_f16(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tws,
                                  const ExtraDst* extra, const GemmParams& p,
