@@ -298,10 +298,13 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
     // power-capped part) against an epilogue that is no longer hidden behind the next tile. Measured on B200 at 8192^3:
     // bf16 +5 % sustained (1383 against 1314 TFLOP/s; the library GEMM 1371), int8 and fp8 -3 to -14 % (their
     // mainloop per tile is half as long, so the exposed epilogue weighs double), bf16 4096^3 -4 % (two waves of 128
-    // tiles). So: 16-bit inputs, at least four waves of wide tiles, K deep enough (96 K blocks = 6144 elements).
+    // tiles), 8192 x 4096 x 8192 -5 % (3.5 waves), 6144 x 7168 x 8192 -1 % (4.5 waves), 8192 x 8192 x 4096 -1 %,
+    // 8192 x 8192 x 6144 +1 %, 16384 x 8192 x 8192 +2 %, 8192 x 8192 x 16384 +6 %. So: 16-bit inputs, at least six
+    // waves of wide tiles, K deep enough (96 K blocks = 6144 elements). The gain is clock under the power cap: a
+    // single launch on an idle GPU is not power-limited and runs faster on the 256 x 256 pairs.
     const long long wide_tiles = static_cast<long long>((M + kWideTileM - 1) / kWideTileM) *
                                  static_cast<long long>((N + kWideTileN - 1) / kWideTileN);
-    const bool auto_wide = want_pair == 0 && elem_bytes == 2 && kb_total >= 96 && wide_tiles >= 4ll * (sms / 2);
+    const bool auto_wide = want_pair == 0 && elem_bytes == 2 && kb_total >= 96 && wide_tiles >= 6ll * (sms / 2);
     best.wide = (want_pair == 2 || auto_wide) && best.pair && best.splits == 1;
     const long long panel_rows = (32ll << 20) / (static_cast<long long>(kb_total) * 128);
     const int tile_m = best.wide ? kWideTileM : (best.pair ? kPairTileM : kBM);

@@ -92,11 +92,12 @@ def test_unaligned_c_takes_the_ordinary_pairs(qlib, oracle, dev):
 
 
 def test_when_the_library_takes_wide_tiles_by_itself(qlib):
-    """16-bit inputs, deep K and at least four waves of 512 x 256 tiles; never for the 8-bit kinds."""
+    """16-bit inputs, deep K and at least six waves of 512 x 256 tiles; never for the 8-bit kinds."""
     q = qlib
     assert q.plan_query(q.BF16, q.BF16, q.B_K_MAJOR, 8192, 8192, 8192)["tile_m"] == 512
     assert q.plan_query(q.FP16, q.FP32, q.B_K_MAJOR, 16384, 8192, 8192)["tile_m"] == 512
     assert q.plan_query(q.BF16, q.BF16, q.B_K_MAJOR, 4096, 4096, 4096)["tile_m"] == 256
+    assert q.plan_query(q.BF16, q.BF16, q.B_K_MAJOR, 6144, 7168, 8192)["tile_m"] == 256
     assert q.plan_query(q.BF16, q.BF16, q.B_K_MAJOR, 8192, 8192, 4096)["tile_m"] == 256
     assert q.plan_query(q.INT8, q.BF16, q.B_K_MAJOR, 8192, 8192, 8192)["tile_m"] == 256
     assert q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 8192, 8192, 8192)["tile_m"] == 256
