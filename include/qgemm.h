@@ -166,8 +166,27 @@ int qgemm_plan_query(int in_dtype, int out_dtype, int b_layout, size_t M, size_t
  * Synchronises the current device and copies its four status words to out4:
  * [0] error code (0 = none, 1 = a bounded wait ran out), [1] CTA, [2] role (1 producer, 2 MMA,
  * 3 epilogue), [3] position. Returns QGEMM_ERR_DEVICE_TIMEOUT if [0] != 0. Clears the words.
+ * The words of qgemm_mix_gemm_splitk_static (which keeps its own, inside the loaded module) are read and
+ * cleared as well and reported when the ordinary ones are clean. Allocates nothing: on a device where no
+ * GEMM has run yet there is nothing to read.
  */
 int qgemm_device_status(int* out4);
+
+/*
+ * The QGEMM_* environment variables (tuning overrides for experiments: QGEMM_TILE_N, QGEMM_SPLIT_K,
+ * QGEMM_GROUP_M, QGEMM_CTA_PAIR, QGEMM_RELAYOUT_B, QGEMM_MAX_CTAS, QGEMM_DIRECT_STORE, QGEMM_FULL_A_TILE,
+ * QGEMM_TAIL_SPLIT, QGEMM_K_CLUSTER, QGEMM_HOST_BANDS, QGEMM_HOST_BANDS_N) are read once, when the library is
+ * loaded; this reads them again. Not meant to run concurrently with GEMM calls of other threads.
+ */
+int qgemm_reload_env(void);
+
+/*
+ * Test hook for failure detection without a GPU fault: the NEXT GEMM this process launches leaves out the TMA
+ * loads of 128-byte K block `k_block` in every CTA, so that the consumer's bounded wait runs out after about a
+ * second, the kernel returns by itself and qgemm_device_status reports where it gave up. One-shot (the launch
+ * that consumes it disarms it); k_block < 0 disarms. Nothing in the library arms it by itself.
+ */
+int qgemm_test_arm_skip_load(int k_block);
 
 /*
  * Split-K mixed GEMM that allocates nothing. It has no counterpart in the reference; it exists for
@@ -213,6 +232,15 @@ int qgemm_mix_gemm_splitk_static(int in_dtype, int out_dtype, const void* A, siz
 int qgemm_gemm_host(int in_dtype, int out_dtype, int b_layout, const void* A_host, size_t lda, const void* B_host,
                     size_t ldb, const float* scale_a_host, const float* scale_b_host, void* C_host, size_t ldc,
                     size_t M, size_t N, size_t K, qgemm_stream_t stream);
+
+/*
+ * The bands qgemm_gemm_host cuts an extent (the rows of A with shrink != 0, the columns of B with shrink == 0)
+ * into: about `bands` (0 = the default, 8) equal bands of whole 256-wide tiles; with `shrink` the last of them is
+ * halved repeatedly down to 256. Writes up to max_bands pairs {lo, hi} to edges_out (may be NULL) and returns the
+ * number of bands. Pure host arithmetic: callers use it to count the launches and copies of a qgemm_gemm_host
+ * call. No counterpart in the reference.
+ */
+int qgemm_host_band_schedule(size_t extent, int bands, int shrink, size_t* edges_out, int max_bands);
 
 /*
  * GEMM whose result is stored to several buffers by the same kernel: C_dsts[0..n_dsts-1] each receive the

@@ -190,6 +190,32 @@ int env_int(const char* name) {
     return v ? std::atoi(v) : 0;
 }
 
+// The QGEMM_* tuning variables are read once, when the library is loaded (and again by qgemm_reload_env): the
+// launch path of a microsecond-scale kernel does not scan the environment.
+EnvSettings read_env() {
+    EnvSettings e;
+    e.tile_n = env_int("QGEMM_TILE_N");
+    e.split_k = env_int("QGEMM_SPLIT_K");
+    e.group_m = env_int("QGEMM_GROUP_M");
+    e.cta_pair = env_int("QGEMM_CTA_PAIR");
+    e.relayout_b = env_int("QGEMM_RELAYOUT_B");
+    e.max_ctas = env_int("QGEMM_MAX_CTAS");
+    e.direct_store = env_int("QGEMM_DIRECT_STORE");
+    e.full_a_tile = env_int("QGEMM_FULL_A_TILE");
+    const char* tail = std::getenv("QGEMM_TAIL_SPLIT");
+    e.tail_split_off = (tail != nullptr && tail[0] == '0') ? 1 : 0;
+    const char* kc = std::getenv("QGEMM_K_CLUSTER");
+    e.k_cluster_off = (kc != nullptr && kc[0] == '0') ? 1 : 0;
+    e.host_bands = std::max(0, env_int("QGEMM_HOST_BANDS"));
+    e.host_bands_n = std::max(0, env_int("QGEMM_HOST_BANDS_N"));
+    return e;
+}
+EnvSettings g_env = read_env();
+
+// One-shot test hook (qgemm_test_arm_skip_load): the next GEMM launched by this process leaves out the loads of
+// this K block. -1 = not armed.
+int g_test_skip_kb = -1;
+
 // Last-wave split of the CTA-pair kernel. T tiles on S clusters run as T / S full waves plus a last wave of
 // R = T % S tiles that keeps only R clusters busy for a whole tile's duration. When R is small, the K range of
 // each of those R tiles is cut into `slices` pieces so that R * slices <= S clusters share them: the last wave
@@ -253,10 +279,10 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
     int want_split = tuning ? tuning->split_k : 0;
     int want_group = tuning ? tuning->group_m : 0;
     int want_pair = tuning ? tuning->cta_pair : 0;
-    if (!want_bn) want_bn = env_int("QGEMM_TILE_N");
-    if (!want_split) want_split = env_int("QGEMM_SPLIT_K");
-    if (!want_group) want_group = env_int("QGEMM_GROUP_M");
-    if (!want_pair) want_pair = env_int("QGEMM_CTA_PAIR");
+    if (!want_bn) want_bn = g_env.tile_n;
+    if (!want_split) want_split = g_env.split_k;
+    if (!want_group) want_group = g_env.group_m;
+    if (!want_pair) want_pair = g_env.cta_pair;
 
     Config best{256, 1, kb_total, 16, false, false, kBM};
     double best_t = 1e300;
@@ -291,7 +317,7 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
     // Small M with the narrow tile: load only the rows of A that exist, which leaves room for up to 16 stages so
     // that a short K is wholly in flight at once.
     best.am = kBM;
-    if (!best.pair && best.bn == 64 && env_int("QGEMM_FULL_A_TILE") == 0) best.am = M <= 32 ? 32 : (M <= 64 ? 64 : kBM);
+    if (!best.pair && best.bn == 64 && g_env.full_a_tile == 0) best.am = M <= 32 ? 32 : (M <= 64 ? 64 : kBM);
     // Tile rows per scheduling group: as many as keep the group's A panel (rows x K bytes) near 32 MiB, so that
     // it stays in L2 while the B panels stream past it.
     // 512 x 256 tiles per CTA pair instead of 256 x 256: a quarter fewer operand bytes from L2 per flop (clock, on a
@@ -370,10 +396,8 @@ int make_plan(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, siz
     // an 8-bit B read in place comes in 128-column chunks: no 64-wide tiles then
     // The last-wave split is the library's own choice: any explicit split-K, CTA cap or store-path override
     // (argument or environment) turns it off, and so does QGEMM_TAIL_SPLIT=0.
-    const char* tail_env = std::getenv("QGEMM_TAIL_SPLIT");
     allow_tail = allow_tail && !(tuning && (tuning->split_k != 0 || tuning->max_ctas != 0)) &&
-                 env_int("QGEMM_SPLIT_K") == 0 && env_int("QGEMM_MAX_CTAS") == 0 &&
-                 env_int("QGEMM_DIRECT_STORE") == 0 && !(tail_env != nullptr && tail_env[0] == '0');
+                 g_env.split_k == 0 && g_env.max_ctas == 0 && g_env.direct_store == 0 && g_env.tail_split_off == 0;
     p->cfg = choose_config(M, N, std::max(p->kb_total, 1), sms, tuning,
                            (b_direct && p->ti.elem_bytes == 1) ? 128 : 64, allow_tail, p->ti.elem_bytes);
     p->ld_relayout = round_up(K, 16 / p->ti.elem_bytes);
@@ -393,10 +417,11 @@ int make_plan(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, siz
     return QGEMM_OK;
 }
 
-int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size_t lda, const void* B, size_t ldb,
-                  const float* scale_a, const float* scale_b, void* C, size_t ldc, size_t M, size_t N, size_t K,
-                  const qgemm_tuning_t* tuning, cudaStream_t stream, void* const* extra_dsts = nullptr,
-                  int n_extra = 0) {
+// The caller holds g_mutex (scratch, tensor-map cache and the kernels' per-device set-up flags have one owner).
+int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* A, size_t lda, const void* B,
+                         size_t ldb, const float* scale_a, const float* scale_b, void* C, size_t ldc, size_t M,
+                         size_t N, size_t K, const qgemm_tuning_t* tuning, cudaStream_t stream,
+                         void* const* extra_dsts = nullptr, int n_extra = 0) {
     if (n_extra < 0 || n_extra > kMaxExtraDst || (n_extra > 0 && extra_dsts == nullptr)) return QGEMM_ERR_INVALID_ARG;
     if (M == 0 || N == 0) return QGEMM_OK;
     if (C == nullptr || ldc < N) return QGEMM_ERR_INVALID_ARG;
@@ -416,7 +441,6 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     if (K > 0 && (A == nullptr || B == nullptr || lda < K)) return QGEMM_ERR_INVALID_ARG;
     if (K > 0 && ldb < (b_layout == QGEMM_B_K_MAJOR ? K : N)) return QGEMM_ERR_INVALID_ARG;
 
-    std::lock_guard<std::mutex> lock(g_mutex);
     DeviceState* st = nullptr;
     int rc = get_state(&st);
     if (rc != QGEMM_OK) return rc;
@@ -424,7 +448,7 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     // A row-major B whose rows TMA can address is fed to the tensor cores in place (MN-major operand).
     TypeInfo ti0;
     if (!type_info(in_dtype, &ti0)) return QGEMM_ERR_UNSUPPORTED;
-    const bool want_relayout = (tuning && tuning->relayout_b > 0) || env_int("QGEMM_RELAYOUT_B") > 0;
+    const bool want_relayout = (tuning && tuning->relayout_b > 0) || g_env.relayout_b > 0;
     const bool b_direct = b_layout == QGEMM_B_ROW_MAJOR && !want_relayout && K > 0 &&
                           reinterpret_cast<uintptr_t>(B) % 16 == 0 && (ldb * ti0.elem_bytes) % 16 == 0;
     Plan plan;
@@ -467,7 +491,7 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
 
     // The wide pair kernel stores through TMA only: without a C it can address that way, take the 256 x 256 pairs.
     if (plan.cfg.wide && (n_extra > 0 || reinterpret_cast<uintptr_t>(C) % 16 != 0 || (ldc * out_bytes) % 16 != 0 ||
-                          env_int("QGEMM_DIRECT_STORE") != 0))
+                          g_env.direct_store != 0))
         plan.cfg.wide = false;
     const Config& cfg = plan.cfg;
     CUtensorMap ta, tb;
@@ -494,7 +518,8 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     p.idesc = ptx::make_idesc(plan.ti.cfmt, plan.ti.fmt, plan.ti.fmt, static_cast<uint32_t>(cfg.wide ? kPairTileM : tile_m),
                               static_cast<uint32_t>(cfg.bn), b_direct ? 1u : 0u);
     p.b_mn_major = b_direct ? 1 : 0;
-    p.test_skip_kb = std::getenv("QGEMM_TEST_SKIP_LOAD") ? env_int("QGEMM_TEST_SKIP_LOAD") : -1;
+    p.test_skip_kb = g_test_skip_kb;  // one-shot: armed by qgemm_test_arm_skip_load, consumed by this launch
+    g_test_skip_kb = -1;
     p.status = st->status;
 
     int launch_out = plan.out_kind;
@@ -517,7 +542,7 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     // The epilogue goes through shared memory + TMA stores when the destination qualifies for a tensor map.
     CUtensorMap tc;
     std::memset(&tc, 0, sizeof(tc));
-    if (p.c_vec_ok && (n_extra > 0 || env_int("QGEMM_DIRECT_STORE") == 0)) {
+    if (p.c_vec_ok && (n_extra > 0 || g_env.direct_store == 0)) {
         const int map_rc = make_output_map(p.C, M, N, static_cast<uint64_t>(p.ldc), static_cast<uint64_t>(cfg.splits),
                                            launch_out, &tc);
         p.c_tma_ok = (map_rc == QGEMM_OK) ? 1 : 0;
@@ -538,7 +563,7 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     if (work > 0x7fffffffLL) return QGEMM_ERR_UNSUPPORTED;
     int grid = static_cast<int>(std::min<long long>(work, st->sm_count));
     int cap = tuning ? tuning->max_ctas : 0;
-    if (!cap) cap = env_int("QGEMM_MAX_CTAS");
+    if (!cap) cap = g_env.max_ctas;
     if (cap > 0) grid = std::min(grid, cap);
 
     cudaError_t e;
@@ -600,7 +625,18 @@ int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size
     return QGEMM_OK;
 }
 
-// Packed int4 operands: widen both to int8 in their own scratch, then the int8 path (exact int32 sums).
+int gemm_dispatch(int in_dtype, int out_dtype, int b_layout, const void* A, size_t lda, const void* B, size_t ldb,
+                  const float* scale_a, const float* scale_b, void* C, size_t ldc, size_t M, size_t N, size_t K,
+                  const qgemm_tuning_t* tuning, cudaStream_t stream, void* const* extra_dsts = nullptr,
+                  int n_extra = 0) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    return gemm_dispatch_locked(in_dtype, out_dtype, b_layout, A, lda, B, ldb, scale_a, scale_b, C, ldc, M, N, K, tuning,
+                                stream, extra_dsts, n_extra);
+}
+
+// Packed int4 operands: widen both to int8 in their own scratch, then the int8 path (exact int32 sums). The
+// lock is held from the moment the scratch pointer is taken until everything that uses it has been enqueued, so
+// that another thread's larger int4 call cannot reallocate it in between.
 int int4_dispatch(int out_dtype, int b_layout, const void* A, size_t lda, const void* B, size_t ldb,
                   const float* scale_a, const float* scale_b, void* C, size_t ldc, size_t M, size_t N, size_t K,
                   const qgemm_tuning_t* tuning, cudaStream_t stream) {
@@ -611,23 +647,19 @@ int int4_dispatch(int out_dtype, int b_layout, const void* A, size_t lda, const 
     if (M > 0x7fffff00ull || N > 0x7fffff00ull || K > 0x7fffff00ull) return QGEMM_ERR_INVALID_ARG;
     const size_t ldu = round_up(std::max<size_t>(K, 1), 16);
     const size_t a_bytes = round_up(M * ldu, 256), b_bytes = round_up(N * ldu, 256);
-    void* buf = nullptr;
-    {
-        std::lock_guard<std::mutex> lock(g_mutex);
-        DeviceState* st = nullptr;
-        int rc = get_state(&st);
-        if (rc != QGEMM_OK) return rc;
-        rc = ensure_buffer(&st->ws_i4, &st->ws_i4_bytes, a_bytes + b_bytes);
-        if (rc != QGEMM_OK) return rc;
-        buf = st->ws_i4;
-    }
-    int8_t* a8 = static_cast<int8_t*>(buf);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState* st = nullptr;
+    int rc = get_state(&st);
+    if (rc != QGEMM_OK) return rc;
+    rc = ensure_buffer(&st->ws_i4, &st->ws_i4_bytes, a_bytes + b_bytes);
+    if (rc != QGEMM_OK) return rc;
+    int8_t* a8 = static_cast<int8_t*>(st->ws_i4);
     int8_t* b8 = a8 + a_bytes;
-    int rc = unpack_int4_launch(A, lda, a8, ldu, M, K, stream);
+    rc = unpack_int4_launch(A, lda, a8, ldu, M, K, stream);
     if (rc != QGEMM_OK) return rc;
     rc = unpack_int4_launch(B, ldb, b8, ldu, N, K, stream);
     if (rc != QGEMM_OK) return rc;
-    return gemm_dispatch(QGEMM_DTYPE_INT8, out_dtype, QGEMM_B_K_MAJOR, a8, ldu, b8, ldu, scale_a, scale_b, C, ldc, M, N,
+    return gemm_dispatch_locked(QGEMM_DTYPE_INT8, out_dtype, QGEMM_B_K_MAJOR, a8, ldu, b8, ldu, scale_a, scale_b, C, ldc, M, N,
                          K, tuning, stream);
 }
 
@@ -696,8 +728,8 @@ int blockscale_dispatch(int out_dtype, int a_layout, int b_layout, const void* A
     p.n_tiles = static_cast<int>((N + 127) / 128);
     p.kb_total = static_cast<int>((K + 127) / 128);
     p.n_scale_blocks = p.n_tiles;
-    p.group_m = env_int("QGEMM_GROUP_M") > 0
-                    ? env_int("QGEMM_GROUP_M")
+    p.group_m = g_env.group_m > 0
+                    ? g_env.group_m
                     : static_cast<int>(std::max<long long>(4, std::min<long long>(4096, (16ll << 20) / (128ll * p.kb_total * kBM))));
     p.idesc = ptx::make_idesc(1u, 0u, 0u, kBM, 128u);
     p.a_scale = a_scale;
@@ -705,7 +737,7 @@ int blockscale_dispatch(int out_dtype, int a_layout, int b_layout, const void* A
     p.status = st->status;
     std::memset(&tc, 0, sizeof(tc));
     if (reinterpret_cast<uintptr_t>(C) % 16 == 0 && (ldc * out_bytes) % 16 == 0 &&
-        env_int("QGEMM_DIRECT_STORE") == 0)
+        g_env.direct_store == 0)
         p.c_tma_ok = make_output_map(C, M, N, ldc, 1, out_kind, &tc) == QGEMM_OK ? 1 : 0;
 
     const long long work = static_cast<long long>(p.m_tiles) * p.n_tiles;
@@ -715,6 +747,9 @@ int blockscale_dispatch(int out_dtype, int a_layout, int b_layout, const void* A
 }
 
 }  // namespace
+
+std::mutex& dispatch_mutex() { return g_mutex; }
+const EnvSettings& env_settings() { return g_env; }
 
 }  // namespace qgemm
 
@@ -841,15 +876,37 @@ int qgemm_plan_query(int in_dtype, int out_dtype, int b_layout, size_t M, size_t
 
 int qgemm_device_status(int* out4) {
     std::lock_guard<std::mutex> lock(g_mutex);
-    DeviceState* st = nullptr;
-    int rc = get_state(&st);
-    if (rc != QGEMM_OK) return rc;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return QGEMM_ERR_CUDA;
+    if (dev < 0 || dev >= kMaxDevices) return QGEMM_ERR_UNSUPPORTED;
     if (cudaDeviceSynchronize() != cudaSuccess) return QGEMM_ERR_CUDA;
+    // Two sets of status words exist per device: the library's own (allocated with its first GEMM on the device) and
+    // those of the allocation-free entry point (part of the loaded module). Both are read and cleared; neither is
+    // created here, so a process that only ever uses the allocation-free entry point still allocates nothing.
     int host[4] = {0, 0, 0, 0};
-    if (cudaMemcpy(host, st->status, sizeof(host), cudaMemcpyDeviceToHost) != cudaSuccess) return QGEMM_ERR_CUDA;
-    if (host[0] != 0 && cudaMemset(st->status, 0, 64) != cudaSuccess) return QGEMM_ERR_CUDA;
+    if (g_dev[dev].init) {
+        if (cudaMemcpy(host, g_dev[dev].status, sizeof(host), cudaMemcpyDeviceToHost) != cudaSuccess)
+            return QGEMM_ERR_CUDA;
+        if (host[0] != 0 && cudaMemset(g_dev[dev].status, 0, 64) != cudaSuccess) return QGEMM_ERR_CUDA;
+    }
+    int fixed[4] = {0, 0, 0, 0};
+    const int rc = static_status_fetch(fixed);
+    if (rc != QGEMM_OK) return rc;
+    if (host[0] == 0 && fixed[0] != 0) std::memcpy(host, fixed, sizeof(host));
     if (out4 != nullptr) std::memcpy(out4, host, sizeof(host));
     return host[0] != 0 ? QGEMM_ERR_DEVICE_TIMEOUT : QGEMM_OK;
+}
+
+int qgemm_reload_env(void) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    g_env = read_env();
+    return QGEMM_OK;
+}
+
+int qgemm_test_arm_skip_load(int k_block) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    g_test_skip_kb = k_block < 0 ? -1 : k_block;
+    return QGEMM_OK;
 }
 
 int qgemm_shutdown(void) {

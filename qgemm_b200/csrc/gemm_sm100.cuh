@@ -91,9 +91,10 @@ __device__ __forceinline__ void record_error(int* status, int code, int role, in
     }
 }
 
-// Returns false when the wait was abandoned (its own limit, or another role's abort).
+// Returns false when the wait was abandoned (its own limit, or another role's abort). `peer_abort` (CTA-pair
+// kernels; 0 = none) is the cluster address of the other CTA's abort flag, raised together with this CTA's.
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                             int role, int where) {
+                                             int role, int where, uint32_t peer_abort = 0) {
 #pragma unroll 1
     for (int i = 0; i < 128; ++i)
         if (ptx::mbar_try_wait(bar, parity)) return true;
@@ -108,6 +109,7 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
             if (*abort_flag != 0) return false;
             if (clock64() - t0 > limit) {
                 *abort_flag = 1;
+                if (peer_abort != 0) ptx::st_shared_cluster_u32(peer_abort, 1u);
                 record_error(status, DEV_ERR_WAIT_TIMEOUT, role, where);
                 return false;
             }

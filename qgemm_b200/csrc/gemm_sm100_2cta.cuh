@@ -78,6 +78,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const int cluster_id = static_cast<int>(blockIdx.x) >> 1;
     const int n_clusters = static_cast<int>(gridDim.x) >> 1;
     const int total_work = p.total_work;
+    // a wait that runs out raises the abort flag of both CTAs of the pair, so that they leave together
+    const uint32_t peer_abort = ptx::mapa_shared(ptx::smem_u32(const_cast<int*>(abort_flag)), rank ^ 1u);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -125,9 +127,17 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 const int row_a = (t.m_blk * 2 + static_cast<int>(rank)) * 128;
                 const int row_b = t.n_blk * BN + static_cast<int>(rank) * 128;
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, p.status, ROLE_PRODUCER, kb)) {
+                    if (!wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, p.status, ROLE_PRODUCER, kb, peer_abort)) {
                         ok = false;
                         break;
+                    }
+                    if (kb == p.test_skip_kb) {
+                        // test hook: neither CTA fills this slot, so the leader's MMA issuer's wait on it runs out
+                        if (++stage == STAGES) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                        continue;
                     }
                     if (rank == 0) ptx::mbar_arrive_expect_tx(bar_full + stage * 8, 2 * (L::kAStage + L::kBStage));
                     const uint32_t leader_full = ptx::mapa_shared(bar_full + stage * 8, 0);
@@ -159,11 +169,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 const int kb0 = item.kb0, kb1 = item.kb1;
                 const uint32_t acc = it & 1u;
                 const uint32_t acc_phase = (it >> 1) & 1u;
-                if (!wait_bounded(bar_tempty + acc * 8, acc_phase ^ 1u, abort_flag, p.status, ROLE_MMA, -1)) break;
+                if (!wait_bounded(bar_tempty + acc * 8, acc_phase ^ 1u, abort_flag, p.status, ROLE_MMA, -1, peer_abort)) break;
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status, ROLE_MMA, kb)) {
+                    if (!wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status, ROLE_MMA, kb, peer_abort)) {
                         ok = false;
                         break;
                     }
@@ -202,7 +212,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             const TileCoord t = item.t;
             const uint32_t acc = it & 1u;
             const uint32_t acc_phase = (it >> 1) & 1u;
-            if (!wait_bounded(bar_tfull + acc * 8, acc_phase, abort_flag, p.status, ROLE_EPILOGUE, w)) break;
+            if (!wait_bounded(bar_tfull + acc * 8, acc_phase, abort_flag, p.status, ROLE_EPILOGUE, w, peer_abort)) break;
             ptx::tc_fence_after();
             const long long row =
                 (static_cast<long long>(t.m_blk) * 2 + static_cast<long long>(rank)) * 128 + quad * 32 + lane;

@@ -64,6 +64,8 @@ gemm_tcgen05_wide_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
     const int cluster_id = static_cast<int>(blockIdx.x) >> 1;
     const int n_clusters = static_cast<int>(gridDim.x) >> 1;
     const int total_work = p.m_tiles * p.n_tiles;
+    // a wait that runs out raises the abort flag of both CTAs of the pair, so that they leave together
+    const uint32_t peer_abort = ptx::mapa_shared(ptx::smem_u32(const_cast<int*>(abort_flag)), rank ^ 1u);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -104,9 +106,17 @@ gemm_tcgen05_wide_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
                 const int row_a = (t.m_blk * 2 + static_cast<int>(rank)) * 256;
                 const int row_b = t.n_blk * BN + static_cast<int>(rank) * 128;
                 for (int kb = 0; kb < p.kb_total; ++kb) {
-                    if (!wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, p.status, ROLE_PRODUCER, kb)) {
+                    if (!wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, p.status, ROLE_PRODUCER, kb, peer_abort)) {
                         ok = false;
                         break;
+                    }
+                    if (kb == p.test_skip_kb) {
+                        // test hook: neither CTA fills this slot, so the leader's MMA issuer's wait on it runs out
+                        if (++stage == STAGES) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                        continue;
                     }
                     if (rank == 0) ptx::mbar_arrive_expect_tx(bar_full + stage * 8, 2 * (L::kAStage + L::kBStage));
                     const uint32_t leader_full = ptx::mapa_shared(bar_full + stage * 8, 0);
@@ -136,7 +146,7 @@ gemm_tcgen05_wide_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
             bool ok = true;
             for (int w = cluster_id; ok && w < total_work; w += n_clusters, ++it) {
                 for (int kb = 0; ok && kb < p.kb_total; ++kb) {
-                    if (!wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status, ROLE_MMA, kb)) {
+                    if (!wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status, ROLE_MMA, kb, peer_abort)) {
                         ok = false;
                         break;
                     }
@@ -149,7 +159,7 @@ gemm_tcgen05_wide_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
                     for (int j = 0; j < 2; ++j) {
                         if (kb == 0) {
                             // accumulator j of the previous tile must have been drained by both CTAs' epilogues
-                            if (!wait_bounded(bar_tempty + j * 8, (it & 1u) ^ 1u, abort_flag, p.status, ROLE_MMA, -1 - j)) {
+                            if (!wait_bounded(bar_tempty + j * 8, (it & 1u) ^ 1u, abort_flag, p.status, ROLE_MMA, -1 - j, peer_abort)) {
                                 ok = false;
                                 break;
                             }
@@ -183,7 +193,7 @@ gemm_tcgen05_wide_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
         uint32_t out_buf = 0;
         for (int w = cluster_id; w < total_work; w += n_clusters, ++it) {
             const TileCoord t = decode_tile(w, p);
-            if (!wait_bounded(bar_tfull, it & 1u, abort_flag, p.status, ROLE_EPILOGUE, w)) break;
+            if (!wait_bounded(bar_tfull, it & 1u, abort_flag, p.status, ROLE_EPILOGUE, w, peer_abort)) break;
             ptx::tc_fence_after();
 #pragma unroll 1
             for (int j = 0; j < 2; ++j) {

@@ -30,6 +30,7 @@ namespace {
 
 constexpr int kMaxDev = 64;
 constexpr int kEventPool = 256;
+constexpr int kDefaultBands = 8;
 
 struct HostPath {
     bool init = false;
@@ -161,6 +162,17 @@ void host_path_shutdown() {
 
 using namespace qgemm;
 
+extern "C" int qgemm_host_band_schedule(size_t extent, int bands, int shrink, size_t* edges_out, int max_bands) {
+    const std::vector<Band> b = band_schedule(extent, bands > 0 ? bands : kDefaultBands, shrink != 0);
+    const int n = static_cast<int>(b.size());
+    if (edges_out != nullptr)
+        for (int i = 0; i < n && i < max_bands; ++i) {
+            edges_out[2 * i] = b[i].lo;
+            edges_out[2 * i + 1] = b[i].hi;
+        }
+    return n;
+}
+
 extern "C" int qgemm_gemm_host(int in_dtype, int out_dtype, int b_layout, const void* A_host, size_t lda,
                                const void* B_host, size_t ldb, const float* scale_a_host, const float* scale_b_host,
                                void* C_host, size_t ldc, size_t M, size_t N, size_t K, qgemm_stream_t stream_) {
@@ -216,10 +228,9 @@ extern "C" int qgemm_gemm_host(int in_dtype, int out_dtype, int b_layout, const 
         sb_d = scales_d + 1;
     }
 
-    const char* env_bands = std::getenv("QGEMM_HOST_BANDS");
-    const char* env_bands_n = std::getenv("QGEMM_HOST_BANDS_N");
-    const int want_bands = env_bands ? std::max(1, std::atoi(env_bands)) : 8;
-    const int want_bands_n = env_bands_n ? std::max(1, std::atoi(env_bands_n)) : want_bands;
+    const EnvSettings& env = env_settings();
+    const int want_bands = env.host_bands > 0 ? env.host_bands : kDefaultBands;
+    const int want_bands_n = env.host_bands_n > 0 ? env.host_bands_n : want_bands;
     // Only the row bands shrink towards the end: the strips that are left after the last byte has arrived should be
     // whole rows of C (contiguous in host memory), not narrow column blocks.
     std::vector<Band> mb = band_schedule(M, want_bands, true);

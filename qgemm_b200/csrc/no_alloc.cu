@@ -42,7 +42,6 @@ struct StaticDevice {
     int sm_count = 0;
 };
 
-std::mutex g_static_mutex;
 StaticDevice g_static_dev[kMaxDevicesStatic];
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -115,6 +114,19 @@ int encode_partials(void* ptr, uint64_t M, uint64_t N, uint64_t ldw, uint64_t sp
 }
 
 }  // namespace
+
+// Called by qgemm_device_status with the dispatch lock held and the device synchronised.
+int static_status_fetch(int host4[4]) {
+    host4[0] = host4[1] = host4[2] = host4[3] = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return QGEMM_ERR_CUDA;
+    if (dev < 0 || dev >= kMaxDevicesStatic || !g_static_dev[dev].ready) return QGEMM_OK;
+    int* words = g_static_dev[dev].status;
+    if (cudaMemcpy(host4, words, 4 * sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return QGEMM_ERR_CUDA;
+    if (host4[0] != 0 && cudaMemset(words, 0, 4 * sizeof(int)) != cudaSuccess) return QGEMM_ERR_CUDA;
+    return QGEMM_OK;
+}
+
 }  // namespace qgemm
 
 using namespace qgemm;
@@ -161,7 +173,7 @@ extern "C" int qgemm_mix_gemm_splitk_static(int in_dtype, int out_dtype, const v
     const size_t need = static_cast<size_t>(splits) * M * ldw * 4;
     if (need > static_cast<size_t>(QGEMM_STATIC_SCRATCH_BYTES)) return QGEMM_ERR_WORKSPACE;  // beyond the fixed cap
 
-    std::lock_guard<std::mutex> lock(g_static_mutex);
+    std::lock_guard<std::mutex> lock(dispatch_mutex());
     StaticDevice* st = nullptr;
     int rc = static_setup(&st);
     if (rc != QGEMM_OK) return rc;

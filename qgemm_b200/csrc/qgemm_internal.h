@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <cstddef>
 #include <cstdint>
+#include <mutex>
 
 #include "../../include/qgemm.h"
 
@@ -26,6 +27,22 @@ int quantize_launch(int in_dtype, int out_dtype, const void* in, size_t ld_in, v
 // ld_in_elems counts 4-bit elements (even); cols even (int4.cu).
 int unpack_int4_launch(const void* in, size_t ld_in_elems, void* out, size_t ld_out, size_t rows, size_t cols,
                        cudaStream_t stream);
+
+// The one lock of the dispatch layer: the per-device scratch, the tensor-map cache and the per-device "kernel
+// attributes configured" flags of the launchers are only touched while it is held (capi.cu).
+std::mutex& dispatch_mutex();
+
+// QGEMM_* environment variables, read when the library is loaded and again by qgemm_reload_env().
+struct EnvSettings {
+    int tile_n = 0, split_k = 0, group_m = 0, cta_pair = 0, relayout_b = 0, max_ctas = 0, direct_store = 0;
+    int full_a_tile = 0, tail_split_off = 0, k_cluster_off = 0;
+    int host_bands = 0, host_bands_n = 0;  // 0 = default
+};
+const EnvSettings& env_settings();
+
+// Status words of the allocation-free entry point on the current device: copied to host4 and cleared when they
+// record an error; all zero when that entry point has not been used on this device. Allocates nothing (no_alloc.cu).
+int static_status_fetch(int host4[4]);
 
 // Frees the streams, events and device buffers of the host-operand path (host_gemm.cu).
 void host_path_shutdown();

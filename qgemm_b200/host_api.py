@@ -18,32 +18,17 @@ from . import B_K_MAJOR, B_ROW_MAJOR, QgemmError, ERR_INVALID_ARG, _check, _dtyp
 
 
 def band_schedule(extent: int, bands: int = 8, shrink: bool = True):
-    """The bands [lo, hi) ``qgemm_gemm_host`` cuts an extent into: about ``bands`` equal ones made of whole
-    256-wide tiles; with ``shrink`` (the rows of A) the last of them is halved repeatedly down to 256, so that what
-    is left after the final upload is a thin strip's GEMM and download. The columns of B are cut without it."""
+    """The bands [lo, hi) ``qgemm_gemm_host`` cuts an extent into, as the library itself computes them
+    (``qgemm_host_band_schedule``): about ``bands`` equal ones made of whole 256-wide tiles; with ``shrink`` (the
+    rows of A) the last of them is halved repeatedly down to 256, so that what is left after the final upload is a
+    thin strip's GEMM and download. The columns of B are cut without it."""
     if extent <= 0:
         return []
-    bands = max(1, bands)
-    rows = -(-extent // bands)
-    rows = -(-rows // 256) * 256
-    sizes = []
-    left = extent
-    while left > 0:
-        sizes.append(min(rows, left))
-        left -= sizes[-1]
-    last = sizes.pop()
-    while shrink and last > 256:
-        half = -(-(last // 2) // 256) * 256
-        if half >= last:
-            break
-        sizes.append(half)
-        last -= half
-    sizes.append(last)
-    edges, r = [], 0
-    for sz in sizes:
-        edges.append((r, r + sz))
-        r += sz
-    return edges
+    L = lib()
+    n = L.qgemm_host_band_schedule(int(extent), int(bands), 1 if shrink else 0, None, 0)
+    buf = (C.c_size_t * (2 * n))()
+    L.qgemm_host_band_schedule(int(extent), int(bands), 1 if shrink else 0, buf, n)
+    return [(int(buf[2 * i]), int(buf[2 * i + 1])) for i in range(n)]
 
 
 def gemm_host(a_host, b_host, c_host, scale_a=None, scale_b=None, b_kmajor: bool = False, device=None) -> None:

@@ -1,5 +1,5 @@
-"""Host-side logic that needs no GPU: the band schedule of the host-operand pipeline (the Python mirror of what
-qgemm_gemm_host cuts A and B into) and the order in which the bands are uploaded."""
+"""Host-side logic that needs no GPU: the band schedule of the host-operand pipeline -- the library's own C code,
+reached through qgemm_host_band_schedule -- and the order in which the bands are uploaded."""
 import pytest
 
 from qgemm_b200.host_api import band_schedule

@@ -28,7 +28,6 @@ def test_two_ranks_leave_the_whole_matrix_on_both(shape):
     M, n_total, K = shape
     world, port = 2, _free_port()
     env = dict(os.environ)
-    env.pop("QGEMM_TEST_SKIP_LOAD", None)
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "peer_gather_worker.py"), str(r), str(world),
                                str(port), str(M), str(n_total), str(K)], env=env, stdout=subprocess.PIPE,
                               stderr=subprocess.STDOUT, text=True) for r in range(world)]
