@@ -234,6 +234,18 @@ int qgemm_gemm_host(int in_dtype, int out_dtype, int b_layout, const void* A_hos
                     size_t M, size_t N, size_t K, qgemm_stream_t stream);
 
 /*
+ * qgemm_gemm_host with A already in DEVICE memory (A_dev [M,K], 16-byte aligned base and lda * sizeof(T) a multiple
+ * of 16; everything else as above): only B is uploaded, in column bands, and every arriving band is followed by the
+ * GEMM and the download of the column strip of C it completes. For the ranks of a column-sharded product, which all
+ * multiply the same A: each uploads a share of A's rows, they exchange the shares over NVLink (an all-gather), and
+ * A crosses PCIe once per box instead of once per GPU. A_dev is read by work ordered after `stream`. No
+ * counterpart in the reference (single GPU, tests/includes/test_config.h:239-286).
+ */
+int qgemm_gemm_host_resident_a(int in_dtype, int out_dtype, int b_layout, const void* A_dev, size_t lda,
+                               const void* B_host, size_t ldb, const float* scale_a_host, const float* scale_b_host,
+                               void* C_host, size_t ldc, size_t M, size_t N, size_t K, qgemm_stream_t stream);
+
+/*
  * The bands qgemm_gemm_host cuts an extent (the rows of A with shrink != 0, the columns of B with shrink == 0)
  * into: about `bands` (0 = the default, 8) equal bands of whole 256-wide tiles; with `shrink` the last of them is
  * halved repeatedly down to 256. Writes up to max_bands pairs {lo, hi} to edges_out (may be NULL) and returns the

@@ -29,7 +29,7 @@ C_ABI_SYMBOLS = (
     "qgemm_status_string", "qgemm_version", "qgemm_mix_gemm_splitk_static",
     "qgemm_fp8_block_scaled_gemm", "qgemm_quantize", "qgemm_gemm_multi_dst", "qgemm_peer_export",
     "qgemm_peer_open", "qgemm_peer_close", "qgemm_gemm_host", "qgemm_plan_query", "qgemm_host_band_schedule",
-    "qgemm_reload_env", "qgemm_test_arm_skip_load",
+    "qgemm_gemm_host_resident_a", "qgemm_reload_env", "qgemm_test_arm_skip_load",
 )
 
 
@@ -81,6 +81,8 @@ def lib() -> C.CDLL:
         L.qgemm_gemm_host.restype = i
         L.qgemm_plan_query.argtypes = [i, i, i, sz, sz, sz, C.POINTER(Tuning), C.POINTER(C.c_int)]
         L.qgemm_plan_query.restype = i
+        L.qgemm_gemm_host_resident_a.argtypes = L.qgemm_gemm_host.argtypes
+        L.qgemm_gemm_host_resident_a.restype = i
         L.qgemm_host_band_schedule.argtypes = [sz, i, i, C.POINTER(sz), i]
         L.qgemm_host_band_schedule.restype = i
         L.qgemm_reload_env.restype = i

@@ -518,8 +518,7 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
     p.idesc = ptx::make_idesc(plan.ti.cfmt, plan.ti.fmt, plan.ti.fmt, static_cast<uint32_t>(cfg.wide ? kPairTileM : tile_m),
                               static_cast<uint32_t>(cfg.bn), b_direct ? 1u : 0u);
     p.b_mn_major = b_direct ? 1 : 0;
-    p.test_skip_kb = g_test_skip_kb;  // one-shot: armed by qgemm_test_arm_skip_load, consumed by this launch
-    g_test_skip_kb = -1;
+    p.test_skip_kb = take_test_skip_kb();
     p.status = st->status;
 
     int launch_out = plan.out_kind;
@@ -749,6 +748,11 @@ int blockscale_dispatch(int out_dtype, int a_layout, int b_layout, const void* A
 }  // namespace
 
 std::mutex& dispatch_mutex() { return g_mutex; }
+int take_test_skip_kb() {
+    const int kb = g_test_skip_kb;
+    g_test_skip_kb = -1;
+    return kb;
+}
 const EnvSettings& env_settings() { return g_env; }
 
 }  // namespace qgemm

@@ -173,10 +173,15 @@ extern "C" int qgemm_host_band_schedule(size_t extent, int bands, int shrink, si
     return n;
 }
 
-extern "C" int qgemm_gemm_host(int in_dtype, int out_dtype, int b_layout, const void* A_host, size_t lda,
-                               const void* B_host, size_t ldb, const float* scale_a_host, const float* scale_b_host,
-                               void* C_host, size_t ldc, size_t M, size_t N, size_t K, qgemm_stream_t stream_) {
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+namespace {
+
+// A_dev != nullptr: A is already on the device (leading dimension lda, 16-byte aligned rows) and only B is uploaded;
+// every arriving column band of B is followed by the GEMM and download of the column strip of C it completes.
+int host_gemm_impl(int in_dtype, int out_dtype, int b_layout, const void* A_host, const void* A_dev, size_t lda,
+                   const void* B_host, size_t ldb, const float* scale_a_host, const float* scale_b_host,
+                   void* C_host, size_t ldc, size_t M, size_t N, size_t K, cudaStream_t stream) {
+    const bool a_resident = A_dev != nullptr;
+    if (a_resident) A_host = A_dev;  // only tested against null below
     const size_t es = elem_bytes_of(in_dtype), os = elem_bytes_of(out_dtype);
     if (es == 0 || es > 2 || os < 2) return QGEMM_ERR_UNSUPPORTED;
     if (b_layout != QGEMM_B_ROW_MAJOR && b_layout != QGEMM_B_K_MAJOR) return QGEMM_ERR_INVALID_ARG;
@@ -196,7 +201,7 @@ extern "C" int qgemm_gemm_host(int in_dtype, int out_dtype, int b_layout, const 
     const size_t lda_d = round_up(std::max<size_t>(K, 1), align_in);
     const size_t ldb_d = kmajor ? lda_d : round_up(N, align_in);
     const size_t ldc_d = round_up(N, align_out);
-    const size_t a_bytes = round_up(M * lda_d * es, 256);
+    const size_t a_bytes = a_resident ? 0 : round_up(M * lda_d * es, 256);
     const size_t b_bytes = round_up((kmajor ? N : std::max<size_t>(K, 1)) * ldb_d * es, 256);
     const size_t c_bytes = round_up(M * ldc_d * os, 256);
 
@@ -204,8 +209,9 @@ extern "C" int qgemm_gemm_host(int in_dtype, int out_dtype, int b_layout, const 
     HostPath& h = g_host[dev];
     int rc = ensure_host_path(h, a_bytes + b_bytes + c_bytes + 256);
     if (rc != QGEMM_OK) return rc;
-    uint8_t* a_d = static_cast<uint8_t*>(h.arena);
-    uint8_t* b_d = a_d + a_bytes;
+    const uint8_t* a_d = a_resident ? static_cast<const uint8_t*>(A_dev) : static_cast<uint8_t*>(h.arena);
+    const size_t lda_use = a_resident ? lda : lda_d;
+    uint8_t* b_d = static_cast<uint8_t*>(h.arena) + a_bytes;
     uint8_t* c_d = b_d + b_bytes;
     float* scales_d = reinterpret_cast<float*>(c_d + c_bytes);
 
@@ -239,12 +245,13 @@ extern "C" int qgemm_gemm_host(int in_dtype, int out_dtype, int b_layout, const 
         mb.assign(1, Band{0, M});
         nb.assign(1, Band{0, N});
     }
+    if (a_resident) mb.clear();
 
     // One GEMM over the strip C[r0:r1, c0:c1] and its download.
     auto strip = [&](size_t r0, size_t r1, size_t c0, size_t c1, cudaEvent_t operands_ready) -> int {
         QG_CUDA(cudaStreamWaitEvent(h.s_compute, operands_ready, 0));
         const uint8_t* b_ptr = kmajor ? b_d + c0 * ldb_d * es : b_d + c0 * es;
-        const int g = qgemm_gemm_ex(in_dtype, out_dtype, b_layout, a_d + r0 * lda_d * es, lda_d, b_ptr, ldb_d, sa_d, sb_d,
+        const int g = qgemm_gemm_ex(in_dtype, out_dtype, b_layout, a_d + r0 * lda_use * es, lda_use, b_ptr, ldb_d, sa_d, sb_d,
                                     c_d + (r0 * ldc_d + c0) * os, ldc_d, r1 - r0, c1 - c0, K, nullptr, h.s_compute);
         if (g != QGEMM_OK) return g;
         cudaEvent_t done = next_event(h);
@@ -256,7 +263,7 @@ extern "C" int qgemm_gemm_host(int in_dtype, int out_dtype, int b_layout, const 
         return QGEMM_OK;
     };
 
-    size_t rows_up = 0, cols_up = 0;  // rows of A and columns of B that are on the device
+    size_t rows_up = a_resident ? M : 0, cols_up = 0;  // rows of A and columns of B that are on the device
     size_t ia = 0, ib = 0;
     while (ia < mb.size() || ib < nb.size()) {
         // alternate, B first, keeping the loaded part of C close to square; B is complete before the last, thin row
@@ -265,7 +272,7 @@ extern "C" int qgemm_gemm_host(int in_dtype, int out_dtype, int b_layout, const 
         if (take_a) {
             const Band b = mb[ia++];
             if (K > 0)
-                QG_CUDA(cudaMemcpy2DAsync(a_d + b.lo * lda_d * es, lda_d * es,
+                QG_CUDA(cudaMemcpy2DAsync(static_cast<uint8_t*>(h.arena) + b.lo * lda_d * es, lda_d * es,
                                           static_cast<const uint8_t*>(A_host) + b.lo * lda * es, lda * es, K * es,
                                           b.hi - b.lo, cudaMemcpyHostToDevice, h.s_in));
             cudaEvent_t up = next_event(h);
@@ -306,4 +313,22 @@ extern "C" int qgemm_gemm_host(int in_dtype, int out_dtype, int b_layout, const 
     QG_CUDA(cudaEventRecord(h.ev_prev_done, stream));
     h.have_prev = true;
     return QGEMM_OK;
+}
+
+}  // namespace
+
+extern "C" int qgemm_gemm_host(int in_dtype, int out_dtype, int b_layout, const void* A_host, size_t lda,
+                               const void* B_host, size_t ldb, const float* scale_a_host, const float* scale_b_host,
+                               void* C_host, size_t ldc, size_t M, size_t N, size_t K, qgemm_stream_t stream) {
+    return host_gemm_impl(in_dtype, out_dtype, b_layout, A_host, nullptr, lda, B_host, ldb, scale_a_host, scale_b_host,
+                          C_host, ldc, M, N, K, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int qgemm_gemm_host_resident_a(int in_dtype, int out_dtype, int b_layout, const void* A_dev, size_t lda,
+                                          const void* B_host, size_t ldb, const float* scale_a_host,
+                                          const float* scale_b_host, void* C_host, size_t ldc, size_t M, size_t N,
+                                          size_t K, qgemm_stream_t stream) {
+    if (A_dev == nullptr) return QGEMM_ERR_INVALID_ARG;
+    return host_gemm_impl(in_dtype, out_dtype, b_layout, nullptr, A_dev, lda, B_host, ldb, scale_a_host, scale_b_host,
+                          C_host, ldc, M, N, K, static_cast<cudaStream_t>(stream));
 }

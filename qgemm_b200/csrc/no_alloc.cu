@@ -206,7 +206,7 @@ extern "C" int qgemm_mix_gemm_splitk_static(int in_dtype, int out_dtype, const v
     p.status = st->status;
     p.c_vec_ok = 1;
     p.c_tma_ok = 1;
-    p.test_skip_kb = -1;
+    p.test_skip_kb = take_test_skip_kb();
 
     const long long work = static_cast<long long>(p.m_tiles) * p.n_tiles * p.splits;
     if (work > 0x7fffffffLL) return QGEMM_ERR_UNSUPPORTED;

@@ -32,6 +32,10 @@ int unpack_int4_launch(const void* in, size_t ld_in_elems, void* out, size_t ld_
 // attributes configured" flags of the launchers are only touched while it is held (capi.cu).
 std::mutex& dispatch_mutex();
 
+// The K block armed by qgemm_test_arm_skip_load (-1 = none); disarms. Called with the dispatch lock held by the
+// launch that consumes it.
+int take_test_skip_kb();
+
 // QGEMM_* environment variables, read when the library is loaded and again by qgemm_reload_env().
 struct EnvSettings {
     int tile_n = 0, split_k = 0, group_m = 0, cta_pair = 0, relayout_b = 0, max_ctas = 0, direct_store = 0;

@@ -82,3 +82,28 @@ def test_static_scratch_entry_fp8_and_limits(qlib, dev):
     assert rc == q.ERR_INVALID_ARG  # more splits than 128-byte K blocks
     rc, st = q.device_status()
     assert rc == 0, st
+
+
+def test_static_scratch_entry_reports_a_wait_that_ran_out(qlib, oracle, dev):
+    """The entry point keeps its own status words inside the module (it may not allocate any). A bounded wait that
+    runs out in its kernel must reach the caller through qgemm_device_status like any other: the failure is made on
+    the host (the one-shot hook that has the producer leave out one K block's loads), nothing faults, and the next
+    call on the same device is right again."""
+    q = qlib
+    M, N, K, S = 128, 128, 1024, 2  # two CTAs, K blocks 0..3 and 4..7
+    a, b, _, _ = _int8_case(dev, M, N, K, seed=43)
+    got = torch.zeros((M, N), dtype=torch.int32, device=dev)
+    q.mix_gemm_splitk_static(a, b, None, None, got, S)  # set-up call
+    assert q.device_status()[0] == q.OK
+
+    q.lib().qgemm_test_arm_skip_load(2)
+    q.mix_gemm_splitk_static(a, b, None, None, got, S)
+    rc, st = q.device_status()
+    assert rc == q.ERR_DEVICE_TIMEOUT
+    assert st[0] == 1 and st[1] == 0 and st[2] == 2 and st[3] == 2  # CTA 0's MMA issuer, waiting for K block 2
+
+    assert q.device_status()[0] == q.OK  # cleared
+    q.mix_gemm_splitk_static(a, b, None, None, got, S)
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy(), oracle.gemm_i8(a.cpu().numpy(), b.cpu().numpy(), True))
+    assert q.device_status()[0] == q.OK
