@@ -163,6 +163,19 @@ int qgemm_plan_query(int in_dtype, int out_dtype, int b_layout, size_t M, size_t
                      const qgemm_tuning_t* tuning, int* out6);
 
 /*
+ * qgemm_plan_query with more fields: writes min(n_out, QGEMM_PLAN_FIELDS) of
+ *   [0..5] as qgemm_plan_query;
+ *   [6] tile columns of the balanced tiling, 0 = equal tiles. A problem with fewer equal tiles than SMs (small M) gets
+ *       the sixteen-column units of N dealt out over as many tile columns as there are SMs per tile row, so that
+ *       every SM pulls an equal share of B; [1] is then the widest tile the kernel is built for and
+ *   [7] the narrowest tile's width in columns (the widest is 16 more when N / 16 does not divide evenly);
+ *   [8] rows of A loaded per pipeline stage; [9] CTAs launched.
+ */
+#define QGEMM_PLAN_FIELDS 10
+int qgemm_plan_query_ex(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, size_t K,
+                        const qgemm_tuning_t* tuning, int* out, int n_out);
+
+/*
  * Synchronises the current device and copies its four status words to out4:
  * [0] error code (0 = none, 1 = a bounded wait ran out), [1] CTA, [2] role (1 producer, 2 MMA,
  * 3 epilogue), [3] position. Returns QGEMM_ERR_DEVICE_TIMEOUT if [0] != 0. Clears the words.
@@ -175,7 +188,7 @@ int qgemm_device_status(int* out4);
 /*
  * The QGEMM_* environment variables (tuning overrides for experiments: QGEMM_TILE_N, QGEMM_SPLIT_K,
  * QGEMM_GROUP_M, QGEMM_CTA_PAIR, QGEMM_RELAYOUT_B, QGEMM_MAX_CTAS, QGEMM_DIRECT_STORE, QGEMM_FULL_A_TILE,
- * QGEMM_TAIL_SPLIT, QGEMM_K_CLUSTER, QGEMM_HOST_BANDS, QGEMM_HOST_BANDS_N) are read once, when the library is
+ * QGEMM_TAIL_SPLIT, QGEMM_BALANCE, QGEMM_HOST_BANDS, QGEMM_HOST_BANDS_N) are read once, when the library is
  * loaded; this reads them again. Not meant to run concurrently with GEMM calls of other threads.
  */
 int qgemm_reload_env(void);

@@ -29,7 +29,7 @@ C_ABI_SYMBOLS = (
     "qgemm_status_string", "qgemm_version", "qgemm_mix_gemm_splitk_static",
     "qgemm_fp8_block_scaled_gemm", "qgemm_quantize", "qgemm_gemm_multi_dst", "qgemm_peer_export",
     "qgemm_peer_open", "qgemm_peer_close", "qgemm_gemm_host", "qgemm_plan_query", "qgemm_host_band_schedule",
-    "qgemm_gemm_host_resident_a", "qgemm_reload_env", "qgemm_test_arm_skip_load",
+    "qgemm_gemm_host_resident_a", "qgemm_plan_query_ex", "qgemm_reload_env", "qgemm_test_arm_skip_load",
 )
 
 
@@ -81,6 +81,8 @@ def lib() -> C.CDLL:
         L.qgemm_gemm_host.restype = i
         L.qgemm_plan_query.argtypes = [i, i, i, sz, sz, sz, C.POINTER(Tuning), C.POINTER(C.c_int)]
         L.qgemm_plan_query.restype = i
+        L.qgemm_plan_query_ex.argtypes = [i, i, i, sz, sz, sz, C.POINTER(Tuning), C.POINTER(C.c_int), i]
+        L.qgemm_plan_query_ex.restype = i
         L.qgemm_gemm_host_resident_a.argtypes = L.qgemm_gemm_host.argtypes
         L.qgemm_gemm_host_resident_a.restype = i
         L.qgemm_host_band_schedule.argtypes = [sz, i, i, C.POINTER(sz), i]
@@ -412,11 +414,15 @@ def workspace_query(in_dtype: int, b_layout: int, M: int, N: int, K: int, tuning
 
 
 def plan_query(in_dtype: int, out_dtype: int, b_layout: int, M: int, N: int, K: int, tuning: Tuning | None = None):
-    """{tile_m, tile_n, ctas_per_tile, split_k, tail_tiles, tail_slices} the library would use for this shape."""
-    out = (C.c_int * 6)()
-    _check(lib().qgemm_plan_query(in_dtype, out_dtype, b_layout, M, N, K, C.byref(tuning) if tuning else None, out),
-           "qgemm_plan_query")
-    keys = ("tile_m", "tile_n", "ctas_per_tile", "split_k", "tail_tiles", "tail_slices")
+    """The kernel configuration the library would use for this shape (qgemm_plan_query_ex): tile_m, tile_n,
+    ctas_per_tile, split_k, tail_tiles, tail_slices, balanced_tiles (tile columns of the balanced tiling, 0 = equal
+    tiles), min_tile_n, a_rows_per_stage, ctas."""
+    n = 10
+    out = (C.c_int * n)()
+    _check(lib().qgemm_plan_query_ex(in_dtype, out_dtype, b_layout, M, N, K, C.byref(tuning) if tuning else None, out,
+                                     n), "qgemm_plan_query_ex")
+    keys = ("tile_m", "tile_n", "ctas_per_tile", "split_k", "tail_tiles", "tail_slices", "balanced_tiles",
+            "min_tile_n", "a_rows_per_stage", "ctas")
     return dict(zip(keys, list(out)))
 
 

@@ -183,6 +183,9 @@ struct Config {
     bool pair;  // two CTAs per 256x256 tile (bn is then 256 and tiles are counted in 256-row units)
     bool wide;  // pair with 512x256 tiles, both accumulators of a CTA in use (gemm_sm100_2cta_wide.cuh)
     int am;     // rows of A loaded per stage (128; 64 or 32 with the 64-wide tile when M is that small)
+    // Balanced column tiling (GemmParams::bal_units): bal_tiles tile columns of bal_units (+1 for the first
+    // bal_wide) sixteen-column units instead of ceil(N / bn) equal ones. bal_tiles == 0: equal tiles.
+    int bal_tiles, bal_units, bal_wide;
 };
 
 int env_int(const char* name) {
@@ -204,8 +207,10 @@ EnvSettings read_env() {
     e.full_a_tile = env_int("QGEMM_FULL_A_TILE");
     const char* tail = std::getenv("QGEMM_TAIL_SPLIT");
     e.tail_split_off = (tail != nullptr && tail[0] == '0') ? 1 : 0;
-    const char* kc = std::getenv("QGEMM_K_CLUSTER");
-    e.k_cluster_off = (kc != nullptr && kc[0] == '0') ? 1 : 0;
+    const char* bal = std::getenv("QGEMM_BALANCE");
+    e.balance_off = (bal != nullptr && bal[0] == '0') ? 1 : 0;
+    const char* early = std::getenv("QGEMM_EARLY_ISSUE");
+    e.early_issue_off = (early != nullptr && early[0] == '0') ? 1 : 0;
     e.host_bands = std::max(0, env_int("QGEMM_HOST_BANDS"));
     e.host_bands_n = std::max(0, env_int("QGEMM_HOST_BANDS_N"));
     return e;
@@ -274,7 +279,7 @@ double estimate(int bn, bool pair, int splits, size_t M, size_t N, int kb_total,
 }
 
 Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuning_t* tuning, int min_bn = 64,
-                     bool allow_tail = false, int elem_bytes = 1) {
+                     bool allow_tail = false, int elem_bytes = 1, bool allow_balance = false) {
     int want_bn = tuning ? tuning->tile_n : 0;
     int want_split = tuning ? tuning->split_k : 0;
     int want_group = tuning ? tuning->group_m : 0;
@@ -284,7 +289,7 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
     if (!want_group) want_group = g_env.group_m;
     if (!want_pair) want_pair = g_env.cta_pair;
 
-    Config best{256, 1, kb_total, 16, false, false, kBM};
+    Config best{256, 1, kb_total, 16, false, false, kBM, 0, 0, 0};
     double best_t = 1e300;
     struct Cand { int bn; bool pair; };
     const Cand cands[] = {{256, true}, {256, false}, {128, false}, {64, false}};
@@ -316,6 +321,29 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
     }
     // Small M with the narrow tile: load only the rows of A that exist, which leaves room for up to 16 stages so
     // that a short K is wholly in flight at once.
+    // Fewer equal tiles than SMs (skinny M: 16 x 7168 x 2048 has 112 tiles of 64 columns for 148 SMs): deal the
+    // sixteen-column units of N out over as many tile columns as there are SMs per tile row, so that every SM pulls
+    // the same share of B. Measured on B200, FP8 N = 7168, K = 2048, graph replay over cold operands: see the
+    // skinny-shape profile. Only for a K-major B (16-row TMA boxes stack into the operand layout), one split, widths
+    // up to 128 columns, and no explicit tile override.
+    if (allow_balance && !best.pair && best.splits == 1 && want_bn == 0 && want_split == 0 && g_env.balance_off == 0 &&
+        !(tuning && tuning->max_ctas != 0) && g_env.max_ctas == 0) {
+        const int m_tiles = static_cast<int>((M + kBM - 1) / kBM);
+        const long long units = static_cast<long long>((N + 15) / 16);
+        const long long cur_tiles = static_cast<long long>((N + best.bn - 1) / best.bn);
+        const long long slots = sms / std::max(1, m_tiles);
+        if (cur_tiles * m_tiles < sms && slots >= 1) {
+            const long long n_ctas = std::max<long long>(1, std::min<long long>(slots, units / 2));  // >= 32 columns
+            const long long u = units / n_ctas, r = units % n_ctas;
+            const long long wmax = (u + (r > 0 ? 1 : 0)) * 16;
+            if (n_ctas > cur_tiles && wmax <= 128) {
+                best.bal_tiles = static_cast<int>(n_ctas);
+                best.bal_units = static_cast<int>(u);
+                best.bal_wide = static_cast<int>(r);
+                best.bn = wmax <= 64 ? 64 : 128;
+            }
+        }
+    }
     best.am = kBM;
     if (!best.pair && best.bn == 64 && g_env.full_a_tile == 0) best.am = M <= 32 ? 32 : (M <= 64 ? 64 : kBM);
     // Tile rows per scheduling group: as many as keep the group's A panel (rows x K bytes) near 32 MiB, so that
@@ -384,7 +412,8 @@ struct Plan {
 };
 
 int make_plan(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, size_t K, int sms,
-              const qgemm_tuning_t* tuning, Plan* p, bool b_direct = false, bool allow_tail = true) {
+              const qgemm_tuning_t* tuning, Plan* p, bool b_direct = false, bool allow_tail = true,
+              bool allow_balance = true) {
     if (!type_info(in_dtype, &p->ti)) return QGEMM_ERR_UNSUPPORTED;
     p->out_kind = out_kind_of(out_dtype);
     if (p->out_kind < 0) return QGEMM_ERR_UNSUPPORTED;
@@ -399,7 +428,8 @@ int make_plan(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, siz
     allow_tail = allow_tail && !(tuning && (tuning->split_k != 0 || tuning->max_ctas != 0)) &&
                  g_env.split_k == 0 && g_env.max_ctas == 0 && g_env.direct_store == 0 && g_env.tail_split_off == 0;
     p->cfg = choose_config(M, N, std::max(p->kb_total, 1), sms, tuning,
-                           (b_direct && p->ti.elem_bytes == 1) ? 128 : 64, allow_tail, p->ti.elem_bytes);
+                           (b_direct && p->ti.elem_bytes == 1) ? 128 : 64, allow_tail, p->ti.elem_bytes,
+                           allow_balance && !b_direct);
     p->ld_relayout = round_up(K, 16 / p->ti.elem_bytes);
     p->relayout_bytes =
         (b_layout == QGEMM_B_ROW_MAJOR && !b_direct) ? round_up(N * p->ld_relayout * p->ti.elem_bytes, 256) : 0;
@@ -452,7 +482,8 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
     const bool b_direct = b_layout == QGEMM_B_ROW_MAJOR && !want_relayout && K > 0 &&
                           reinterpret_cast<uintptr_t>(B) % 16 == 0 && (ldb * ti0.elem_bytes) % 16 == 0;
     Plan plan;
-    rc = make_plan(in_dtype, out_dtype, b_layout, M, N, K, st->sm_count, tuning, &plan, b_direct, n_extra == 0);
+    rc = make_plan(in_dtype, out_dtype, b_layout, M, N, K, st->sm_count, tuning, &plan, b_direct, n_extra == 0,
+                   n_extra == 0);
     if (rc != QGEMM_OK) return rc;
     if (plan.out_kind == OUT_RAW32 && (scale_a != nullptr || scale_b != nullptr)) return QGEMM_ERR_INVALID_ARG;
     const int out_bytes = (plan.out_kind == OUT_BF16 || plan.out_kind == OUT_F16) ? 2 : 4;
@@ -500,7 +531,9 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
     if (b_direct)  // [K rows, N columns]; one box = 128 bytes of N x one 128-byte K block of rows
         rc = make_operand_map(B, K, N, ldb, in_dtype, 128u / static_cast<uint32_t>(es), &tb);
     else
-        rc = make_operand_map(b_kmajor, N, K, ldb_k, in_dtype, cfg.pair ? 128u : static_cast<uint32_t>(cfg.bn), &tb);
+        rc = make_operand_map(b_kmajor, N, K, ldb_k, in_dtype,
+                              cfg.pair ? 128u : (cfg.bal_tiles > 0 ? static_cast<uint32_t>(cfg.bal_units * 16)
+                                                                   : static_cast<uint32_t>(cfg.bn)), &tb);
     if (rc != QGEMM_OK) return rc;
 
     GemmParams p;
@@ -510,7 +543,9 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
     p.K = static_cast<int>(K);
     const int tile_m = cfg.wide ? kWideTileM : (cfg.pair ? kPairTileM : kBM);
     p.m_tiles = static_cast<int>((M + tile_m - 1) / tile_m);
-    p.n_tiles = static_cast<int>((N + cfg.bn - 1) / cfg.bn);
+    p.n_tiles = cfg.bal_tiles > 0 ? cfg.bal_tiles : static_cast<int>((N + cfg.bn - 1) / cfg.bn);
+    p.bal_units = cfg.bal_tiles > 0 ? cfg.bal_units : 0;
+    p.bal_wide = cfg.bal_tiles > 0 ? cfg.bal_wide : 0;
     p.splits = cfg.splits;
     p.kb_total = plan.kb_total;
     p.kb_per_split = cfg.kb_per_split;
@@ -519,6 +554,7 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
                               static_cast<uint32_t>(cfg.bn), b_direct ? 1u : 0u);
     p.b_mn_major = b_direct ? 1 : 0;
     p.test_skip_kb = take_test_skip_kb();
+    p.early_issue = g_env.early_issue_off ? 0 : 1;
     p.status = st->status;
 
     int launch_out = plan.out_kind;
@@ -541,7 +577,11 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
     // The epilogue goes through shared memory + TMA stores when the destination qualifies for a tensor map.
     CUtensorMap tc;
     std::memset(&tc, 0, sizeof(tc));
-    if (p.c_vec_ok && (n_extra > 0 || g_env.direct_store == 0)) {
+    if (cfg.bal_tiles > 0) {
+        // balanced tiles store from registers; the third tensor-map slot carries B with the wide tiles' box instead
+        rc = make_operand_map(b_kmajor, N, K, ldb_k, in_dtype, static_cast<uint32_t>((cfg.bal_units + 1) * 16), &tc);
+        if (rc != QGEMM_OK) return rc;
+    } else if (p.c_vec_ok && (n_extra > 0 || g_env.direct_store == 0)) {
         const int map_rc = make_output_map(p.C, M, N, static_cast<uint64_t>(p.ldc), static_cast<uint64_t>(cfg.splits),
                                            launch_out, &tc);
         p.c_tma_ok = (map_rc == QGEMM_OK) ? 1 : 0;
@@ -710,7 +750,7 @@ int blockscale_dispatch(int out_dtype, int a_layout, int b_layout, const void* A
         return QGEMM_ERR_ALIGNMENT;
     }
 
-    CUtensorMap ta, tb, tc;
+    CUtensorMap ta, tb;
     rc = make_operand_map(a_k, M, K, lda_k, QGEMM_DTYPE_FP8_E4M3, kBM, &ta);
     if (rc != QGEMM_OK) return rc;
     rc = make_operand_map(b_k, N, K, ldb_k, QGEMM_DTYPE_FP8_E4M3, 128u, &tb);
@@ -734,15 +774,12 @@ int blockscale_dispatch(int out_dtype, int a_layout, int b_layout, const void* A
     p.a_scale = a_scale;
     p.b_scale = b_scale;
     p.status = st->status;
-    std::memset(&tc, 0, sizeof(tc));
-    if (reinterpret_cast<uintptr_t>(C) % 16 == 0 && (ldc * out_bytes) % 16 == 0 &&
-        g_env.direct_store == 0)
-        p.c_tma_ok = make_output_map(C, M, N, ldc, 1, out_kind, &tc) == QGEMM_OK ? 1 : 0;
+    p.c_vec_ok = (reinterpret_cast<uintptr_t>(C) % 16 == 0 && (ldc * out_bytes) % 16 == 0) ? 1 : 0;
 
     const long long work = static_cast<long long>(p.m_tiles) * p.n_tiles;
     if (work > 0x7fffffffLL) return QGEMM_ERR_UNSUPPORTED;
     const int grid = static_cast<int>(std::min<long long>(work, st->sm_count));
-    return launch_fp8_blockscale(out_kind, ta, tb, tc, p, grid, stream) == cudaSuccess ? QGEMM_OK : QGEMM_ERR_CUDA;
+    return launch_fp8_blockscale(out_kind, ta, tb, p, grid, stream) == cudaSuccess ? QGEMM_OK : QGEMM_ERR_CUDA;
 }
 
 }  // namespace
@@ -875,6 +912,31 @@ int qgemm_plan_query(int in_dtype, int out_dtype, int b_layout, size_t M, size_t
     out6[3] = plan.cfg.splits;
     out6[4] = plan.tail_tiles;
     out6[5] = plan.tail_slices;
+    return QGEMM_OK;
+}
+
+int qgemm_plan_query_ex(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, size_t K,
+                        const qgemm_tuning_t* tuning, int* out, int n_out) {
+    if (out == nullptr || n_out < 0) return QGEMM_ERR_INVALID_ARG;
+    int sms = 148;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_dev[dev].init)
+            sms = g_dev[dev].sm_count;
+    }
+    Plan plan;
+    const int rc = make_plan(in_dtype == QGEMM_DTYPE_INT4 ? QGEMM_DTYPE_INT8 : in_dtype, out_dtype, b_layout, M, N,
+                             std::max<size_t>(K, 1), sms, tuning, &plan);
+    if (rc != QGEMM_OK) return rc;
+    const Config& c = plan.cfg;
+    const int tile_m = c.wide ? kWideTileM : (c.pair ? kPairTileM : kBM);
+    const long long tiles_n = c.bal_tiles > 0 ? c.bal_tiles : static_cast<long long>((N + c.bn - 1) / c.bn);
+    const long long ctas = static_cast<long long>((M + tile_m - 1) / tile_m) * tiles_n * c.splits * (c.pair ? 2 : 1);
+    const int vals[QGEMM_PLAN_FIELDS] = {
+        tile_m, c.bn, c.pair ? 2 : 1, c.splits, plan.tail_tiles, plan.tail_slices, c.bal_tiles,
+        c.bal_tiles > 0 ? c.bal_units * 16 : c.bn, c.am, static_cast<int>(std::min<long long>(ctas, sms))};
+    for (int i = 0; i < n_out && i < QGEMM_PLAN_FIELDS; ++i) out[i] = vals[i];
     return QGEMM_OK;
 }
 

@@ -226,10 +226,10 @@ struct BlockScaleParams {
     const float* a_scale;  // [kb_total][M]
     const float* b_scale;  // [kb_total][n_scale_blocks]
     int* status;
-    int c_tma_ok;
+    int c_vec_ok;  // C base and ldc allow 16-byte vector stores
 };
-cudaError_t launch_fp8_blockscale(int out_kind, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
-                                  const BlockScaleParams& p, int grid, cudaStream_t stream);
+cudaError_t launch_fp8_blockscale(int out_kind, const CUtensorMap& ta, const CUtensorMap& tb, const BlockScaleParams& p,
+                                  int grid, cudaStream_t stream);
 
 // Adds up the K slices of the last-wave tiles (splitk_reduce.cu): `slots` tiles stored as
 // [splits][slots * 256][256] 32-bit partial sums; `tiles` locates slot i in C (m_tiles, n_tiles, group_m,

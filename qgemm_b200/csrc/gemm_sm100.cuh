@@ -60,6 +60,14 @@ struct GemmParams {
     int tail_kb_per_slice;
     int total_work;
     int tile_offset;  // added to the tile number by decode_tile (the pass that sums the slices locates slot i with it)
+    // Balanced column tiling (lone-CTA kernel, K-major B, one wave): instead of n_tiles equal tiles of BN columns,
+    // the N / 16 sixteen-column units are dealt out over n_tiles tiles, tile n getting bal_units units, the first
+    // bal_wide tiles one more, so that a problem with fewer equal tiles than SMs still gives every SM a tile (and
+    // the same share of B to pull from HBM). bal_units == 0: equal tiles. Widths never exceed the kernel's BN.
+    int bal_units;
+    int bal_wide;
+    int early_issue;  // lone-CTA kernel: warp 0 requests the first tile's first ring of K blocks before the CTA-wide
+                      // set-up barrier
     int test_skip_kb;  // failure-detection test hook: the producer leaves out the loads of this K block (-1 = none),
                        // so the consumer's bounded wait runs out and the kernel returns through its error path
 };
@@ -138,6 +146,17 @@ __device__ __forceinline__ TileCoord decode_tile(int w, const GemmParams& p) {
     t.n_blk = r / gm;
     t.m_blk = first_m + (r - t.n_blk * gm);
     return t;
+}
+
+// Column origin and width of tile column n_blk (see GemmParams::bal_units).
+__device__ __forceinline__ void tile_columns(const GemmParams& p, int n_blk, int bn, int& col0, int& width) {
+    if (p.bal_units > 0) {
+        col0 = (n_blk * p.bal_units + min(n_blk, p.bal_wide)) * 16;
+        width = (p.bal_units + (n_blk < p.bal_wide ? 1 : 0)) * 16;
+    } else {
+        col0 = n_blk * bn;
+        width = bn;
+    }
 }
 
 // One work item of the CTA-pair kernel: a whole tile, or one K slice of a last-wave tile.
@@ -344,23 +363,73 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int warp = static_cast<int>(threadIdx.x) >> 5;
     const int lane = static_cast<int>(threadIdx.x) & 31;
     const int total_work = p.m_tiles * p.n_tiles * p.splits;
+    // The successor in the stream may be scheduled as soon as SMs free up; it waits for this grid's completion at its
+    // own griddepcontrol.wait. Signalled first, so that warp 0's early wait below does not hold it back.
+    ptx::pdl_launch_dependents();
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            ptx::mbar_init(bar_full + s * 8, 1);
-            ptx::mbar_init(bar_empty + s * 8, 1);
+    // The loads of one K block of one tile into ring slot `stage`.
+    auto load_stage = [&](const TileCoord& t, int col0, int width, int kb, uint32_t stage) {
+        const uint32_t full = bar_full + stage * 8;
+        if (kb == p.test_skip_kb) {
+            // test hook: this slot is never filled, so the MMA issuer's wait on it runs out
+        } else if (p.bal_units > 0) {
+            // tile of `width` columns: tmap_b's box has the narrow tiles' rows, and tmap_c (no TMA store in this
+            // mode, see the epilogue) is the same B with a box sixteen rows taller for the wide tiles
+            ptx::mbar_arrive_expect_tx(full, L::kAStage + width * 128);
+            ptx::tma_load_2d(smem_a + stage * L::kAStage, &tmap_a, full, kb * BK, t.m_blk * kBM);
+            ptx::tma_load_2d(smem_b + stage * L::kBStage, width == p.bal_units * 16 ? &tmap_b : &tmap_c, full, kb * BK,
+                             col0);
+        } else if (p.b_mn_major) {
+            ptx::mbar_arrive_expect_tx(full, L::kAStage + L::kBStage);
+            ptx::tma_load_2d(smem_a + stage * L::kAStage, &tmap_a, full, kb * BK, t.m_blk * kBM);
+            // one box per 128-byte chunk of N: [BK rows of K] x [CHUNK columns]
+            constexpr int CHUNK = 128 / ELT;
+#pragma unroll
+            for (int j = 0; j < BN / CHUNK; ++j)
+                ptx::tma_load_2d(smem_b + stage * L::kBStage + j * (BK * 128), &tmap_b, full, col0 + j * CHUNK,
+                                 kb * BK);
+        } else {
+            ptx::mbar_arrive_expect_tx(full, L::kAStage + L::kBStage);
+            ptx::tma_load_2d(smem_a + stage * L::kAStage, &tmap_a, full, kb * BK, t.m_blk * kBM);
+            ptx::tma_load_2d(smem_b + stage * L::kBStage, &tmap_b, full, kb * BK, col0);
         }
-        for (int a = 0; a < 2; ++a) {
-            ptx::mbar_init(bar_tfull + a * 8, 1);
-            ptx::mbar_init(bar_tempty + a * 8, 4);
-        }
-        *abort_flag = 0;
-        ptx::fence_barrier_init();
+    };
+    // Ring slots of this CTA's first tile that thread 0 fills straight after initialising the barriers, before the
+    // CTA-wide set-up barrier: the first bytes are on their way while tensor memory is still being allocated.
+    int early = 0;
+    if (static_cast<int>(blockIdx.x) < total_work) {
+        const TileCoord t0 = decode_tile(blockIdx.x, p);
+        const int kb0 = t0.split * p.kb_per_split;
+        early = p.early_issue ? min(STAGES, min(p.kb_total, kb0 + p.kb_per_split) - kb0) : 0;
     }
-    if (warp == 0 && lane == 0) {
-        ptx::prefetch_tensormap(&tmap_a);
-        ptx::prefetch_tensormap(&tmap_b);
-        if (p.c_tma_ok) ptx::prefetch_tensormap(&tmap_c);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int s = 0; s < STAGES; ++s) {
+                ptx::mbar_init(bar_full + s * 8, 1);
+                ptx::mbar_init(bar_empty + s * 8, 1);
+            }
+            for (int a = 0; a < 2; ++a) {
+                ptx::mbar_init(bar_tfull + a * 8, 1);
+                ptx::mbar_init(bar_tempty + a * 8, 4);
+            }
+            *abort_flag = 0;
+            ptx::fence_barrier_init();
+            ptx::prefetch_tensormap(&tmap_a);
+            ptx::prefetch_tensormap(&tmap_b);
+            if (p.c_tma_ok || p.bal_units > 0) ptx::prefetch_tensormap(&tmap_c);
+        }
+        __syncwarp();
+        if (p.early_issue && early > 0) {
+            // lane i issues the loads of K block i of this CTA's first tile: the whole first ring is requested by two
+            // warp-wide instructions instead of a loop in one thread
+            ptx::pdl_wait();  // the operands may be the predecessor's output
+            const TileCoord t0 = decode_tile(blockIdx.x, p);
+            int col0, width;
+            tile_columns(p, t0.n_blk, BN, col0, width);
+            const int kb0 = t0.split * p.kb_per_split;
+            for (int i = lane; i < early; i += 32) load_stage(t0, col0, width, kb0 + i, static_cast<uint32_t>(i));
+        }
     }
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
@@ -370,8 +439,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // Everything above touched no global memory; from here on the predecessor's results are needed.
-    ptx::pdl_launch_dependents();
+    // Apart from warp 0's early loads, everything above touched no global memory; from here on the predecessor's
+    // results are needed.
     ptx::pdl_wait();
 
     if (warp == 0) {
@@ -383,27 +452,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 const TileCoord t = decode_tile(w, p);
                 const int kb0 = t.split * p.kb_per_split;
                 const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                int col0, width;
+                tile_columns(p, t.n_blk, BN, col0, width);
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, p.status, ROLE_PRODUCER, kb)) {
-                        ok = false;
-                        break;
-                    }
-                    const uint32_t full = bar_full + stage * 8;
-                    if (kb == p.test_skip_kb) {
-                        // test hook: this slot is never filled, so the MMA issuer's wait on it runs out
-                    } else if (p.b_mn_major) {
-                        ptx::mbar_arrive_expect_tx(full, L::kAStage + L::kBStage);
-                        ptx::tma_load_2d(smem_a + stage * L::kAStage, &tmap_a, full, kb * BK, t.m_blk * kBM);
-                        // one box per 128-byte chunk of N: [BK rows of K] x [CHUNK columns]
-                        constexpr int CHUNK = 128 / ELT;
-#pragma unroll
-                        for (int j = 0; j < BN / CHUNK; ++j)
-                            ptx::tma_load_2d(smem_b + stage * L::kBStage + j * (BK * 128), &tmap_b, full,
-                                             t.n_blk * BN + j * CHUNK, kb * BK);
-                    } else {
-                        ptx::mbar_arrive_expect_tx(full, L::kAStage + L::kBStage);
-                        ptx::tma_load_2d(smem_a + stage * L::kAStage, &tmap_a, full, kb * BK, t.m_blk * kBM);
-                        ptx::tma_load_2d(smem_b + stage * L::kBStage, &tmap_b, full, kb * BK, t.n_blk * BN);
+                    const bool already = (w == static_cast<int>(blockIdx.x)) && (kb - kb0 < early);
+                    if (!already) {
+                        if (!wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, p.status, ROLE_PRODUCER, kb)) {
+                            ok = false;
+                            break;
+                        }
+                        load_stage(t, col0, width, kb, stage);
                     }
                     if (++stage == STAGES) {
                         stage = 0;
@@ -427,6 +485,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 if (!wait_bounded(bar_tempty + acc * 8, acc_phase ^ 1u, abort_flag, p.status, ROLE_MMA, -1)) break;
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
+                uint32_t idesc = p.idesc;
+                if (p.bal_units > 0) {  // the instruction's N is this tile's width
+                    int col0, width;
+                    tile_columns(p, t.n_blk, BN, col0, width);
+                    idesc = (idesc & ~(0x3fu << 17)) | (static_cast<uint32_t>(width >> 3) << 17);
+                }
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status, ROLE_MMA, kb)) {
                         ok = false;
@@ -442,7 +506,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const uint32_t b_step = p.b_mn_major ? static_cast<uint32_t>((32 / ELT) * 128 / 16) : 2u;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per 128-byte block
-                        ptx::umma_ss<KIND>(d_tmem, a_desc + 2u * k, b_desc + b_step * k, p.idesc,
+                        ptx::umma_ss<KIND>(d_tmem, a_desc + 2u * k, b_desc + b_step * k, idesc,
                                            (kb > kb0 || k > 0) ? 1u : 0u);
                     }
                     ptx::tc_commit(bar_empty + stage * 8);
@@ -474,7 +538,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint8_t* c_base = reinterpret_cast<uint8_t*>(p.C) +
                               static_cast<long long>(t.split) * p.split_stride * OutBytes<OUT>::value;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
-            if (p.c_tma_ok) {
+            if (p.bal_units > 0) {
+                // balanced tiles end at any multiple of 16 columns: registers -> global, clipped at the tile's end;
+                // a warp whose 32 rows are all beyond M has nothing to read or store
+                int col0, width;
+                tile_columns(p, t.n_blk, BN, col0, width);
+                const int n_end = min(p.N, col0 + width);
+                if (t.m_blk * kBM + quad * 32 < p.M) {
+#pragma unroll 1
+                    for (int c = 0; c < BN / 32; ++c) {
+                        const int n0 = col0 + c * 32;
+                        if (n0 >= n_end) break;  // warp-uniform
+                        uint32_t v[32];
+                        ptx::tmem_ld_32x32b_x32(t_addr + c * 32, v);
+                        ptx::tmem_ld_wait();
+                        if (row < p.M)
+                            store_chunk<KIND, OUT>(c_base, p.ldc, row, n0, min(32, n_end - n0), p.c_vec_ok != 0, v, alpha);
+                    }
+                }
+            } else if (p.c_tma_ok) {
                 epilogue_tma<KIND, OUT, BN>(&tmap_c, t_addr, t.m_blk * kBM + quad * 32, p.M, t.n_blk * BN, p.N, t.split,
                                             smem_base + L::kOutOffset + (warp - 2) * 8192, lane, alpha, out_buf);
             } else {
