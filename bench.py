@@ -103,6 +103,8 @@ def parse_args():
                     help="skip the burst / 3-second sustained timing of the GEMM kernel alone")
     ap.add_argument("--no-c5", action="store_true", help="skip the column-sharded int8 block")
     ap.add_argument("--no-configs", action="store_true", help="skip the short measurements of the other configurations")
+    ap.add_argument("--configs", default="", help="comma-separated subset of the other configurations to measure "
+                    "(names of WORKLOADS, or hbm_passes); default: all of them")
     ap.add_argument("--no-gather", action="store_true", help="c5, N > 1: skip the all-gather and fused-gather timings")
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--split-k", type=int, default=0)
@@ -1002,17 +1004,19 @@ def main():
     configs = None
     if world == 1 and not args.no_configs:
         configs = {}
+        wanted = [n for n in args.configs.split(",") if n] or CONFIG_BLOCK + ["hbm_passes"]
         for name in CONFIG_BLOCK:
-            if name == args.workload:
+            if name == args.workload or name not in wanted:
                 continue
             try:
                 configs[name] = run_config(ctx, args, name)
             except Exception as exc:
                 configs[name] = {"error": repr(exc)[:300]}
-        try:
-            configs["hbm_passes"] = run_hbm_passes(ctx, args)
-        except Exception as exc:
-            configs["hbm_passes"] = {"error": repr(exc)[:300]}
+        if "hbm_passes" in wanted:
+            try:
+                configs["hbm_passes"] = run_hbm_passes(ctx, args)
+            except Exception as exc:
+                configs["hbm_passes"] = {"error": repr(exc)[:300]}
 
     ctx.sampler.stop()
     rc, st = q.device_status()

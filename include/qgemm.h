@@ -165,9 +165,10 @@ int qgemm_plan_query(int in_dtype, int out_dtype, int b_layout, size_t M, size_t
 /*
  * qgemm_plan_query with more fields: writes min(n_out, QGEMM_PLAN_FIELDS) of
  *   [0..5] as qgemm_plan_query;
- *   [6] tile columns of the balanced tiling, 0 = equal tiles. A problem with fewer equal tiles than SMs (small M) gets
- *       the sixteen-column units of N dealt out over as many tile columns as there are SMs per tile row, so that
- *       every SM pulls an equal share of B; [1] is then the widest tile the kernel is built for and
+ *   [6] tile columns of the balanced tiling, 0 = equal tiles. With QGEMM_BALANCE=1 in the environment a problem with
+ *       fewer equal tiles than SMs (small M) gets the sixteen-column units of N dealt out over as many tile columns as
+ *       there are SMs per tile row, so that every SM pulls an equal share of B (off by default: measured, it does not
+ *       pay on B200); [1] is then the widest tile the kernel is built for and
  *   [7] the narrowest tile's width in columns (the widest is 16 more when N / 16 does not divide evenly);
  *   [8] rows of A loaded per pipeline stage; [9] CTAs launched.
  */
@@ -296,6 +297,12 @@ int qgemm_gemm_multi_dst(int in_dtype, int out_dtype, int b_layout, const void* 
  *   qgemm_peer_close   unmaps it; call before the exporting process frees the allocation.
  */
 #define QGEMM_PEER_HANDLE_BYTES 64
+/* A device allocation of its own (cudaMalloc) for a buffer that will be exported: an exported handle covers the
+ * whole allocation that contains the buffer, so a buffer carved out of a framework's caching allocator would expose
+ * its neighbours in the same block to every process that maps it. Free with qgemm_peer_free after every peer has
+ * closed its mapping. */
+int qgemm_peer_alloc(size_t bytes, void** ptr_out);
+int qgemm_peer_free(void* ptr);
 int qgemm_peer_export(const void* ptr, void* handle_out, size_t* offset_out);
 int qgemm_peer_open(const void* handle, void** base_out);
 int qgemm_peer_close(void* base);

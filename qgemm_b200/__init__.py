@@ -29,7 +29,7 @@ C_ABI_SYMBOLS = (
     "qgemm_status_string", "qgemm_version", "qgemm_mix_gemm_splitk_static",
     "qgemm_fp8_block_scaled_gemm", "qgemm_quantize", "qgemm_gemm_multi_dst", "qgemm_peer_export",
     "qgemm_peer_open", "qgemm_peer_close", "qgemm_gemm_host", "qgemm_plan_query", "qgemm_host_band_schedule",
-    "qgemm_gemm_host_resident_a", "qgemm_plan_query_ex", "qgemm_reload_env", "qgemm_test_arm_skip_load",
+    "qgemm_gemm_host_resident_a", "qgemm_plan_query_ex", "qgemm_peer_alloc", "qgemm_peer_free", "qgemm_reload_env", "qgemm_test_arm_skip_load",
 )
 
 
@@ -90,6 +90,10 @@ def lib() -> C.CDLL:
         L.qgemm_reload_env.restype = i
         L.qgemm_test_arm_skip_load.argtypes = [i]
         L.qgemm_test_arm_skip_load.restype = i
+        L.qgemm_peer_alloc.argtypes = [sz, C.POINTER(C.c_void_p)]
+        L.qgemm_peer_alloc.restype = i
+        L.qgemm_peer_free.argtypes = [vp]
+        L.qgemm_peer_free.restype = i
         L.qgemm_peer_export.argtypes = [vp, vp, C.POINTER(sz)]
         L.qgemm_peer_export.restype = i
         L.qgemm_peer_open.argtypes = [vp, C.POINTER(C.c_void_p)]
@@ -333,6 +337,40 @@ def gemm_multi_dst(a, b, scale_a, scale_b, dst_ptrs, ldc: int, out_dtype, n_cols
             max(a.stride(0), K), b.data_ptr(), max(b.stride(0), b.shape[1]), sa, sb, arr, len(dst_ptrs), int(ldc),
             M, N, K, _stream_ptr(a))
     _check(rc, "qgemm_gemm_multi_dst")
+
+
+class _DeviceBlock:
+    """A cudaMalloc'ed block of its own, seen by torch through the CUDA array interface (no copy); freed when the
+    last tensor that views it is gone and :meth:`free` has been called, or at interpreter exit."""
+
+    def __init__(self, nbytes: int, device):
+        torch = _torch()
+        self.device = torch.device(device)
+        ptr = C.c_void_p(0)
+        with torch.cuda.device(self.device):
+            _check(lib().qgemm_peer_alloc(int(nbytes), C.byref(ptr)), "qgemm_peer_alloc")
+        self.ptr, self.nbytes = int(ptr.value), int(nbytes)
+        self.__cuda_array_interface__ = {"shape": (self.nbytes,), "typestr": "|u1", "data": (self.ptr, False),
+                                         "version": 2}
+
+    def free(self) -> None:
+        if self.ptr:
+            with _torch().cuda.device(self.device):
+                _check(lib().qgemm_peer_free(C.c_void_p(self.ptr)), "qgemm_peer_free")
+            self.ptr = 0
+
+
+def peer_tensor(shape, dtype, device):
+    """(tensor, block): a tensor of ``shape`` / ``dtype`` in a device allocation of its own, so that exporting it with
+    :func:`peer_export` exposes nothing else of this process. Call ``block.free()`` when every peer has unmapped it
+    and the tensor is no longer used."""
+    torch = _torch()
+    n = 1
+    for d in shape:
+        n *= int(d)
+    block = _DeviceBlock(max(1, n * torch.empty((), dtype=dtype).element_size()), device)
+    flat = torch.as_tensor(block, device=torch.device(device))
+    return flat.view(dtype).view(*shape), block
 
 
 def peer_export(t):

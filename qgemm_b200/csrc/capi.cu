@@ -207,10 +207,7 @@ EnvSettings read_env() {
     e.full_a_tile = env_int("QGEMM_FULL_A_TILE");
     const char* tail = std::getenv("QGEMM_TAIL_SPLIT");
     e.tail_split_off = (tail != nullptr && tail[0] == '0') ? 1 : 0;
-    const char* bal = std::getenv("QGEMM_BALANCE");
-    e.balance_off = (bal != nullptr && bal[0] == '0') ? 1 : 0;
-    const char* early = std::getenv("QGEMM_EARLY_ISSUE");
-    e.early_issue_off = (early != nullptr && early[0] == '0') ? 1 : 0;
+    e.balance = env_int("QGEMM_BALANCE") > 0 ? 1 : 0;
     e.host_bands = std::max(0, env_int("QGEMM_HOST_BANDS"));
     e.host_bands_n = std::max(0, env_int("QGEMM_HOST_BANDS_N"));
     return e;
@@ -323,10 +320,12 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
     // that a short K is wholly in flight at once.
     // Fewer equal tiles than SMs (skinny M: 16 x 7168 x 2048 has 112 tiles of 64 columns for 148 SMs): deal the
     // sixteen-column units of N out over as many tile columns as there are SMs per tile row, so that every SM pulls
-    // the same share of B. Measured on B200, FP8 N = 7168, K = 2048, graph replay over cold operands: see the
-    // skinny-shape profile. Only for a K-major B (16-row TMA boxes stack into the operand layout), one split, widths
-    // up to 128 columns, and no explicit tile override.
-    if (allow_balance && !best.pair && best.splits == 1 && want_bn == 0 && want_split == 0 && g_env.balance_off == 0 &&
+    // the same share of B. Off unless QGEMM_BALANCE=1: measured on B200 (FP8, N = 7168, K = 2048, graph replay over
+    // cold operands) it does not pay -- M = 16: 6.62 us either way (the streaming phase of a CTA shortens by 12 %, but
+    // with every SM taken the successor's CTAs can no longer start their set-up early); M = 64 and 256: 7.9 vs 6.8 and
+    // 11.1 vs 8.1 us, because every further tile column re-reads A from L2 and the tiles' odd widths rule out the
+    // TMA-store epilogue. Only for a K-major B, one split, widths up to 128 columns, no explicit tile override.
+    if (allow_balance && !best.pair && best.splits == 1 && want_bn == 0 && want_split == 0 && g_env.balance != 0 &&
         !(tuning && tuning->max_ctas != 0) && g_env.max_ctas == 0) {
         const int m_tiles = static_cast<int>((M + kBM - 1) / kBM);
         const long long units = static_cast<long long>((N + 15) / 16);
@@ -345,7 +344,7 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
         }
     }
     best.am = kBM;
-    if (!best.pair && best.bn == 64 && g_env.full_a_tile == 0) best.am = M <= 32 ? 32 : (M <= 64 ? 64 : kBM);
+    if (!best.pair && best.bn == 64 && g_env.full_a_tile == 0) best.am = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : kBM));
     // Tile rows per scheduling group: as many as keep the group's A panel (rows x K bytes) near 32 MiB, so that
     // it stays in L2 while the B panels stream past it.
     // 512 x 256 tiles per CTA pair instead of 256 x 256: a quarter fewer operand bytes from L2 per flop (clock, on a
@@ -554,7 +553,6 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
                               static_cast<uint32_t>(cfg.bn), b_direct ? 1u : 0u);
     p.b_mn_major = b_direct ? 1 : 0;
     p.test_skip_kb = take_test_skip_kb();
-    p.early_issue = g_env.early_issue_off ? 0 : 1;
     p.status = st->status;
 
     int launch_out = plan.out_kind;
@@ -750,7 +748,7 @@ int blockscale_dispatch(int out_dtype, int a_layout, int b_layout, const void* A
         return QGEMM_ERR_ALIGNMENT;
     }
 
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, tc;
     rc = make_operand_map(a_k, M, K, lda_k, QGEMM_DTYPE_FP8_E4M3, kBM, &ta);
     if (rc != QGEMM_OK) return rc;
     rc = make_operand_map(b_k, N, K, ldb_k, QGEMM_DTYPE_FP8_E4M3, 128u, &tb);
@@ -774,12 +772,14 @@ int blockscale_dispatch(int out_dtype, int a_layout, int b_layout, const void* A
     p.a_scale = a_scale;
     p.b_scale = b_scale;
     p.status = st->status;
-    p.c_vec_ok = (reinterpret_cast<uintptr_t>(C) % 16 == 0 && (ldc * out_bytes) % 16 == 0) ? 1 : 0;
+    std::memset(&tc, 0, sizeof(tc));
+    if (reinterpret_cast<uintptr_t>(C) % 16 == 0 && (ldc * out_bytes) % 16 == 0 && g_env.direct_store == 0)
+        p.c_tma_ok = make_output_map(C, M, N, ldc, 1, out_kind, &tc) == QGEMM_OK ? 1 : 0;
 
     const long long work = static_cast<long long>(p.m_tiles) * p.n_tiles;
     if (work > 0x7fffffffLL) return QGEMM_ERR_UNSUPPORTED;
     const int grid = static_cast<int>(std::min<long long>(work, st->sm_count));
-    return launch_fp8_blockscale(out_kind, ta, tb, p, grid, stream) == cudaSuccess ? QGEMM_OK : QGEMM_ERR_CUDA;
+    return launch_fp8_blockscale(out_kind, ta, tb, tc, p, grid, stream) == cudaSuccess ? QGEMM_OK : QGEMM_ERR_CUDA;
 }
 
 }  // namespace

@@ -12,18 +12,16 @@
 // one block only. The epilogue warps drain each partial with tcgen05.ld and fold it into fp32
 // registers with one fused multiply-add per element, scale = a_scale * b_scale, while the tensor
 // cores already work on the next blocks in the other partials -- the rescale in CUDA cores that the
-// reference does per K tile in registers. After the last block the registers are rounded once and
-// stored (64 or 128 contiguous bytes per row and warp).
+// reference does per K tile in registers. After the last block the registers are rounded and leave
+// through the same swizzled-staging + TMA-store path as the plain GEMM.
 //
 // Barriers: full[stage] (TMA bytes landed), done[blk % 12] (one tcgen05.commit per K block: the block has been
-// multiplied, which both frees its stage and publishes its partial), pempty[partial] (all sixteen rescale warps
-// have the partial in registers). Loads run the whole ring ahead; the MMA issuer waits for a free partial.
-//
-// What bounds the kernel is the latency of one drain (wake on done[], tcgen05.ld, wait, hand the partial back), not its
-// arithmetic: a rescale warp that drains one block per round trip spends about 500 cycles per block, twice the 256
-// cycles the tensor cores need for it. So each rescale warp drains TWO blocks per round trip (both loads in flight
-// before the one tcgen05.wait::ld), and the 128 columns of a tile are spread over four warps per lane quadrant
-// (32 columns each) so that two blocks' worth of registers fit.
+// multiplied, which both frees its stage and publishes its partial), pempty[partial] (all eight rescale warps
+// have the partial in registers). Loads run the whole ring ahead (the producer waits for a free stage only); the MMA
+// issuers wait for a free partial -- with the wait in the producer a TMA round trip sat inside the partial's cycle
+// (measured 7 % slower at 4096 x 7168 x 7168).
+// Two warps issue the MMAs, one the even K blocks and one the odd ones (blocks go into different partials, so their
+// MMAs are independent): measured 12-16 % faster on shapes below about 4096^3, no change above.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -38,19 +36,17 @@ constexpr int kBsBN = 128;
 constexpr int kBsStages = 6;
 constexpr int kBsPartials = 4;                           // partial accumulators in flight (4 x 128 = all 512 columns)
 constexpr int kBsDone = 12;                              // "K block multiplied" barriers: lcm(stages, partials)
-constexpr int kBsEpilogueWarps = 16;                     // four warps per tensor-memory lane quadrant
-constexpr int kBsFirstRescaleWarp = 4;                   // warps 0..3: producer, MMA issuer and two idle warps (one
-                                                         // warpgroup, so that it can give its registers away)
-constexpr int kBsThreads = 32 * (kBsFirstRescaleWarp + kBsEpilogueWarps);
-constexpr int kBsRegsService = 24;                       // registers per thread after setmaxnreg: service warps ...
-constexpr int kBsRegsRescale = 120;                      // ... and rescale warps (per SM sub-partition: 24 + 4 x 120 <= 512)
-constexpr int kBsColsPerWarp = kBsBN / 4;                // each of the four warps of a quadrant takes 32 columns
+constexpr int kBsEpilogueWarps = 8;                      // two warps per tensor-memory lane quadrant
+constexpr int kBsIssuerB = 2 + kBsEpilogueWarps;         // second MMA-issuing warp (odd K blocks), after the rescale warps
+constexpr int kBsThreads = 32 * (3 + kBsEpilogueWarps);  // producer, MMA issuer (even blocks), 8 rescale warps, issuer (odd)
+constexpr int kBsColsPerWarp = kBsBN / 2;                // each of the two warps of a quadrant takes 64 columns
 
 struct BsSmem {
     static constexpr int kAStage = 128 * 128;
     static constexpr int kBStage = kBsBN * 128;
     static constexpr int kTiles = kBsStages * (kAStage + kBStage);
-    static constexpr int kBarOffset = kTiles;  // full[S], done[12], pempty[P]
+    static constexpr int kOutOffset = kTiles;
+    static constexpr int kBarOffset = kTiles + kBsEpilogueWarps * 4096;  // full[S], done[12], pempty[P]
     static constexpr int kMiscOffset = kBarOffset + (kBsStages + kBsDone + kBsPartials) * 8;
     static constexpr int kTotal = kMiscOffset + 16;
     static constexpr int kDynamicBytes = kTotal + 1024;
@@ -72,7 +68,7 @@ __device__ __forceinline__ void bs_decode(int w, const BlockScaleParams& p, int&
 template <int OUT>
 __global__ void __launch_bounds__(kBsThreads, 1)
 fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                      const BlockScaleParams p) {
+                      const __grid_constant__ CUtensorMap tmap_c, const BlockScaleParams p) {
     using L = BsSmem;
     constexpr int STAGES = kBsStages;
     constexpr int BN = kBsBN;
@@ -90,9 +86,6 @@ fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const uint32_t smem_b = smem_base + STAGES * L::kAStage;
     // One tcgen05.commit per K block: done[i] (i = running K-block count mod 12) says "that block has been multiplied",
     // which frees its shared-memory stage for the producer and publishes its partial to the rescale warps at once.
-    // The wait for a free partial is the producer's (a load is only issued once the partial its block will be
-    // multiplied into has been handed back), so full[stage] stands for both and the issuing thread waits once per
-    // block; measured 8-10 % faster than the issuer waiting for the partial itself.
     const uint32_t bar_full = smem_base + L::kBarOffset;
     const uint32_t bar_done = bar_full + STAGES * 8;
     const uint32_t bar_pempty = bar_done + kBsDone * 8;
@@ -113,6 +106,7 @@ fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     if (warp == 0 && lane == 0) {
         ptx::prefetch_tensormap(&tmap_a);
         ptx::prefetch_tensormap(&tmap_b);
+        if (p.c_tma_ok) ptx::prefetch_tensormap(&tmap_c);
     }
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
@@ -125,23 +119,19 @@ fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     ptx::pdl_launch_dependents();
     ptx::pdl_wait();
 
-    // The sixteen rescale warps hold two K blocks of partial sums plus their accumulators in registers; the four
-    // service warps need next to none. Each warpgroup resizes its register allocation accordingly.
-    // (The resize sits at the head of each group's own branch: after a join the compiler would have to assume the
-    // smaller of the two budgets.)
-    if (warp < kBsFirstRescaleWarp) {
-      ptx::setmaxnreg_dec<kBsRegsService>();
-      if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer: runs the whole ring ahead
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
         if (ptx::elect_one()) {
             uint32_t stage = 0;
+            uint32_t blk = 0;               // running K-block count
             uint32_t prev = kBsDone - STAGES, prev_phase = 1;  // done[] slot of block blk - STAGES and its parity
             bool ok = true;
             for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
                 int m_blk, n_blk;
                 bs_decode(w, p, m_blk, n_blk);
-                for (int kb = 0; kb < p.kb_total; ++kb) {
-                    // the stage is free once the block that used it last (blk - STAGES) has been multiplied
+                for (int kb = 0; kb < p.kb_total; ++kb, ++blk) {
+                    // the stage is free once the block that used it last (blk - STAGES) has been multiplied, and the
+                    // partial this block goes into (blk % P) once the rescale warps have drained block blk - P
                     if (!wait_bounded(bar_done + prev * 8, prev_phase, abort_flag, p.status, ROLE_PRODUCER, kb)) {
                         ok = false;
                         break;
@@ -158,8 +148,11 @@ fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 }
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer: one partial per K block
+    } else if (warp == 1 || warp == kBsIssuerB) {
+        // ------------------------------------------------------------ MMA issuers: one partial per K block; warp 1
+        // takes the even blocks and warp kBsIssuerB the odd ones. Blocks go into different partials, so their MMAs
+        // are independent, and each tcgen05.commit tracks the MMAs of its own thread only.
+        const uint32_t my_parity = warp == 1 ? 0u : 1u;
         if (ptx::elect_one()) {
             uint32_t stage = 0, phase = 0;
             uint32_t blk = 0;   // running K-block count: partial buffer blk % P
@@ -168,21 +161,23 @@ fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
                 for (int kb = 0; kb < p.kb_total; ++kb, ++blk) {
                     const uint32_t buf = blk & PMASK;
-                    // the partial was drained four blocks ago, so it is normally free already (one try_wait)
-                    if (!wait_bounded(bar_pempty + buf * 8, ((blk >> PSHIFT) & 1u) ^ 1u, abort_flag, p.status, ROLE_MMA,
-                                      -1 - kb) ||
-                        !wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status, ROLE_MMA, kb)) {
-                        ok = false;
-                        break;
-                    }
-                    ptx::tc_fence_after();
-                    const uint64_t a_desc = ptx::make_kmajor_sw128_desc(smem_a + stage * L::kAStage);
-                    const uint64_t b_desc = ptx::make_kmajor_sw128_desc(smem_b + stage * L::kBStage);
-                    const uint32_t d_tmem = tmem_base + buf * BN;
+                    if ((blk & 1u) == my_parity) {
+                        // the partial was drained four blocks ago, so it is normally free already (one try_wait)
+                        if (!wait_bounded(bar_pempty + buf * 8, ((blk >> PSHIFT) & 1u) ^ 1u, abort_flag, p.status, ROLE_MMA,
+                                          -1 - kb) ||
+                            !wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status, ROLE_MMA, kb)) {
+                            ok = false;
+                            break;
+                        }
+                        ptx::tc_fence_after();
+                        const uint64_t a_desc = ptx::make_kmajor_sw128_desc(smem_a + stage * L::kAStage);
+                        const uint64_t b_desc = ptx::make_kmajor_sw128_desc(smem_b + stage * L::kBStage);
+                        const uint32_t d_tmem = tmem_base + buf * BN;
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        ptx::umma_ss<ptx::KIND_F8>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, k > 0 ? 1u : 0u);
-                    ptx::tc_commit(bar_done + slot * 8);
+                        for (int k = 0; k < 4; ++k)
+                            ptx::umma_ss<ptx::KIND_F8>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, k > 0 ? 1u : 0u);
+                        ptx::tc_commit(bar_done + slot * 8);
+                    }
                     if (++slot == kBsDone) slot = 0;
                     if (++stage == STAGES) {
                         stage = 0;
@@ -191,100 +186,116 @@ fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 }
             }
         }
-      }
     } else {
-        ptx::setmaxnreg_inc<kBsRegsRescale>();
-        // ------------------------------------------------------------ rescale + accumulate + store (warps 4..19)
-        // This branch lives within kBsRegsRescale registers with 96 of them holding data (32 accumulators and two
-        // blocks of 32 partial sums), so everything else is kept to a few words: the done[] slot and its parity are
-        // derived from the running block count, tile coordinates are decoded again where they are needed.
-        const uint32_t t_row = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
-                               ((warp - kBsFirstRescaleWarp) >> 2) * kBsColsPerWarp;
-        uint32_t blk = 0;  // running K-block count: partial blk % 4, done[] slot blk % 12 with parity (blk / 12) & 1
+        // ------------------------------------------------------------ rescale + accumulate + store (warps 2..9)
+        const int quad = warp & 3;              // tensor-memory lane quadrant
+        const int half = (warp - 2) >> 2;       // which 64 of the tile's 128 columns
+        constexpr int CPW = kBsColsPerWarp;
+        uint32_t blk = 0;
+        uint32_t slot = 0, slot_phase = 0;  // done[] slot of block blk and its parity
         bool ok = true;
-#pragma unroll 1
         for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
-            const float* sa_ptr;
-            const float* sb_ptr;
-            {
-                int m_blk, n_blk;
-                bs_decode(w, p, m_blk, n_blk);
-                const int row = m_blk * kBM + (warp & 3) * 32 + lane;
-                sa_ptr = p.a_scale + (row < p.M ? row : 0);
-                sb_ptr = p.b_scale + n_blk;
-            }
-            float acc[32];
+            int m_blk, n_blk;
+            bs_decode(w, p, m_blk, n_blk);
+            const int row0 = m_blk * kBM + quad * 32;
+            const int row = row0 + lane;
+            const bool row_ok = row < p.M;
+            float acc[CPW];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) acc[j] = 0.0f;
-            // two K blocks per round trip: both partials are requested before the one wait
-#pragma unroll 1
-            for (int pairs = p.kb_total >> 1; pairs > 0; --pairs, blk += 2) {
-                const float s0 = __ldg(sa_ptr) * __ldg(sb_ptr);
-                const float s1 = __ldg(sa_ptr + p.M) * __ldg(sb_ptr + p.n_scale_blocks);
-                sa_ptr += 2 * static_cast<long long>(p.M);
-                sb_ptr += 2 * p.n_scale_blocks;
+            for (int j = 0; j < CPW; ++j) acc[j] = 0.0f;
+            // scales are fetched one K block ahead so that their latency never sits between a partial and its FMAs
+            float sa_next = row_ok ? __ldg(p.a_scale + row) : 0.0f;
+            float sb_next = __ldg(p.b_scale + n_blk);
+            for (int kb = 0; kb < p.kb_total; ++kb, ++blk) {
+                const uint32_t buf = blk & PMASK;
+                const float sa = sa_next, sb = sb_next;
+                if (kb + 1 < p.kb_total) {
+                    sa_next = row_ok ? __ldg(p.a_scale + static_cast<long long>(kb + 1) * p.M + row) : 0.0f;
+                    sb_next = __ldg(p.b_scale + static_cast<long long>(kb + 1) * p.n_scale_blocks + n_blk);
+                }
+                if (!wait_bounded(bar_done + slot * 8, slot_phase, abort_flag, p.status, ROLE_EPILOGUE, kb)) {
+                    ok = false;
+                    break;
+                }
+                if (++slot == kBsDone) {
+                    slot = 0;
+                    slot_phase ^= 1u;
+                }
+                ptx::tc_fence_after();
+                const float s = sa * sb;
+                const uint32_t t_addr =
+                    tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN + half * CPW;
                 uint32_t v0[32], v1[32];
-                if (!wait_bounded(bar_done + (blk % kBsDone) * 8, (blk / kBsDone) & 1u, abort_flag, p.status,
-                                  ROLE_EPILOGUE, static_cast<int>(blk))) {
-                    ok = false;
-                    break;
-                }
-                ptx::tc_fence_after();
-                ptx::tmem_ld_32x32b_x32(t_row + (blk & PMASK) * BN, v0);
-                if (!wait_bounded(bar_done + ((blk + 1) % kBsDone) * 8, ((blk + 1) / kBsDone) & 1u, abort_flag, p.status,
-                                  ROLE_EPILOGUE, static_cast<int>(blk + 1))) {
-                    ok = false;
-                    ptx::tmem_ld_wait();
-                    break;
-                }
-                ptx::tc_fence_after();
-                ptx::tmem_ld_32x32b_x32(t_row + ((blk + 1) & PMASK) * BN, v1);
+                ptx::tmem_ld_32x32b_x32(t_addr, v0);
+                ptx::tmem_ld_32x32b_x32(t_addr + 32, v1);
                 ptx::tmem_ld_wait();
-                // both partials are in registers: hand the buffers back before the arithmetic
+                // the partial is in registers: hand the buffer back before the arithmetic
                 ptx::tc_fence_before();
                 __syncwarp();
-                if (lane == 0) {
-                    ptx::mbar_arrive(bar_pempty + (blk & PMASK) * 8);
-                    ptx::mbar_arrive(bar_pempty + ((blk + 1) & PMASK) * 8);
-                }
+                if (lane == 0) ptx::mbar_arrive(bar_pempty + buf * 8);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(v0[j]), s0, acc[j]);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(v1[j]), s1, acc[j]);
-            }
-            if (ok && (p.kb_total & 1)) {  // odd block count: the last one on its own
-                const float s0 = __ldg(sa_ptr) * __ldg(sb_ptr);
-                uint32_t v0[32];
-                if (!wait_bounded(bar_done + (blk % kBsDone) * 8, (blk / kBsDone) & 1u, abort_flag, p.status,
-                                  ROLE_EPILOGUE, static_cast<int>(blk))) {
-                    ok = false;
-                } else {
-                    ptx::tc_fence_after();
-                    ptx::tmem_ld_32x32b_x32(t_row + (blk & PMASK) * BN, v0);
-                    ptx::tmem_ld_wait();
-                    ptx::tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(bar_pempty + (blk & PMASK) * 8);
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(v0[j]), s0, acc[j]);
-                    ++blk;
+                for (int j = 0; j < 32; ++j) {
+                    acc[j] = fmaf(__uint_as_float(v0[j]), s, acc[j]);
+                    acc[32 + j] = fmaf(__uint_as_float(v1[j]), s, acc[32 + j]);
                 }
             }
             if (!ok) break;
-            // ---- round and store this warp's 32 rows x 32 columns: one rounding, straight from registers (64 or
-            // 128 contiguous bytes per row; once per tile, against kb_total drains)
-            int m_blk, n_blk;
-            bs_decode(w, p, m_blk, n_blk);
-            const int row = m_blk * kBM + (warp & 3) * 32 + lane;
-            const int n0 = n_blk * BN + ((warp - kBsFirstRescaleWarp) >> 2) * kBsColsPerWarp;
-            if (row < p.M && n0 < p.N) {
-                uint32_t bits[32];
+            // ---- round and store this warp's 32 rows x 64 columns
+            constexpr int OB = OutBytes<OUT>::value;
+            constexpr int CW = 128 / OB;  // columns per 128-byte chunk
 #pragma unroll
-                for (int j = 0; j < 32; ++j) bits[j] = __float_as_uint(acc[j]);
-                store_chunk<ptx::KIND_F8, OUT>(reinterpret_cast<uint8_t*>(p.C), p.ldc, row, n0, min(32, p.N - n0),
-                                               p.c_vec_ok != 0, bits, 1.0f);
+            for (int c = 0; c < CPW / CW; ++c) {
+                const int n0 = n_blk * BN + half * CPW + c * CW;
+                if (n0 >= p.N) break;
+                uint32_t u[32];
+                if constexpr (OUT == OUT_F32) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) u[j] = __float_as_uint(acc[c * 32 + j]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if constexpr (OUT == OUT_BF16) {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+                            u[j] = *reinterpret_cast<uint32_t*>(&h);
+                        } else {
+                            __half2 h = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+                            u[j] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                    }
+                }
+                if (p.c_tma_ok) {
+                    if (row0 < p.M) {
+                        // one 4 KB staging buffer per warp: the previous store must have read it
+                        if (lane == 0) ptx::tma_store_wait_read<0>();
+                        __syncwarp();
+                        const uint32_t stage_base = smem_base + L::kOutOffset + (warp - 2) * 4096;
+                        const uint32_t row_addr = stage_base + static_cast<uint32_t>(lane) * 128u;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            ptx::st_shared_v4(row_addr + static_cast<uint32_t>((j ^ (lane & 7)) * 16), u[4 * j],
+                                              u[4 * j + 1], u[4 * j + 2], u[4 * j + 3]);
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            ptx::tma_store_3d(&tmap_c, stage_base, n0, row0, 0);
+                            ptx::tma_store_commit();
+                        }
+                    }
+                } else if (row_ok) {
+                    // unaligned C: predicated element stores
+                    uint8_t* dst = reinterpret_cast<uint8_t*>(p.C) + (static_cast<long long>(row) * p.ldc + n0) * OB;
+#pragma unroll
+                    for (int j = 0; j < CW; ++j) {
+                        if (n0 + j < p.N) {
+                            if constexpr (OB == 4) reinterpret_cast<uint32_t*>(dst)[j] = u[j];
+                            else reinterpret_cast<uint16_t*>(dst)[j] =
+                                static_cast<uint16_t>((j & 1) ? (u[j >> 1] >> 16) : (u[j >> 1] & 0xffffu));
+                        }
+                    }
+                }
             }
         }
+        if (lane == 0) ptx::tma_store_wait_read<0>();
     }
 
     // ---------------------------------------------------------------- teardown
@@ -301,8 +312,8 @@ fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 }
 
 template <int OUT>
-cudaError_t launch_bs(const CUtensorMap& ta, const CUtensorMap& tb, const BlockScaleParams& p, int grid,
-                      cudaStream_t stream) {
+cudaError_t launch_bs(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const BlockScaleParams& p,
+                      int grid, cudaStream_t stream) {
     auto kernel = fp8_blockscale_kernel<OUT>;
     constexpr int smem = BsSmem::kDynamicBytes;
     static bool configured[64] = {};
@@ -315,17 +326,17 @@ cudaError_t launch_bs(const CUtensorMap& ta, const CUtensorMap& tb, const BlockS
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    return launch_pdl(kernel, dim3(grid), dim3(kBsThreads), smem, stream, ta, tb, p);
+    return launch_pdl(kernel, dim3(grid), dim3(kBsThreads), smem, stream, ta, tb, tc, p);
 }
 
 }  // namespace
 
-cudaError_t launch_fp8_blockscale(int out_kind, const CUtensorMap& ta, const CUtensorMap& tb, const BlockScaleParams& p,
-                                  int grid, cudaStream_t stream) {
+cudaError_t launch_fp8_blockscale(int out_kind, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                                  const BlockScaleParams& p, int grid, cudaStream_t stream) {
     switch (out_kind) {
-        case OUT_F32: return launch_bs<OUT_F32>(ta, tb, p, grid, stream);
-        case OUT_BF16: return launch_bs<OUT_BF16>(ta, tb, p, grid, stream);
-        case OUT_F16: return launch_bs<OUT_F16>(ta, tb, p, grid, stream);
+        case OUT_F32: return launch_bs<OUT_F32>(ta, tb, tc, p, grid, stream);
+        case OUT_BF16: return launch_bs<OUT_BF16>(ta, tb, tc, p, grid, stream);
+        case OUT_F16: return launch_bs<OUT_F16>(ta, tb, tc, p, grid, stream);
         default: return cudaErrorInvalidValue;
     }
 }

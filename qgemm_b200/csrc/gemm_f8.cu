@@ -16,3 +16,10 @@ cudaError_t launch_gemm_wide_f8(int out, const CUtensorMap& ta, const CUtensorMa
     return launch_wide_kind<ptx::KIND_F8>(out, ta, tb, tc, p, clusters, stream);
 }
 }  // namespace qgemm
+
+#ifdef QGEMM_STAMPS
+// Diagnostic build only: the cycle stamps of the last FP8 lone-CTA launch ([first CTA | last CTA] x 16).
+extern "C" int qgemm_debug_stamps(long long* out32) {
+    return cudaMemcpyFromSymbol(out32, qgemm::g_stamps, sizeof(long long) * 32) == cudaSuccess ? 0 : 4;
+}
+#endif

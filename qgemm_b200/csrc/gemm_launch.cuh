@@ -62,7 +62,7 @@ cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     return launch_pdl(kernel, dim3(grid), dim3(kGemmThreads), smem, stream, ta, tb, tc, p);
 }
 
-// `am` = rows of A loaded per stage: 128, or 64 / 32 with the 64-wide tile for small M.
+// `am` = rows of A loaded per stage: 128, or 64 / 32 / 16 with the 64-wide tile for small M.
 template <int KIND>
 cudaError_t launch_kind(int bn, int out, int am, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
                         const GemmParams& p, int grid, cudaStream_t stream) {
@@ -78,6 +78,7 @@ cudaError_t launch_kind(int bn, int out, int am, const CUtensorMap& ta, const CU
     QGEMM_CASES(64, 128)
     QGEMM_CASES(64, 64)
     QGEMM_CASES(64, 32)
+    QGEMM_CASES(64, 16)
 #undef QGEMM_CASES
 #undef QGEMM_CASE
     return cudaErrorInvalidValue;
@@ -226,10 +227,10 @@ struct BlockScaleParams {
     const float* a_scale;  // [kb_total][M]
     const float* b_scale;  // [kb_total][n_scale_blocks]
     int* status;
-    int c_vec_ok;  // C base and ldc allow 16-byte vector stores
+    int c_tma_ok;
 };
-cudaError_t launch_fp8_blockscale(int out_kind, const CUtensorMap& ta, const CUtensorMap& tb, const BlockScaleParams& p,
-                                  int grid, cudaStream_t stream);
+cudaError_t launch_fp8_blockscale(int out_kind, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                                  const BlockScaleParams& p, int grid, cudaStream_t stream);
 
 // Adds up the K slices of the last-wave tiles (splitk_reduce.cu): `slots` tiles stored as
 // [splits][slots * 256][256] 32-bit partial sums; `tiles` locates slot i in C (m_tiles, n_tiles, group_m,

@@ -66,8 +66,6 @@ struct GemmParams {
     // the same share of B to pull from HBM). bal_units == 0: equal tiles. Widths never exceed the kernel's BN.
     int bal_units;
     int bal_wide;
-    int early_issue;  // lone-CTA kernel: warp 0 requests the first tile's first ring of K blocks before the CTA-wide
-                      // set-up barrier
     int test_skip_kb;  // failure-detection test hook: the producer leaves out the loads of this K block (-1 = none),
                        // so the consumer's bounded wait runs out and the kernel returns through its error path
 };
@@ -125,6 +123,20 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
     }
     return true;
 }
+
+// Diagnostic build only (-DQGEMM_STAMPS): SM cycle counter at points of the lone-CTA kernel's timeline, for the first
+// and the last CTA of the grid, read back with qgemm_debug_stamps. Compiled out otherwise.
+#ifdef QGEMM_STAMPS
+static __device__ long long g_stamps[2][16];
+#define QGEMM_STAMP(i)                                                                \
+    do {                                                                              \
+        if (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1) g_stamps[blockIdx.x == 0 ? 0 : 1][i] = clock64(); \
+    } while (0)
+#else
+#define QGEMM_STAMP(i) \
+    do {               \
+    } while (0)
+#endif
 
 struct TileCoord {
     int m_blk, n_blk, split;
@@ -363,9 +375,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int warp = static_cast<int>(threadIdx.x) >> 5;
     const int lane = static_cast<int>(threadIdx.x) & 31;
     const int total_work = p.m_tiles * p.n_tiles * p.splits;
-    // The successor in the stream may be scheduled as soon as SMs free up; it waits for this grid's completion at its
-    // own griddepcontrol.wait. Signalled first, so that warp 0's early wait below does not hold it back.
-    ptx::pdl_launch_dependents();
+    if (threadIdx.x == 0) QGEMM_STAMP(0);
 
     // The loads of one K block of one tile into ring slot `stage`.
     auto load_stage = [&](const TileCoord& t, int col0, int width, int kb, uint32_t stage) {
@@ -394,42 +404,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             ptx::tma_load_2d(smem_b + stage * L::kBStage, &tmap_b, full, kb * BK, col0);
         }
     };
-    // Ring slots of this CTA's first tile that thread 0 fills straight after initialising the barriers, before the
-    // CTA-wide set-up barrier: the first bytes are on their way while tensor memory is still being allocated.
-    int early = 0;
-    if (static_cast<int>(blockIdx.x) < total_work) {
-        const TileCoord t0 = decode_tile(blockIdx.x, p);
-        const int kb0 = t0.split * p.kb_per_split;
-        early = p.early_issue ? min(STAGES, min(p.kb_total, kb0 + p.kb_per_split) - kb0) : 0;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(bar_full + s * 8, 1);
+            ptx::mbar_init(bar_empty + s * 8, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(bar_tfull + a * 8, 1);
+            ptx::mbar_init(bar_tempty + a * 8, 4);
+        }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
     }
-
-    if (warp == 0) {
-        if (lane == 0) {
-            for (int s = 0; s < STAGES; ++s) {
-                ptx::mbar_init(bar_full + s * 8, 1);
-                ptx::mbar_init(bar_empty + s * 8, 1);
-            }
-            for (int a = 0; a < 2; ++a) {
-                ptx::mbar_init(bar_tfull + a * 8, 1);
-                ptx::mbar_init(bar_tempty + a * 8, 4);
-            }
-            *abort_flag = 0;
-            ptx::fence_barrier_init();
-            ptx::prefetch_tensormap(&tmap_a);
-            ptx::prefetch_tensormap(&tmap_b);
-            if (p.c_tma_ok || p.bal_units > 0) ptx::prefetch_tensormap(&tmap_c);
-        }
-        __syncwarp();
-        if (p.early_issue && early > 0) {
-            // lane i issues the loads of K block i of this CTA's first tile: the whole first ring is requested by two
-            // warp-wide instructions instead of a loop in one thread
-            ptx::pdl_wait();  // the operands may be the predecessor's output
-            const TileCoord t0 = decode_tile(blockIdx.x, p);
-            int col0, width;
-            tile_columns(p, t0.n_blk, BN, col0, width);
-            const int kb0 = t0.split * p.kb_per_split;
-            for (int i = lane; i < early; i += 32) load_stage(t0, col0, width, kb0 + i, static_cast<uint32_t>(i));
-        }
+    if (warp == 0 && lane == 0) {
+        ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_b);
+        if (p.c_tma_ok || p.bal_units > 0) ptx::prefetch_tensormap(&tmap_c);
     }
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
@@ -439,9 +429,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // Apart from warp 0's early loads, everything above touched no global memory; from here on the predecessor's
-    // results are needed.
+    // Everything above touched no global memory; from here on the predecessor's results are needed.
+    ptx::pdl_launch_dependents();
     ptx::pdl_wait();
+    if (threadIdx.x == 0) QGEMM_STAMP(1);
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -455,14 +446,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 int col0, width;
                 tile_columns(p, t.n_blk, BN, col0, width);
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    const bool already = (w == static_cast<int>(blockIdx.x)) && (kb - kb0 < early);
-                    if (!already) {
-                        if (!wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, p.status, ROLE_PRODUCER, kb)) {
-                            ok = false;
-                            break;
-                        }
-                        load_stage(t, col0, width, kb, stage);
+                    if (!wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, p.status, ROLE_PRODUCER, kb)) {
+                        ok = false;
+                        break;
                     }
+                    load_stage(t, col0, width, kb, stage);
+                    if (kb == kb0) QGEMM_STAMP(2);
+                    if (kb == kb1 - 1) QGEMM_STAMP(3);
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1u;
@@ -497,6 +487,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         break;
                     }
                     ptx::tc_fence_after();
+                    if (kb == kb0) QGEMM_STAMP(4);
+                    if (kb == kb1 - 1) QGEMM_STAMP(5);
                     const uint64_t a_desc = ptx::make_kmajor_sw128_desc(smem_a + stage * L::kAStage);
                     const uint64_t b_desc =
                         p.b_mn_major ? ptx::make_mnmajor_sw128_desc(smem_b + stage * L::kBStage, BK * 128)
@@ -516,6 +508,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                 }
                 if (ok) ptx::tc_commit(bar_tfull + acc * 8);
+                QGEMM_STAMP(6);
             }
         }
     } else {
@@ -534,6 +527,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const uint32_t acc_phase = (it >> 1) & 1u;
             if (!wait_bounded(bar_tfull + acc * 8, acc_phase, abort_flag, p.status, ROLE_EPILOGUE, w)) break;
             ptx::tc_fence_after();
+            if (warp == 2 && lane == 0) QGEMM_STAMP(7);
             const long long row = static_cast<long long>(t.m_blk) * kBM + quad * 32 + lane;
             uint8_t* c_base = reinterpret_cast<uint8_t*>(p.C) +
                               static_cast<long long>(t.split) * p.split_stride * OutBytes<OUT>::value;
@@ -578,11 +572,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         // the staging buffers must have been read by every TMA store before the CTA (and its shared memory) goes away;
         // the global writes themselves complete with the grid
         if (lane == 0) ptx::tma_store_wait_read<0>();
+        if (warp == 2 && lane == 0) QGEMM_STAMP(8);
     }
 
     // ---------------------------------------------------------------- teardown
     ptx::tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) QGEMM_STAMP(9);
     if (*abort_flag != 0) {
         // Let TMA copies and MMAs that were already issued finish before the memory they touch
         // is released.

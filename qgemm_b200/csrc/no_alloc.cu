@@ -207,7 +207,6 @@ extern "C" int qgemm_mix_gemm_splitk_static(int in_dtype, int out_dtype, const v
     p.c_vec_ok = 1;
     p.c_tma_ok = 1;
     p.test_skip_kb = take_test_skip_kb();
-    p.early_issue = 1;
 
     const long long work = static_cast<long long>(p.m_tiles) * p.n_tiles * p.splits;
     if (work > 0x7fffffffLL) return QGEMM_ERR_UNSUPPORTED;

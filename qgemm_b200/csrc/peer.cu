@@ -53,6 +53,26 @@ int qgemm_peer_export(const void* ptr, void* handle_out, size_t* offset_out) {
     return QGEMM_OK;
 }
 
+int qgemm_peer_alloc(size_t bytes, void** ptr_out) {
+    if (ptr_out == nullptr || bytes == 0) return QGEMM_ERR_INVALID_ARG;
+    void* p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return QGEMM_ERR_WORKSPACE;
+    }
+    *ptr_out = p;
+    return QGEMM_OK;
+}
+
+int qgemm_peer_free(void* ptr) {
+    if (ptr == nullptr) return QGEMM_OK;
+    if (cudaFree(ptr) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return QGEMM_ERR_CUDA;
+    }
+    return QGEMM_OK;
+}
+
 int qgemm_peer_open(const void* handle, void** base_out) {
     if (handle == nullptr || base_out == nullptr) return QGEMM_ERR_INVALID_ARG;
     cudaIpcMemHandle_t h;

@@ -71,14 +71,15 @@ class GatheredOutput:
     def __init__(self, M: int, n_total: int, dtype, device, group=None):
         import torch
         import torch.distributed as dist
-        from . import peer_export, peer_open
+        from . import peer_export, peer_open, peer_tensor
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         self.device = torch.device(device)
         self.M, self.n_total = int(M), int(n_total)
-        # a fresh allocation of its own, so that the exported handle covers nothing else
-        self.local = torch.empty((self.M, self.n_total), dtype=dtype, device=self.device)
+        # a device allocation of its own (not a piece of torch's caching allocator, whose blocks hold unrelated
+        # tensors): the exported handle covers the whole allocation that contains the matrix
+        self.local, self._block = peer_tensor((self.M, self.n_total), dtype, self.device)
         handle, offset = peer_export(self.local)
         everyone = [None] * self.world
         dist.all_gather_object(everyone, (handle, offset), group=group)
@@ -112,7 +113,9 @@ class GatheredOutput:
         for base in self._opened:
             peer_close(base, self.device)
         self._opened = []
-        dist.barrier(group=self.group)
+        dist.barrier(group=self.group)  # nobody maps this rank's matrix any more
+        self.local = None
+        self._block.free()
 
 
 def sharded_mix_gemm_gather(a, b_slice, scale_a, scale_b, out: GatheredOutput) -> None:

@@ -212,14 +212,32 @@ public:
         cudaFree(dout);
     }
 
-    void run_benchmark() {
+    // The shape presets of the reference's tests/includes/example_configs.h:8-53 -- "small", "medium", "large" and
+    // "mixed" (square, tall, wide and two transformer projection shapes), with its warm-up / run counts -- for one
+    // precision. An unknown name gives an empty list.
+    static std::vector<TestConfig> preset(const std::string& name, const std::string& precision) {
+        struct Row { int m, n, k, warmup, runs; };
+        std::vector<Row> rows;
+        if (name == "small") rows = {{128, 128, 128, 3, 10}, {256, 256, 256, 3, 10}, {512, 512, 512, 3, 10}};
+        else if (name == "medium") rows = {{512, 512, 512, 5, 20}, {1024, 1024, 1024, 5, 20}, {2048, 2048, 2048, 5, 20}};
+        else if (name == "large") rows = {{2048, 2048, 2048, 3, 10}, {4096, 4096, 4096, 3, 10}, {8192, 8192, 8192, 3, 5}};
+        else if (name == "mixed")
+            rows = {{512, 512, 512, 5, 10},   {1024, 1024, 1024, 5, 10}, {2048, 512, 1024, 5, 10},  {4096, 1024, 2048, 5, 10},
+                    {512, 2048, 1024, 5, 10}, {1024, 4096, 2048, 5, 10}, {1024, 4096, 1024, 5, 10}, {4096, 1024, 4096, 5, 10}};
+        std::vector<TestConfig> out;
+        for (const Row& r : rows) out.emplace_back(r.m, r.n, r.k, precision, r.warmup, r.runs);
+        return out;
+    }
+
+    void run_benchmark(const std::string& preset_name = "", const std::string& precision = "bf16") {
         std::cout << "\n=== QGEMM Benchmark Results ===" << std::endl;
-        const std::vector<TestConfig> configs = {
+        std::vector<TestConfig> configs = {
             TestConfig(1024, 1024, 1024, "fp16"), TestConfig(1024, 1024, 1024, "bf16"),
             TestConfig(2048, 2048, 2048, "bf16"), TestConfig(4096, 4096, 4096, "bf16"),
             TestConfig(1000, 1016, 520, "bf16"),  TestConfig(4096, 4096, 4096, "int8"),
             TestConfig(4096, 4096, 4096, "fp8"),  TestConfig(64, 7168, 2048, "fp8"),
         };
+        if (!preset_name.empty()) configs = preset(preset_name, precision);
         for (const auto& c : configs) {
             if (c.precision == "bf16") run_config<__nv_bfloat16, float, false>(c, 1e-3);
             else if (c.precision == "fp16") run_config<__half, float, false>(c, 1e-3);
@@ -229,6 +247,7 @@ public:
             } else run_config<__nv_fp8_e4m3, __nv_bfloat16, true>(c, 1e-2);
         }
         std::cout << std::endl;
+        if (!preset_name.empty()) return;
         run_transpose<__nv_bfloat16>(8192, 8192, "bf16");
         run_transpose<int8_t>(4096, 8192, "int8");
         run_transpose<__nv_bfloat16>(1000, 333, "bf16");
@@ -271,13 +290,26 @@ private:
     mutable int failures_ = 0;
 };
 
-int main() {
+// gemm_benchmark                      the library's own shape list, every precision, then the transposes
+// gemm_benchmark <preset> [precision] one of the reference's presets: small | medium | large | mixed; precision
+//                                     bf16 (default) | fp16 | int8 | fp8
+int main(int argc, char** argv) {
+    const std::string preset_name = argc > 1 ? argv[1] : "";
+    const std::string precision = argc > 2 ? argv[2] : "bf16";
+    if (!preset_name.empty() && GemmTestFramework::preset(preset_name, precision).empty()) {
+        std::cerr << "unknown preset '" << preset_name << "' (small | medium | large | mixed)" << std::endl;
+        return 2;
+    }
+    if (precision != "bf16" && precision != "fp16" && precision != "int8" && precision != "fp8") {
+        std::cerr << "unknown precision '" << precision << "' (bf16 | fp16 | int8 | fp8)" << std::endl;
+        return 2;
+    }
     std::cout << "QGEMM Benchmark Test Suite" << std::endl;
     cudaDeviceProp prop;
     CHECK_CUDA(cudaGetDeviceProperties(&prop, 0));
     std::cout << "GPU: " << prop.name << "\nCompute Capability: " << prop.major << "." << prop.minor << std::endl;
     GemmTestFramework framework;
-    framework.run_benchmark();
+    framework.run_benchmark(preset_name, precision);
     if (framework.failures() != 0) {
         std::cout << "\n" << framework.failures() << " check(s) FAILED" << std::endl;
         return 1;

@@ -1,7 +1,11 @@
-"""Balanced column tiling: a problem with fewer equal tiles than SMs (small M) has the sixteen-column units of N dealt
-out over as many tile columns as there are SMs, tile widths differing by at most 16. Same sums as the equal tiling
-(each output element is one CTA's K loop in the same order), so the two must agree bit for bit; and the skinny FP8
-shapes of the sweep (M = 16, 64, 256 at N = 7168, K = 2048) must be planned that way."""
+"""Balanced column tiling (opt-in, QGEMM_BALANCE=1): a problem with fewer equal tiles than SMs (small M) has the
+sixteen-column units of N dealt out over as many tile columns as there are SMs, tile widths differing by at most 16.
+Same sums as the equal tiling (each output element is one CTA's K loop in the same order), so the two must agree bit
+for bit; and with the switch on, the skinny FP8 shapes of the sweep (M = 16, 64, 256 at N = 7168, K = 2048) must be
+planned that way. The switch is read from the environment when the library is loaded: the tests set it and have the
+library read its environment again."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -9,6 +13,16 @@ import torch
 from qgemm_b200 import datagen
 
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def balanced_on(qlib):
+    os.environ["QGEMM_BALANCE"] = "1"
+    qlib.lib().qgemm_reload_env()
+    yield
+    del os.environ["QGEMM_BALANCE"]
+    qlib.lib().qgemm_reload_env()
+    assert qlib.plan_query(qlib.FP8_E4M3, qlib.BF16, qlib.B_K_MAJOR, 16, 7168, 2048, None)["balanced_tiles"] == 0
 
 
 @pytest.mark.parametrize("M", [16, 64, 256])

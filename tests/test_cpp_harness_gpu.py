@@ -35,3 +35,16 @@ def test_cpp_harness(qlib, dev):
         assert all(v == "PASS" for _, v in lst), lst
         assert any(n.startswith(("GEMM_kernel", "MIX_GEMM")) for n, _ in lst)
     assert res.stdout.count("matrix_transpose<") == 3 and "FAIL" not in res.stdout
+
+
+@pytest.mark.parametrize("preset,precision,problems", [("small", "fp16", 3), ("mixed", "bf16", 8)])
+def test_cpp_harness_reference_presets(qlib, dev, preset, precision, problems):
+    """The shape presets of the reference's tests/includes/example_configs.h:8-53, selected on the command line."""
+    if not os.path.exists(BINARY):
+        import __graft_entry__
+        __graft_entry__.build()
+    res = subprocess.run([BINARY, preset, precision], capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
+    assert len(re.findall(r"^Problem size: M=", res.stdout, flags=re.M)) == problems
+    assert "FAIL" not in res.stdout and res.stdout.count("PASS") >= 3 * problems
+    assert subprocess.run([BINARY, "no-such-preset"], capture_output=True).returncode == 2
