@@ -44,7 +44,9 @@ if ROOT not in sys.path:
 # line reports it as `traffic` with `traffic_source` saying so. None where no capture of that workload exists.
 NCU_TRAFFIC_BYTES = {
     "c2_bf16_8192": 883.1e6 + 120.8e6,
-    "f1_fp8_blockscale": 131.4e6 + 39.6e6,
+    "c3_int8_8192": 237.3e6 + 115.2e6,
+    "c4_fp8_16": 14.74e6,
+    "f1_fp8_blockscale": 131.1e6 + 40.1e6,
 }
 
 NOMINAL_PEAK_TFLOPS = {"bf16": 2250.0, "fp16": 2250.0, "int8": 4500.0, "fp8": 4500.0}
@@ -106,6 +108,10 @@ def parse_args():
     ap.add_argument("--configs", default="", help="comma-separated subset of the other configurations to measure "
                     "(names of WORKLOADS, or hbm_passes); default: all of them")
     ap.add_argument("--no-gather", action="store_true", help="c5, N > 1: skip the all-gather and fused-gather timings")
+    ap.add_argument("--stamps", action="store_true",
+                    help="diagnostic library only (python -m qgemm_b200.build --stamps, then "
+                         "QGEMM_LIBRARY=qgemm_b200/libqgemm_stamps.so): add the lone-CTA kernel's cycle stamps of the "
+                         "last launch of the primary workload to the line")
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--split-k", type=int, default=0)
     ap.add_argument("--group-m", type=int, default=0)
@@ -756,6 +762,10 @@ def run_primary(ctx, args):
     check["ok"] = ctx.all_ok(bool(check.get("ok")))
     check["path"] = "the call timed as `value`, same tuning, every rank's own column block"
 
+    stamps = None
+    if args.stamps:
+        stamps = read_stamps(ctx)
+
     ms_list = sorted(r["ms_per_step"] for r in regions)
     ms_per_step = statistics.median(ms_list)
     value = world * flop / (ms_per_step * 1e-3) / 1e12
@@ -783,7 +793,27 @@ def run_primary(ctx, args):
         out["relayout_roofline"] = relayout
     if direct_b is not None:
         out["direct_b"] = direct_b
+    if stamps is not None:
+        out["kernel_timeline_cycles"] = stamps
     return out
+
+
+def read_stamps(ctx):
+    """SM cycle counts along the lone-CTA kernel's timeline (first and last CTA of the last FP8 launch), relative to
+    the CTA's entry; only a library built with -DQGEMM_STAMPS exports them."""
+    import ctypes as C
+    L = ctx.q.lib()
+    if not hasattr(L, "qgemm_debug_stamps"):
+        return {"unavailable": "the loaded library is not the diagnostic build (QGEMM_LIBRARY)"}
+    buf = (C.c_longlong * 32)()
+    ctx.torch.cuda.synchronize()
+    if L.qgemm_debug_stamps(buf) != 0:
+        return {"unavailable": "qgemm_debug_stamps failed"}
+    names = ["entry", "set-up done, predecessor complete", "first load issued", "last load issued",
+             "first K block landed", "last K block landed", "accumulator committed", "epilogue woke", "epilogue stored"]
+    vals = list(buf)
+    return {which: {n: vals[base + i] - vals[base] for i, n in enumerate(names)}
+            for which, base in (("first_cta", 0), ("last_cta", 16))}
 
 
 def run_e2e(ctx, args, ops):

@@ -13,7 +13,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libqgemm.so")
+#: the library to load; QGEMM_LIBRARY names another build of it (e.g. the diagnostic one of ``build.py --stamps``)
+LIB_PATH = os.environ.get("QGEMM_LIBRARY") or os.path.join(HERE, "libqgemm.so")
 
 # qgemm_status_t
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_CUDA, ERR_WORKSPACE, ERR_DEVICE_TIMEOUT = range(7)

@@ -15,6 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB_PATH = os.path.join(HERE, "libqgemm.so")
+STAMPS_LIB_PATH = os.path.join(HERE, "libqgemm_stamps.so")  # the diagnostic build, beside the product library
 
 SOURCES = ["gemm_f16.cu", "gemm_i8.cu", "gemm_f8.cu", "transpose.cu", "splitk_reduce.cu", "capi.cu", "cxx_api.cu",
            "no_alloc.cu", "gemm_blockscale.cu", "quantize.cu", "peer.cu", "host_gemm.cu", "int4.cu"]
@@ -47,10 +48,10 @@ def _deps_mtime() -> float:
     return newest
 
 
-def _compile(src: str, verbose: bool) -> str:
-    obj = os.path.join(OBJ_DIR, src.replace(".cu", ".o"))
-    cmd = [_nvcc(), *ARCH_FLAGS, *NVCC_FLAGS, *_host_compiler_flags(), "-I", os.path.join(HERE, "..", "include"),
-           "-c", os.path.join(CSRC, src), "-o", obj]
+def _compile(src: str, verbose: bool, defines=(), obj_dir: str = OBJ_DIR) -> str:
+    obj = os.path.join(obj_dir, src.replace(".cu", ".o"))
+    cmd = [_nvcc(), *ARCH_FLAGS, *NVCC_FLAGS, *_host_compiler_flags(), *[f"-D{d}" for d in defines], "-I",
+           os.path.join(HERE, "..", "include"), "-c", os.path.join(CSRC, src), "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
@@ -62,19 +63,24 @@ def _compile(src: str, verbose: bool) -> str:
     return obj
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Build libqgemm.so if it is missing or older than any source. Returns its path."""
-    if not force and os.path.exists(LIB_PATH) and os.path.getmtime(LIB_PATH) >= _deps_mtime():
+def build(force: bool = False, verbose: bool = False, stamps: bool = False) -> str:
+    """Build libqgemm.so if it is missing or older than any source. Returns its path. ``stamps`` builds the
+    diagnostic variant libqgemm_stamps.so instead (-DQGEMM_STAMPS): the lone-CTA GEMM kernel records SM cycle counts
+    along its timeline and the library exports qgemm_debug_stamps to read them; load it with QGEMM_LIBRARY=<path>."""
+    out_path = STAMPS_LIB_PATH if stamps else LIB_PATH
+    if not force and not stamps and os.path.exists(LIB_PATH) and os.path.getmtime(LIB_PATH) >= _deps_mtime():
         return LIB_PATH
-    os.makedirs(OBJ_DIR, exist_ok=True)
+    obj_dir = OBJ_DIR + ("_stamps" if stamps else "")
+    os.makedirs(obj_dir, exist_ok=True)
+    defines = ("QGEMM_STAMPS",) if stamps else ()
     with cf.ThreadPoolExecutor(max_workers=min(8, len(SOURCES))) as pool:
-        objs = list(pool.map(lambda s: _compile(s, verbose), SOURCES))
-    cmd = [_nvcc(), *ARCH_FLAGS, *_host_compiler_flags(), "-shared", "-o", LIB_PATH, *objs, "-lcudart"]
+        objs = list(pool.map(lambda s: _compile(s, verbose, defines, obj_dir), SOURCES))
+    cmd = [_nvcc(), *ARCH_FLAGS, *_host_compiler_flags(), "-shared", "-o", out_path, *objs, "-lcudart"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
-    return LIB_PATH
+    return out_path
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, stamps="--stamps" in sys.argv))

@@ -421,6 +421,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         ptx::prefetch_tensormap(&tmap_b);
         if (p.c_tma_ok || p.bal_units > 0) ptx::prefetch_tensormap(&tmap_c);
     }
+    // This CTA's first tile is decoded here, while the predecessor in the stream may still be running: the integer
+    // divisions of decode_tile would otherwise sit between the predecessor's end and the first load (a skinny problem
+    // is one tile per CTA, and its whole body is a few microseconds).
+    const TileCoord first_tile =
+        static_cast<int>(blockIdx.x) < total_work ? decode_tile(blockIdx.x, p) : TileCoord{0, 0, 0};
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
         ptx::tmem_relinquish();
@@ -440,7 +445,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
-                const TileCoord t = decode_tile(w, p);
+                const TileCoord t = (w == static_cast<int>(blockIdx.x)) ? first_tile : decode_tile(w, p);
                 const int kb0 = t.split * p.kb_per_split;
                 const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
                 int col0, width;
@@ -467,7 +472,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint32_t it = 0;
             bool ok = true;
             for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x, ++it) {
-                const TileCoord t = decode_tile(w, p);
+                const TileCoord t = (w == static_cast<int>(blockIdx.x)) ? first_tile : decode_tile(w, p);
                 const int kb0 = t.split * p.kb_per_split;
                 const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
                 const uint32_t acc = it & 1u;
@@ -522,7 +527,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         uint32_t it = 0;
         uint32_t out_buf = 0;
         for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++it) {
-            const TileCoord t = decode_tile(w, p);
+            const TileCoord t = (w == static_cast<int>(blockIdx.x)) ? first_tile : decode_tile(w, p);
             const uint32_t acc = it & 1u;
             const uint32_t acc_phase = (it >> 1) & 1u;
             if (!wait_bounded(bar_tfull + acc * 8, acc_phase, abort_flag, p.status, ROLE_EPILOGUE, w)) break;

@@ -121,3 +121,34 @@ def test_scratch_grows_on_demand_and_survives_shutdown(qlib, oracle, dev):
     q.gemm(a, b, acc, b_kmajor=False)
     assert np.array_equal(acc.cpu().numpy(), oracle.gemm_i8(ai, bi, False))
     assert q.device_status()[0] == q.OK
+
+
+@pytest.mark.parametrize("M,N,K,b_kmajor", [(1000, 2100, 264, False), (512, 1536, 512, True), (130, 300, 128, False)])
+def test_host_gemm_with_a_resident_on_the_device(qlib, oracle, dev, M, N, K, b_kmajor):
+    """qgemm_gemm_host_resident_a: A already on the device (as after the ranks of a column-sharded product have
+    exchanged their shares of it), B from the host band by band, C to the host. Same result as the oracle, and the
+    same bits as the call that uploads A itself."""
+    from qgemm_b200.host_api import gemm_host_resident_a
+    a_bits, a_val = oracle.round_bf16(datagen.normal((M, K), seed=N, stream=0))
+    b_shape = (N, K) if b_kmajor else (K, N)
+    b_bits, b_val = oracle.round_bf16(datagen.normal(b_shape, seed=N, stream=1))
+    a_h = torch.from_numpy(a_bits.view(np.int16)).view(torch.bfloat16).pin_memory()
+    b_h = torch.from_numpy(b_bits.view(np.int16)).view(torch.bfloat16).pin_memory()
+    c_res = torch.zeros((M, N), dtype=torch.bfloat16).pin_memory()
+    c_up = torch.zeros((M, N), dtype=torch.bfloat16).pin_memory()
+    a_d = a_h.to(dev)
+    for _ in range(2):
+        c_res.zero_()
+        gemm_host_resident_a(a_d, b_h, c_res, None, None, b_kmajor)
+        torch.cuda.synchronize()
+        assert oracle.rel_l2(c_res.float().numpy(), oracle.gemm_f32(a_val, b_val, b_kmajor)) <= 4e-3  # bf16 output
+    gemm_host(a_h, b_h, c_up, b_kmajor=b_kmajor, device=dev)
+    torch.cuda.synchronize()
+    # both compute each element as one K loop of the same kernel family; tile shapes may differ between the strips
+    assert oracle.rel_l2(c_res.float().numpy(), c_up.float().numpy()) <= 1e-6 or \
+        oracle.bf16_ulp_distance(c_res.view(torch.int16).numpy().view(np.uint16),
+                                 c_up.view(torch.int16).numpy().view(np.uint16)) <= 1
+    L = qlib.lib()
+    assert L.qgemm_gemm_host_resident_a(qlib.BF16, qlib.BF16, qlib.B_K_MAJOR, None, K, b_h.data_ptr(), K, None, None,
+                                        c_res.data_ptr(), N, M, N, K, None) == qlib.ERR_INVALID_ARG
+    assert qlib.device_status()[0] == qlib.OK
