@@ -750,7 +750,10 @@ def run_primary(ctx, args):
     # ---------------- e2e: host buffers through the host-level call, copies inside the timed region
     e2e = None
     if not args.no_e2e and not blockscale:
-        e2e = run_e2e(ctx, args, ops)
+        try:
+            e2e = run_e2e(ctx, args, ops)
+        except Exception as exc:  # the headline must not go down with the host-operand leg
+            e2e = {"error": repr(exc)[:300]}
     kernel_replica()
     for i in range(4, n_regions):
         region("host-operand steps" if i == 4 else "pause")

@@ -189,7 +189,7 @@ int qgemm_device_status(int* out4);
 /*
  * The QGEMM_* environment variables (tuning overrides for experiments: QGEMM_TILE_N, QGEMM_SPLIT_K,
  * QGEMM_GROUP_M, QGEMM_CTA_PAIR, QGEMM_RELAYOUT_B, QGEMM_MAX_CTAS, QGEMM_DIRECT_STORE, QGEMM_FULL_A_TILE,
- * QGEMM_TAIL_SPLIT, QGEMM_BALANCE, QGEMM_HOST_BANDS, QGEMM_HOST_BANDS_N) are read once, when the library is
+ * QGEMM_TAIL_SPLIT, QGEMM_BALANCE, QGEMM_PREFETCH, QGEMM_HOST_BANDS, QGEMM_HOST_BANDS_N) are read once, when the library is
  * loaded; this reads them again. Not meant to run concurrently with GEMM calls of other threads.
  */
 int qgemm_reload_env(void);
@@ -220,7 +220,8 @@ int qgemm_test_arm_skip_load(int k_block);
  * kernel; make that first call before starting any stream capture. All calls on a device share the one
  * array, which keeps the previous call's partial sums (none of them needs clearing: each call overwrites
  * what it later reads), so calls that overlap on the GPU (for example on different streams with no
- * ordering between them) race with each other and must be serialised by the caller.
+ * ordering between them) race with each other and must be serialised by the caller. A bounded wait that runs out in
+ * its kernels is reported by qgemm_device_status like any other, which allocates nothing either.
  */
 #define QGEMM_STATIC_SCRATCH_BYTES (32u << 20)
 int qgemm_mix_gemm_splitk_static(int in_dtype, int out_dtype, const void* A, size_t lda, const void* B, size_t ldb,

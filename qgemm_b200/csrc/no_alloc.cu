@@ -14,6 +14,9 @@
 // overwrites every partial the reduction pass reads for the rows and columns it writes -- but two
 // calls that overlap on the GPU (for example on different streams with no ordering) race on it.
 //
+// A bounded wait that runs out in this path is recorded in status words that are part of the module as well;
+// qgemm_device_status reads and clears them (static_status_fetch below) without allocating.
+//
 // The first call on a device does the set-up (cudaGetSymbolAddress for the two arrays, the kernel's
 // shared-memory attribute); it should come before any stream capture is started.
 #include <cuda.h>

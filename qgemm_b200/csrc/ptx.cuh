@@ -82,6 +82,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
         : "memory");
 }
 
+// Hint: bring one box of a tensor into L2 (no shared memory, no completion to wait for). L2 is the GPU's point of
+// coherence, so a box prefetched before its producer has written it is simply updated there: the hint can be issued
+// ahead of griddepcontrol.wait.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* tmap, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                 ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y)
+                 : "memory");
+}
+
 // 3-D tiled store shared -> global (bulk async-group completion); z selects a slab (split-K partial sums are
 // [split][M][N]). Elements outside the tensor are clipped by the hardware, rows beyond M per slab. Never issued
 // with a negative coordinate.
