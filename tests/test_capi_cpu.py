@@ -84,3 +84,33 @@ def test_workspace_planning(qlib):
     t = qlib.Tuning(128, 64, 0, 0)
     assert qlib.workspace_query(qlib.INT8, qlib.B_K_MAJOR, 128, 128, 256, t) <= 2 * 128 * 128 * 4
     assert qlib.workspace_query(qlib.BF16, qlib.B_K_MAJOR, 0, 8, 8) == 0
+
+
+def test_plan_query_ex_and_environment_reload(qlib):
+    """Planning is host arithmetic: which kernel configuration a shape gets can be asked without a GPU. The QGEMM_*
+    variables are read when the library is loaded; qgemm_reload_env reads them again."""
+    import os
+    q = qlib
+    big = q.plan_query(q.BF16, q.BF16, q.B_K_MAJOR, 8192, 8192, 8192)
+    assert (big["tile_m"], big["tile_n"], big["ctas_per_tile"], big["split_k"]) == (512, 256, 2, 1)
+    assert big["ctas"] == 148
+    skinny = q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 16, 7168, 2048)
+    assert (skinny["tile_n"], skinny["ctas_per_tile"], skinny["a_rows_per_stage"], skinny["ctas"]) == (64, 1, 16, 112)
+    assert skinny["balanced_tiles"] == 0  # opt-in
+    deep = q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 32, 2048, 8192)
+    assert deep["split_k"] > 1  # few tile columns, long K: split-K is the planner's own choice here
+    os.environ["QGEMM_BALANCE"] = "1"
+    try:
+        assert q.lib().qgemm_reload_env() == q.OK
+        for M, N in ((16, 7168), (64, 7168), (256, 7168), (100, 7000), (128, 2360)):
+            plan = q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, M, N, 2048)
+            m_tiles = -(-M // 128)
+            assert plan["balanced_tiles"] > 0 and plan["balanced_tiles"] * m_tiles <= 148, plan
+            units, tiles, narrow = -(-N // 16), plan["balanced_tiles"], plan["min_tile_n"] // 16
+            wide_tiles = units - tiles * narrow  # tiles one unit wider than the narrowest
+            assert 0 <= wide_tiles < tiles and narrow >= 2
+            assert (narrow + (1 if wide_tiles else 0)) * 16 <= plan["tile_n"]  # the kernel's widest tile covers them
+    finally:
+        del os.environ["QGEMM_BALANCE"]
+        q.lib().qgemm_reload_env()
+    assert q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 16, 7168, 2048)["balanced_tiles"] == 0

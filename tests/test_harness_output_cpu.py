@@ -1,9 +1,9 @@
 """The C++ harness's output format against the reference's OWN result parser.
 
 tests/golden/gemm_benchmark_mixed_bf16.txt is the stdout of `tests/gemm_benchmark mixed bf16` on a B200 (the
-reference's "mixed" shape preset). Where the reference tree is available (QGEMM_REFERENCE_DIR, default
-/root/reference) its scripts/benchmark_to_md.py is loaded from there, unmodified, and must read every problem and
-every row of that output; elsewhere the test is skipped -- the parser is the reference's file and is not copied here."""
+reference's "mixed" shape preset). Where the reference tree is available (QGEMM_REFERENCE_DIR, or its usual mount
+point) its scripts/benchmark_to_md.py is loaded from there, unmodified, and must read every problem and every row of
+that output; elsewhere the test is skipped -- the parser is the reference's file and is not copied here."""
 import importlib.util
 import os
 
