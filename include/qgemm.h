@@ -170,9 +170,12 @@ int qgemm_plan_query(int in_dtype, int out_dtype, int b_layout, size_t M, size_t
  *       there are SMs per tile row, so that every SM pulls an equal share of B (off by default: measured, it does not
  *       pay on B200); [1] is then the widest tile the kernel is built for and
  *   [7] the narrowest tile's width in columns (the widest is 16 more when N / 16 does not divide evenly);
- *   [8] rows of A loaded per pipeline stage; [9] CTAs launched.
+ *   [8] rows of A loaded per pipeline stage; [9] CTAs launched;
+ *   [10] CTAs per cluster when the K slices of [3] are added up inside one launch through distributed shared memory
+ *        (2 or 4), 0 when they go through scratch and a second kernel. QGEMM_KCLUSTER=0 in the environment turns the
+ *        one-launch form off.
  */
-#define QGEMM_PLAN_FIELDS 10
+#define QGEMM_PLAN_FIELDS 11
 int qgemm_plan_query_ex(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, size_t K,
                         const qgemm_tuning_t* tuning, int* out, int n_out);
 

@@ -17,7 +17,7 @@ OBJ_DIR = os.path.join(HERE, "build")
 LIB_PATH = os.path.join(HERE, "libqgemm.so")
 STAMPS_LIB_PATH = os.path.join(HERE, "libqgemm_stamps.so")  # the diagnostic build, beside the product library
 
-SOURCES = ["gemm_f16.cu", "gemm_i8.cu", "gemm_f8.cu", "transpose.cu", "splitk_reduce.cu", "capi.cu", "cxx_api.cu",
+SOURCES = ["gemm_f16.cu", "gemm_i8.cu", "gemm_f8.cu", "gemm_kc_f16.cu", "gemm_kc_i8.cu", "gemm_kc_f8.cu", "transpose.cu", "splitk_reduce.cu", "capi.cu", "cxx_api.cu",
            "no_alloc.cu", "gemm_blockscale.cu", "quantize.cu", "peer.cu", "host_gemm.cu", "int4.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",

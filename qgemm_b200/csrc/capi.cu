@@ -186,6 +186,9 @@ struct Config {
     // Balanced column tiling (GemmParams::bal_units): bal_tiles tile columns of bal_units (+1 for the first
     // bal_wide) sixteen-column units instead of ceil(N / bn) equal ones. bal_tiles == 0: equal tiles.
     int bal_tiles, bal_units, bal_wide;
+    // K slices handled inside one launch by clusters of this many CTAs (gemm_sm100_kcluster.cuh); 0 = the slices are
+    // separate work items whose partial sums go through scratch and splitk_reduce_kernel.
+    int kcluster;
 };
 
 int env_int(const char* name) {
@@ -210,6 +213,8 @@ EnvSettings read_env() {
     e.balance = env_int("QGEMM_BALANCE") > 0 ? 1 : 0;
     const char* pf = std::getenv("QGEMM_PREFETCH");
     e.prefetch_off = (pf != nullptr && pf[0] == '0') ? 1 : 0;
+    const char* kc = std::getenv("QGEMM_KCLUSTER");
+    e.kcluster_off = (kc != nullptr && kc[0] == '0') ? 1 : 0;
     e.host_bands = std::max(0, env_int("QGEMM_HOST_BANDS"));
     e.host_bands_n = std::max(0, env_int("QGEMM_HOST_BANDS_N"));
     return e;
@@ -248,8 +253,11 @@ bool tail_split(long long tiles, int clusters, int kb_total, int* tail_tiles, in
 
 // Estimated duration in units of "one 128-byte K block of a 128x256 tile" (about 0.27 us at peak).
 // `pair` = CTA pairs on 256x256 tiles (half as many schedulable units, a third fewer bytes per flop).
+// `in_cluster` = the K slices of a tile run on the CTAs of one cluster and are added up through distributed shared
+// memory (gemm_sm100_kcluster.cuh): no slabs in global memory, no second kernel.
+constexpr double kClusterReduceCost = 2.0;
 double estimate(int bn, bool pair, int splits, size_t M, size_t N, int kb_total, int sms, int* kbps_out,
-                bool allow_tail = false) {
+                bool allow_tail = false, bool in_cluster = false) {
     const int tile_m = pair ? kPairTileM : kBM;
     const int mt = static_cast<int>((M + tile_m - 1) / tile_m);
     const int nt = static_cast<int>((N + bn - 1) / bn);
@@ -268,7 +276,11 @@ double estimate(int bn, bool pair, int splits, size_t M, size_t N, int kb_total,
     int tt = 0, ts = 0, tk = 0;
     if (pair && real_splits == 1 && allow_tail && tail_split(units, slots, kb_total, &tt, &ts, &tk))
         t = static_cast<double>(waves - 1) * (kbps * t_kb + fill) + (tk * t_kb + fill) + kTailOverhead;
-    if (real_splits > 1) {
+    if (real_splits > 1 && in_cluster) {
+        // full 128-row tiles have four times the partial sums of a 32-row problem to put through shared memory
+        // (measured: FP8 1024 x 512 x 2048 in two slices 6.9 us against 6.0 unsplit, so the split must not be taken there)
+        t += M > 64 ? 2.0 * kClusterReduceCost : kClusterReduceCost;
+    } else if (real_splits > 1) {
         // partial slabs are written once and read once by the second pass (~1.75 MB per unit of time)
         const double slab_bytes = static_cast<double>(real_splits) * M * N * 4.0;
         t += 12.0 + 2.0 * slab_bytes / 1.75e6;
@@ -277,8 +289,16 @@ double estimate(int bn, bool pair, int splits, size_t M, size_t N, int kb_total,
     return t;
 }
 
+// Clusters of `slices` CTAs that run at once: what the device reports, or, without a device (planning queries on a
+// machine without a GPU), seven eighths of SMs / slices -- a GPC's SM count is rarely a multiple of the cluster size.
+int kcluster_capacity(int slices, int sms) {
+    const int n = kcluster_max_clusters(slices);
+    return n > 0 ? n : (sms / slices) * 7 / 8;
+}
+
 Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuning_t* tuning, int min_bn = 64,
-                     bool allow_tail = false, int elem_bytes = 1, bool allow_balance = false) {
+                     bool allow_tail = false, int elem_bytes = 1, bool allow_balance = false,
+                     bool allow_kcluster = false) {
     int want_bn = tuning ? tuning->tile_n : 0;
     int want_split = tuning ? tuning->split_k : 0;
     int want_group = tuning ? tuning->group_m : 0;
@@ -288,7 +308,7 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
     if (!want_group) want_group = g_env.group_m;
     if (!want_pair) want_pair = g_env.cta_pair;
 
-    Config best{256, 1, kb_total, 16, false, false, kBM, 0, 0, 0};
+    Config best{256, 1, kb_total, 16, false, false, kBM, 0, 0, 0, 0};
     double best_t = 1e300;
     struct Cand { int bn; bool pair; };
     const Cand cands[] = {{256, true}, {256, false}, {128, false}, {64, false}};
@@ -309,6 +329,27 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
                 best.pair = c.pair;
                 best.kb_per_split = kbps;
                 best.splits = (kb_total + kbps - 1) / kbps;
+                best.kcluster = 0;
+            }
+            // The same slices inside one launch: 2, 4 or 8 non-empty slices of 64-wide tiles, as many clusters as the
+            // device runs at once (one wave), K-major B, no CTA cap, balanced tiling not switched on. Measured on B200 against the two-launch form at
+            // the same split (graph replay over cold operands, us): FP8 32 x 2048 x 8192 7.5 / 8.7, 128 x 2048 x 16384
+            // 11.6 / 12.9, 128 x 1024 x 4096 6.1 / 6.9; BF16 32 x 2048 x 8192 10.1 / 11.7, 256 x 1024 x 8192 10.9 / 12.4.
+            if (allow_kcluster && g_env.kcluster_off == 0 && g_env.balance == 0 && !c.pair && c.bn == 64 && (s == 2 || s == 4 || s == 8) &&
+                (kb_total + kbps - 1) / kbps == s && !(tuning && tuning->max_ctas != 0) && g_env.max_ctas == 0) {
+                const long long tiles = static_cast<long long>((M + kBM - 1) / kBM) * static_cast<long long>((N + 63) / 64);
+                if (tiles <= kcluster_capacity(s, sms)) {
+                    int kbps2 = 0;
+                    const double tc = estimate(c.bn, false, s, M, N, kb_total, sms, &kbps2, false, true);
+                    if (tc < best_t) {
+                        best_t = tc;
+                        best.bn = c.bn;
+                        best.pair = false;
+                        best.kb_per_split = kbps2;
+                        best.splits = s;
+                        best.kcluster = s;
+                    }
+                }
             }
         }
     }
@@ -430,12 +471,12 @@ int make_plan(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, siz
                  g_env.split_k == 0 && g_env.max_ctas == 0 && g_env.direct_store == 0 && g_env.tail_split_off == 0;
     p->cfg = choose_config(M, N, std::max(p->kb_total, 1), sms, tuning,
                            (b_direct && p->ti.elem_bytes == 1) ? 128 : 64, allow_tail, p->ti.elem_bytes,
-                           allow_balance && !b_direct);
+                           allow_balance && !b_direct, !b_direct);
     p->ld_relayout = round_up(K, 16 / p->ti.elem_bytes);
     p->relayout_bytes =
         (b_layout == QGEMM_B_ROW_MAJOR && !b_direct) ? round_up(N * p->ld_relayout * p->ti.elem_bytes, 256) : 0;
     p->ldw = round_up(N, 4);
-    p->partial_bytes = p->cfg.splits > 1 ? static_cast<size_t>(p->cfg.splits) * M * p->ldw * 4 : 0;
+    p->partial_bytes = (p->cfg.splits > 1 && p->cfg.kcluster == 0) ? static_cast<size_t>(p->cfg.splits) * M * p->ldw * 4 : 0;
     p->tail_tiles = p->tail_slices = p->tail_kb_per_slice = 0;
     if (allow_tail && p->cfg.pair && !p->cfg.wide && p->cfg.splits == 1) {
         const long long tiles = static_cast<long long>((M + kPairTileM - 1) / kPairTileM) *
@@ -547,7 +588,7 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
     p.n_tiles = cfg.bal_tiles > 0 ? cfg.bal_tiles : static_cast<int>((N + cfg.bn - 1) / cfg.bn);
     p.bal_units = cfg.bal_tiles > 0 ? cfg.bal_units : 0;
     p.bal_wide = cfg.bal_tiles > 0 ? cfg.bal_wide : 0;
-    p.splits = cfg.splits;
+    p.splits = cfg.kcluster > 0 ? 1 : cfg.splits;  // in-cluster slices are not work items
     p.kb_total = plan.kb_total;
     p.kb_per_split = cfg.kb_per_split;
     p.group_m = cfg.group_m;
@@ -559,7 +600,7 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
 
     int launch_out = plan.out_kind;
     uint8_t* partials = static_cast<uint8_t*>(st->ws) + plan.relayout_bytes;
-    if (cfg.splits > 1) {
+    if (cfg.splits > 1 && cfg.kcluster == 0) {
         p.C = partials;
         p.ldc = static_cast<long long>(plan.ldw);
         p.split_stride = static_cast<long long>(M) * static_cast<long long>(plan.ldw);
@@ -582,7 +623,7 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
         rc = make_operand_map(b_kmajor, N, K, ldb_k, in_dtype, static_cast<uint32_t>((cfg.bal_units + 1) * 16), &tc);
         if (rc != QGEMM_OK) return rc;
     } else if (p.c_vec_ok && (n_extra > 0 || g_env.direct_store == 0)) {
-        const int map_rc = make_output_map(p.C, M, N, static_cast<uint64_t>(p.ldc), static_cast<uint64_t>(cfg.splits),
+        const int map_rc = make_output_map(p.C, M, N, static_cast<uint64_t>(p.ldc), static_cast<uint64_t>(p.splits),
                                            launch_out, &tc);
         p.c_tma_ok = (map_rc == QGEMM_OK) ? 1 : 0;
     }
@@ -609,11 +650,12 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
     // flight at once): let the CTAs pull B towards L2 ahead of the dependency wait. Measured on B200 (FP8, graph replay
     // over cold operands): 256 x 7168 x 2048 (6 stages for 16 K blocks) 7.86 -> 7.19 us; where the whole K loop fits in
     // the ring it changes nothing (16 / 64 x 7168 x 2048: 6.31 -> 6.24, 6.48 -> 6.42 us) or costs a little (1024^3
-    // 5.42 -> 5.63 us), hence the condition.
+    // 5.42 -> 5.63 us), hence the condition. Not with K slices: there the burst of hints delays the loads themselves
+    // (BF16 32 x 2048 x 8192 in four slices 15.1 -> 11.7 us without, FP8 128 x 2048 x 16384 16.0 -> 12.9 us).
     {
         const int stages = std::min(16, (192 * 1024) / ((cfg.am + cfg.bn) * 128));
-        if (!cfg.pair && !b_direct && cfg.bal_tiles == 0 && work <= st->sm_count && cfg.kb_per_split > stages &&
-            g_env.prefetch_off == 0) {
+        if (!cfg.pair && !b_direct && cfg.bal_tiles == 0 && cfg.splits == 1 && work <= st->sm_count &&
+            cfg.kb_per_split > stages && g_env.prefetch_off == 0) {
             p.prefetch_b = 1;
             p.prefetch_helpers = st->sm_count - static_cast<int>(work);
         }
@@ -651,6 +693,12 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
             case ptx::KIND_I8: e = launch_gemm_pair_i8(launch_out, ta, tb, tc, tws, extra_arg, p, clusters, stream); break;
             default: e = launch_gemm_pair_f8(launch_out, ta, tb, tc, tws, extra_arg, p, clusters, stream); break;
         }
+    } else if (cfg.kcluster > 0) {
+        switch (plan.ti.kind) {
+            case ptx::KIND_F16: e = launch_gemm_kcluster_f16(launch_out, cfg.am, cfg.kcluster, ta, tb, p, static_cast<int>(work), stream); break;
+            case ptx::KIND_I8: e = launch_gemm_kcluster_i8(launch_out, cfg.am, cfg.kcluster, ta, tb, p, static_cast<int>(work), stream); break;
+            default: e = launch_gemm_kcluster_f8(launch_out, cfg.am, cfg.kcluster, ta, tb, p, static_cast<int>(work), stream); break;
+        }
     } else {
         switch (plan.ti.kind) {
             case ptx::KIND_F16: e = launch_gemm_f16(cfg.bn, launch_out, cfg.am, ta, tb, tc, p, grid, stream); break;
@@ -670,7 +718,7 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
         if (rc != QGEMM_OK) return rc;
     }
 
-    if (cfg.splits > 1) {
+    if (cfg.splits > 1 && cfg.kcluster == 0) {
         rc = splitk_reduce_launch(partials, p.split_stride, p.ldc, cfg.splits, plan.ti.acc_int, C,
                                   static_cast<long long>(ldc), p.M, p.N, plan.out_kind, scale_a, scale_b, stream);
         if (rc != QGEMM_OK) return rc;
@@ -951,7 +999,7 @@ int qgemm_plan_query_ex(int in_dtype, int out_dtype, int b_layout, size_t M, siz
     const long long ctas = static_cast<long long>((M + tile_m - 1) / tile_m) * tiles_n * c.splits * (c.pair ? 2 : 1);
     const int vals[QGEMM_PLAN_FIELDS] = {
         tile_m, c.bn, c.pair ? 2 : 1, c.splits, plan.tail_tiles, plan.tail_slices, c.bal_tiles,
-        c.bal_tiles > 0 ? c.bal_units * 16 : c.bn, c.am, static_cast<int>(std::min<long long>(ctas, sms))};
+        c.bal_tiles > 0 ? c.bal_units * 16 : c.bn, c.am, static_cast<int>(std::min<long long>(ctas, sms)), c.kcluster};
     for (int i = 0; i < n_out && i < QGEMM_PLAN_FIELDS; ++i) out[i] = vals[i];
     return QGEMM_OK;
 }

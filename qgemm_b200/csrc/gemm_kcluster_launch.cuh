@@ -1,0 +1,70 @@
+// Host-side launch of the in-cluster split-K kernel (gemm_sm100_kcluster.cuh); one translation unit per kind.
+#pragma once
+#include "gemm_launch.cuh"
+#include "gemm_sm100_kcluster.cuh"
+
+namespace qgemm {
+
+template <int KIND, int OUT, int AM, int S>
+cudaError_t launch_kcluster_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int tiles,
+                                cudaStream_t stream) {
+    constexpr int BN = 64;
+    constexpr int STAGES = StagesFor<BN, AM>::value;
+    auto kernel = gemm_tcgen05_kcluster_kernel<KIND, BN, STAGES, OUT, AM, S>;
+    constexpr int smem = GemmSmem<BN, STAGES, AM>::kDynamicBytes;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!configured[dev]) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(tiles) * S);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = S;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, ta, tb, p);
+}
+
+// `am` = rows of A loaded per stage (128 / 64 / 32 / 16), `slices` = CTAs per cluster = K slices (2, 4 or 8).
+template <int KIND>
+cudaError_t launch_kcluster_kind(int out, int am, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
+                                 const GemmParams& p, int tiles, cudaStream_t stream) {
+#define QGEMM_KC_CASE(OUT_, AM_, S_) \
+    if (out == OUT_ && am == AM_ && slices == S_) return launch_kcluster_one<KIND, OUT_, AM_, S_>(ta, tb, p, tiles, stream);
+#define QGEMM_KC_CASES(AM_, S_)         \
+    QGEMM_KC_CASE(OUT_F32, AM_, S_)     \
+    QGEMM_KC_CASE(OUT_BF16, AM_, S_)    \
+    QGEMM_KC_CASE(OUT_F16, AM_, S_)     \
+    QGEMM_KC_CASE(OUT_RAW32, AM_, S_)
+    QGEMM_KC_CASES(128, 2)
+    QGEMM_KC_CASES(128, 4)
+    QGEMM_KC_CASES(128, 8)
+    QGEMM_KC_CASES(64, 2)
+    QGEMM_KC_CASES(64, 4)
+    QGEMM_KC_CASES(64, 8)
+    QGEMM_KC_CASES(32, 2)
+    QGEMM_KC_CASES(32, 4)
+    QGEMM_KC_CASES(32, 8)
+    QGEMM_KC_CASES(16, 2)
+    QGEMM_KC_CASES(16, 4)
+    QGEMM_KC_CASES(16, 8)
+#undef QGEMM_KC_CASES
+#undef QGEMM_KC_CASE
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace qgemm

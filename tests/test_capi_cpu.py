@@ -114,3 +114,32 @@ def test_plan_query_ex_and_environment_reload(qlib):
         del os.environ["QGEMM_BALANCE"]
         q.lib().qgemm_reload_env()
     assert q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 16, 7168, 2048)["balanced_tiles"] == 0
+
+
+def test_plan_in_cluster_split_k(qlib):
+    """Few 64-wide tiles and a long K: the planner cuts K into 2, 4 or 8 slices that the CTAs of one cluster add up
+    inside one launch (cluster_slices), as many as still fit the device in one wave. Without a device the number of
+    clusters that run at once is taken as seven eighths of SMs / slices."""
+    import os
+    q = qlib
+    for dt in (q.FP8_E4M3, q.BF16, q.INT8):
+        deep = q.plan_query(dt, q.BF16, q.B_K_MAJOR, 32, 2048, 8192)  # 32 tiles: four slices = 128 CTAs
+        assert (deep["tile_n"], deep["split_k"], deep["cluster_slices"], deep["ctas"]) == (64, 4, 4, 128), deep
+        two = q.plan_query(dt, q.BF16, q.B_K_MAJOR, 32, 4096, 4096)  # 64 tiles: two slices
+        assert (two["split_k"], two["cluster_slices"]) == (2, 2), two
+        eight = q.plan_query(dt, q.BF16, q.B_K_MAJOR, 64, 512, 16384)  # 8 tiles: eight slices
+        assert (eight["split_k"], eight["cluster_slices"]) == (8, 8), eight
+    # more tiles than half the SMs, or a short K: no slices
+    assert q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 16, 7168, 2048)["cluster_slices"] == 0
+    assert q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 128, 1024, 512)["split_k"] == 1
+    # a row-major B that is read in place, a CTA cap, or the switch: the slices go through scratch, or there are none
+    assert q.plan_query(q.BF16, q.BF16, q.B_K_MAJOR, 32, 2048, 8192, q.Tuning(0, 0, 0, 64, 0, 0))["cluster_slices"] == 0
+    os.environ["QGEMM_KCLUSTER"] = "0"
+    try:
+        q.lib().qgemm_reload_env()
+        off = q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 32, 2048, 8192)
+        assert off["cluster_slices"] == 0 and off["split_k"] > 1, off
+    finally:
+        del os.environ["QGEMM_KCLUSTER"]
+        q.lib().qgemm_reload_env()
+    assert q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 32, 2048, 8192)["cluster_slices"] == 4
