@@ -213,6 +213,7 @@ EnvSettings read_env() {
     e.balance = env_int("QGEMM_BALANCE") > 0 ? 1 : 0;
     const char* pf = std::getenv("QGEMM_PREFETCH");
     e.prefetch_off = (pf != nullptr && pf[0] == '0') ? 1 : 0;
+    e.prefetch_force = (pf != nullptr && pf[0] == '1') ? 1 : 0;  // experiments: hints wherever the kernel can issue them
     const char* kc = std::getenv("QGEMM_KCLUSTER");
     e.kcluster_off = (kc != nullptr && kc[0] == '0') ? 1 : 0;
     e.host_bands = std::max(0, env_int("QGEMM_HOST_BANDS"));
@@ -331,13 +332,15 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
                 best.splits = (kb_total + kbps - 1) / kbps;
                 best.kcluster = 0;
             }
-            // The same slices inside one launch: 2, 4 or 8 non-empty slices of 64-wide tiles, as many clusters as the
-            // device runs at once (one wave), K-major B, no CTA cap, balanced tiling not switched on. Measured on B200 against the two-launch form at
+            // The same slices inside one launch: 2, 4 or 8 non-empty slices of 64- or 128-wide tiles, as many clusters as the
+            // device runs at once (one wave), K-major B, no CTA cap, balanced tiling not switched on; the 128-wide
+            // tile (which always loads 128 rows of A) only when M has more than 64 rows or the caller asked for it. Measured on B200 against the two-launch form at
             // the same split (graph replay over cold operands, us): FP8 32 x 2048 x 8192 7.5 / 8.7, 128 x 2048 x 16384
             // 11.6 / 12.9, 128 x 1024 x 4096 6.1 / 6.9; BF16 32 x 2048 x 8192 10.1 / 11.7, 256 x 1024 x 8192 10.9 / 12.4.
-            if (allow_kcluster && g_env.kcluster_off == 0 && g_env.balance == 0 && !c.pair && c.bn == 64 && (s == 2 || s == 4 || s == 8) &&
+            if (allow_kcluster && g_env.kcluster_off == 0 && g_env.balance == 0 && !c.pair && (c.bn == 64 || (c.bn == 128 && (M > 64 || want_bn == 128))) && (s == 2 || s == 4 || s == 8) &&
                 (kb_total + kbps - 1) / kbps == s && !(tuning && tuning->max_ctas != 0) && g_env.max_ctas == 0) {
-                const long long tiles = static_cast<long long>((M + kBM - 1) / kBM) * static_cast<long long>((N + 63) / 64);
+                const long long tiles =
+                    static_cast<long long>((M + kBM - 1) / kBM) * static_cast<long long>((N + c.bn - 1) / c.bn);
                 if (tiles <= kcluster_capacity(s, sms)) {
                     int kbps2 = 0;
                     const double tc = estimate(c.bn, false, s, M, N, kb_total, sms, &kbps2, false, true);
@@ -646,19 +649,21 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
     if (!cap) cap = g_env.max_ctas;
     if (cap > 0) grid = std::min(grid, cap);
 
-    // One tile per CTA, B K-major in memory, and a K loop longer than the ring (so that the loads cannot all be in
-    // flight at once): let the CTAs pull B towards L2 ahead of the dependency wait. Measured on B200 (FP8, graph replay
-    // over cold operands): 256 x 7168 x 2048 (6 stages for 16 K blocks) 7.86 -> 7.19 us; where the whole K loop fits in
-    // the ring it changes nothing (16 / 64 x 7168 x 2048: 6.31 -> 6.24, 6.48 -> 6.42 us) or costs a little (1024^3
-    // 5.42 -> 5.63 us), hence the condition. Not with K slices: there the burst of hints delays the loads themselves
-    // (BF16 32 x 2048 x 8192 in four slices 15.1 -> 11.7 us without, FP8 128 x 2048 x 16384 16.0 -> 12.9 us).
+    // One tile per CTA, B K-major in memory, and a K loop a little longer than the ring (so that the loads cannot all be
+    // in flight at once): let the CTAs pull B towards L2 ahead of the dependency wait. Measured on B200 (FP8, graph
+    // replay over cold operands): 256 x 7168 x 2048 (6 stages for 16 K blocks) 7.86 -> 7.19 us; where the whole K loop
+    // fits in the ring it changes nothing (16 / 64 x 7168 x 2048: 6.31 -> 6.24, 6.48 -> 6.42 us) or costs a little
+    // (1024^3 5.42 -> 5.63 us). For a long K loop the burst of hints gets in the way of the loads themselves and the
+    // kernel runs at half speed or worse (FP8 1024 x 2048 x 8192, 64 K blocks: 18.0 us without, 34.3 with; 2048 x 1024 x
+    // 4096: 10.6 / 17.8; the same for K slices, BF16 32 x 2048 x 8192 in four: 11.7 / 15.1), hence the upper limit of
+    // 16 K blocks and no hints for K slices. With the 64-wide tile (8 or more stages) it does not pay either (FP8
+    // 128 x 8192 x 2048: 6.89 us without, 7.37 with): 128-wide tiles only.
     {
         const int stages = std::min(16, (192 * 1024) / ((cfg.am + cfg.bn) * 128));
-        if (!cfg.pair && !b_direct && cfg.bal_tiles == 0 && cfg.splits == 1 && work <= st->sm_count &&
-            cfg.kb_per_split > stages && g_env.prefetch_off == 0) {
+        const bool can = !cfg.pair && !b_direct && cfg.bal_tiles == 0 && cfg.kcluster == 0 && work <= st->sm_count;
+        if (can && (g_env.prefetch_force != 0 || (cfg.splits == 1 && cfg.bn == 128 && cfg.kb_per_split > stages &&
+                                                  cfg.kb_per_split <= 16 && g_env.prefetch_off == 0)))
             p.prefetch_b = 1;
-            p.prefetch_helpers = st->sm_count - static_cast<int>(work);
-        }
     }
 
     cudaError_t e;
@@ -695,9 +700,9 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
         }
     } else if (cfg.kcluster > 0) {
         switch (plan.ti.kind) {
-            case ptx::KIND_F16: e = launch_gemm_kcluster_f16(launch_out, cfg.am, cfg.kcluster, ta, tb, p, static_cast<int>(work), stream); break;
-            case ptx::KIND_I8: e = launch_gemm_kcluster_i8(launch_out, cfg.am, cfg.kcluster, ta, tb, p, static_cast<int>(work), stream); break;
-            default: e = launch_gemm_kcluster_f8(launch_out, cfg.am, cfg.kcluster, ta, tb, p, static_cast<int>(work), stream); break;
+            case ptx::KIND_F16: e = launch_gemm_kcluster_f16(cfg.bn, launch_out, cfg.am, cfg.kcluster, ta, tb, p, static_cast<int>(work), stream); break;
+            case ptx::KIND_I8: e = launch_gemm_kcluster_i8(cfg.bn, launch_out, cfg.am, cfg.kcluster, ta, tb, p, static_cast<int>(work), stream); break;
+            default: e = launch_gemm_kcluster_f8(cfg.bn, launch_out, cfg.am, cfg.kcluster, ta, tb, p, static_cast<int>(work), stream); break;
         }
     } else {
         switch (plan.ti.kind) {

@@ -2,8 +2,8 @@
 #include "gemm_kcluster_launch.cuh"
 
 namespace qgemm {
-cudaError_t launch_gemm_kcluster_f16(int out, int am, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
+cudaError_t launch_gemm_kcluster_f16(int bn, int out, int am, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
                                     const GemmParams& p, int tiles, cudaStream_t stream) {
-    return launch_kcluster_kind<ptx::KIND_F16>(out, am, slices, ta, tb, p, tiles, stream);
+    return launch_kcluster_kind<ptx::KIND_F16>(bn, out, am, slices, ta, tb, p, tiles, stream);
 }
 }  // namespace qgemm

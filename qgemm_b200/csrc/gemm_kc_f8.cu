@@ -2,9 +2,9 @@
 #include "gemm_kcluster_launch.cuh"
 
 namespace qgemm {
-cudaError_t launch_gemm_kcluster_f8(int out, int am, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
+cudaError_t launch_gemm_kcluster_f8(int bn, int out, int am, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
                                     const GemmParams& p, int tiles, cudaStream_t stream) {
-    return launch_kcluster_kind<ptx::KIND_F8>(out, am, slices, ta, tb, p, tiles, stream);
+    return launch_kcluster_kind<ptx::KIND_F8>(bn, out, am, slices, ta, tb, p, tiles, stream);
 }
 
 // How many clusters of `slices` CTAs of this kernel the current device keeps resident at once (a cluster needs its
@@ -19,9 +19,9 @@ static int max_clusters_of() {
         return 0;
     }
     if (cached[dev] != 0) return cached[dev];
-    constexpr int STAGES = StagesFor<64, 128>::value;
-    auto kernel = gemm_tcgen05_kcluster_kernel<ptx::KIND_F8, 64, STAGES, OUT_BF16, 128, S>;
-    constexpr int smem = GemmSmem<64, STAGES, 128>::kDynamicBytes;
+    constexpr int STAGES = StagesFor<128, 128>::value;
+    auto kernel = gemm_tcgen05_kcluster_kernel<ptx::KIND_F8, 128, STAGES, OUT_BF16, 128, S>;
+    constexpr int smem = GemmSmem<128, STAGES, 128>::kDynamicBytes;
     int n = 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(S * 32);

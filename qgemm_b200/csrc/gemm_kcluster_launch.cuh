@@ -5,10 +5,9 @@
 
 namespace qgemm {
 
-template <int KIND, int OUT, int AM, int S>
+template <int KIND, int BN, int OUT, int AM, int S>
 cudaError_t launch_kcluster_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int tiles,
                                 cudaStream_t stream) {
-    constexpr int BN = 64;
     constexpr int STAGES = StagesFor<BN, AM>::value;
     auto kernel = gemm_tcgen05_kcluster_kernel<KIND, BN, STAGES, OUT, AM, S>;
     constexpr int smem = GemmSmem<BN, STAGES, AM>::kDynamicBytes;
@@ -39,29 +38,34 @@ cudaError_t launch_kcluster_one(const CUtensorMap& ta, const CUtensorMap& tb, co
     return cudaLaunchKernelEx(&cfg, kernel, ta, tb, p);
 }
 
-// `am` = rows of A loaded per stage (128 / 64 / 32 / 16), `slices` = CTAs per cluster = K slices (2, 4 or 8).
+// `bn` = tile width (64 or 128), `am` = rows of A loaded per stage (128, or 64 / 32 / 16 with the 64-wide tile),
+// `slices` = CTAs per cluster = K slices (2, 4 or 8).
 template <int KIND>
-cudaError_t launch_kcluster_kind(int out, int am, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
+cudaError_t launch_kcluster_kind(int bn, int out, int am, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
                                  const GemmParams& p, int tiles, cudaStream_t stream) {
-#define QGEMM_KC_CASE(OUT_, AM_, S_) \
-    if (out == OUT_ && am == AM_ && slices == S_) return launch_kcluster_one<KIND, OUT_, AM_, S_>(ta, tb, p, tiles, stream);
-#define QGEMM_KC_CASES(AM_, S_)         \
-    QGEMM_KC_CASE(OUT_F32, AM_, S_)     \
-    QGEMM_KC_CASE(OUT_BF16, AM_, S_)    \
-    QGEMM_KC_CASE(OUT_F16, AM_, S_)     \
-    QGEMM_KC_CASE(OUT_RAW32, AM_, S_)
-    QGEMM_KC_CASES(128, 2)
-    QGEMM_KC_CASES(128, 4)
-    QGEMM_KC_CASES(128, 8)
-    QGEMM_KC_CASES(64, 2)
-    QGEMM_KC_CASES(64, 4)
-    QGEMM_KC_CASES(64, 8)
-    QGEMM_KC_CASES(32, 2)
-    QGEMM_KC_CASES(32, 4)
-    QGEMM_KC_CASES(32, 8)
-    QGEMM_KC_CASES(16, 2)
-    QGEMM_KC_CASES(16, 4)
-    QGEMM_KC_CASES(16, 8)
+#define QGEMM_KC_CASE(BN_, OUT_, AM_, S_)                          \
+    if (bn == BN_ && out == OUT_ && am == AM_ && slices == S_) \
+        return launch_kcluster_one<KIND, BN_, OUT_, AM_, S_>(ta, tb, p, tiles, stream);
+#define QGEMM_KC_CASES(BN_, AM_, S_)         \
+    QGEMM_KC_CASE(BN_, OUT_F32, AM_, S_)     \
+    QGEMM_KC_CASE(BN_, OUT_BF16, AM_, S_)    \
+    QGEMM_KC_CASE(BN_, OUT_F16, AM_, S_)     \
+    QGEMM_KC_CASE(BN_, OUT_RAW32, AM_, S_)
+    QGEMM_KC_CASES(128, 128, 2)
+    QGEMM_KC_CASES(128, 128, 4)
+    QGEMM_KC_CASES(128, 128, 8)
+    QGEMM_KC_CASES(64, 128, 2)
+    QGEMM_KC_CASES(64, 128, 4)
+    QGEMM_KC_CASES(64, 128, 8)
+    QGEMM_KC_CASES(64, 64, 2)
+    QGEMM_KC_CASES(64, 64, 4)
+    QGEMM_KC_CASES(64, 64, 8)
+    QGEMM_KC_CASES(64, 32, 2)
+    QGEMM_KC_CASES(64, 32, 4)
+    QGEMM_KC_CASES(64, 32, 8)
+    QGEMM_KC_CASES(64, 16, 2)
+    QGEMM_KC_CASES(64, 16, 4)
+    QGEMM_KC_CASES(64, 16, 8)
 #undef QGEMM_KC_CASES
 #undef QGEMM_KC_CASE
     return cudaErrorInvalidValue;

@@ -239,12 +239,12 @@ int splitk_reduce_tiles_launch(const void* partials, int slots, int splits, bool
                                int M, int N, int out_kind, const float* scale_a, const float* scale_b,
                                const GemmParams& tiles, cudaStream_t stream);
 
-// In-cluster split-K (gemm_sm100_kcluster.cuh; gemm_kc_*.cu): `tiles` clusters of `slices` CTAs, 64-wide tiles.
-cudaError_t launch_gemm_kcluster_f16(int out, int am, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
+// In-cluster split-K (gemm_sm100_kcluster.cuh; gemm_kc_*.cu): `tiles` clusters of `slices` CTAs, 64- or 128-wide tiles.
+cudaError_t launch_gemm_kcluster_f16(int bn, int out, int am, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
                                      const GemmParams& p, int tiles, cudaStream_t stream);
-cudaError_t launch_gemm_kcluster_i8(int out, int am, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
+cudaError_t launch_gemm_kcluster_i8(int bn, int out, int am, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
                                     const GemmParams& p, int tiles, cudaStream_t stream);
-cudaError_t launch_gemm_kcluster_f8(int out, int am, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
+cudaError_t launch_gemm_kcluster_f8(int bn, int out, int am, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
                                     const GemmParams& p, int tiles, cudaStream_t stream);
 // Clusters of `slices` CTAs the current device keeps resident at once; 0 = unknown (no device).
 int kcluster_max_clusters(int slices);

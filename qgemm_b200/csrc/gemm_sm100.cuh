@@ -66,12 +66,9 @@ struct GemmParams {
     // the same share of B to pull from HBM). bal_units == 0: equal tiles. Widths never exceed the kernel's BN.
     int bal_units;
     int bal_wide;
-    // Single-wave problems whose K loop is longer than the ring (one tile per CTA, HBM-bound): before the dependency
-    // wait, while the predecessor in the stream is still running, the CTA asks for its B tile to be brought into L2;
-    // the CTAs below prefetch_helpers (those that find an idle SM at once when the predecessor's grid was as small as
-    // this one) do the same for the tiles of CTAs prefetch_helpers, 2 * prefetch_helpers, ... further on. 0 / 0 = off.
+    // Single-wave problems whose K loop is a little longer than the ring (one tile per CTA): before the dependency wait,
+    // while the predecessor in the stream is still running, the CTA asks for its B tile to be brought into L2. 0 = off.
     int prefetch_b;
-    int prefetch_helpers;
     int test_skip_kb;  // failure-detection test hook: the producer leaves out the loads of this K block (-1 = none),
                        // so the consumer's bounded wait runs out and the kernel returns through its error path
 };
@@ -429,15 +426,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     if (p.prefetch_b && warp == 2 && static_cast<int>(blockIdx.x) < total_work) {
         // B does not wait for the predecessor: a hint into L2 is harmless even if B were still being written
-        for (int w = blockIdx.x; w < total_work; w += max(1, p.prefetch_helpers)) {
-            const TileCoord t = decode_tile(w, p);
-            int col0, width;
-            tile_columns(p, t.n_blk, BN, col0, width);
-            const int kb0 = t.split * p.kb_per_split;
-            const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
-            for (int kb = kb0 + lane; kb < kb1; kb += 32) ptx::tma_prefetch_l2_2d(&tmap_b, kb * BK, col0);
-            if (p.prefetch_helpers <= 0 || static_cast<int>(blockIdx.x) >= p.prefetch_helpers) break;
-        }
+        const TileCoord t = decode_tile(blockIdx.x, p);
+        int col0, width;
+        tile_columns(p, t.n_blk, BN, col0, width);
+        const int kb0 = t.split * p.kb_per_split;
+        const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+        for (int kb = kb0 + lane; kb < kb1; kb += 32) ptx::tma_prefetch_l2_2d(&tmap_b, kb * BK, col0);
     }
     // This CTA's first tile is decoded here, while the predecessor in the stream may still be running: the integer
     // divisions of decode_tile would otherwise sit between the predecessor's end and the first load (a skinny problem

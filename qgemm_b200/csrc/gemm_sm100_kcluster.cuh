@@ -32,7 +32,7 @@ gemm_tcgen05_kcluster_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
                              const GemmParams p) {
     using L = GemmSmem<BN, STAGES, AM>;
     static_assert(S == 2 || S == 4 || S == 8, "cluster size (8 is the largest portable one)");
-    static_assert(BN == 64, "sixteen threads x four columns cover a row of the tile");
+    static_assert(BN == 64 || BN == 128, "BN / 4 threads x four columns cover a row of the tile");
     static_assert(kBM * (BN + kKcPad) * 4 <= L::kTiles, "the partial tile fits in the pipeline's ring");
     static_assert(STAGES * L::kAStage + (kBM - AM) * 128 <= L::kTiles, "the MMA's 128-row read of A stays inside the tile area");
     constexpr int ELT = (KIND == ptx::KIND_F16) ? 2 : 1;
@@ -171,11 +171,12 @@ gemm_tcgen05_kcluster_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
     ptx::cluster_wait();
 
     // ---------------------------------------------------------------- step 4: this CTA's rows of the sum
-    // The tile's valid rows are dealt out over the S CTAs. Sixteen threads share a row, four columns each, so that a
-    // warp's read of a peer's shared memory is two contiguous 256-byte runs and its store to C two contiguous runs too.
+    // The tile's valid rows are dealt out over the S CTAs. BN / 4 threads share a row, four columns each, so that a
+    // warp's read of a peer's shared memory is one or two contiguous runs of 256 bytes or more, and its store to C too.
     if (warp >= 2 && *abort_flag == 0) {
         const int e = static_cast<int>(threadIdx.x) - 64;  // 0..127
-        const int sub = e & 15;
+        constexpr int TPR = BN / 4;  // threads per row
+        const int sub = e & (TPR - 1);
         const int rows_valid = min(kBM, p.M - t.m_blk * kBM);
         const int rows_per_cta = (rows_valid + S - 1) / S;
         const int r0 = static_cast<int>(rank) * rows_per_cta;
@@ -190,7 +191,7 @@ gemm_tcgen05_kcluster_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
         constexpr int OB = OutBytes<OUT>::value;
         if (n_valid > 0) {
 #pragma unroll 2
-            for (int r = r0 + (e >> 4); r < r1; r += 8) {
+            for (int r = r0 + e / TPR; r < r1; r += 128 / TPR) {
                 const uint32_t own = smem_base + static_cast<uint32_t>((r * ROW_WORDS + sub * 4) * 4);
                 uint32_t w[S][4];
 #pragma unroll

@@ -77,9 +77,12 @@ def test_workspace_planning(qlib):
     # row-major B needs a relaid-out copy: N * round_up(K, 8) * 2 bytes for bf16
     assert qlib.workspace_query(qlib.BF16, qlib.B_ROW_MAJOR, 8192, 8192, 8192) == 8192 * 8192 * 2
     assert qlib.workspace_query(qlib.BF16, qlib.B_K_MAJOR, 8192, 8192, 8192) == 0
-    # an explicit split-K adds splits * M * round_up(N, 4) * 4 bytes of partial sums
+    # an explicit split-K whose slices go through scratch adds splits * M * round_up(N, 4) * 4 bytes of partial sums
+    t = qlib.Tuning(128, 3, 0, 0)
+    assert qlib.workspace_query(qlib.INT8, qlib.B_K_MAJOR, 100, 518, 2048, t) == 3 * 100 * 520 * 4
+    # 2, 4 or 8 slices of few tiles are added up inside the launch (clusters): no partial sums in scratch
     t = qlib.Tuning(128, 4, 0, 0)
-    assert qlib.workspace_query(qlib.INT8, qlib.B_K_MAJOR, 100, 518, 2048, t) == 4 * 100 * 520 * 4
+    assert qlib.workspace_query(qlib.INT8, qlib.B_K_MAJOR, 100, 518, 2048, t) == 0
     # more splits than 128-byte K blocks cannot be honoured: the plan falls back to what exists
     t = qlib.Tuning(128, 64, 0, 0)
     assert qlib.workspace_query(qlib.INT8, qlib.B_K_MAJOR, 128, 128, 256, t) <= 2 * 128 * 128 * 4

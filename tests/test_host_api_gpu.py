@@ -110,9 +110,10 @@ def test_scratch_grows_on_demand_and_survives_shutdown(qlib, oracle, dev):
     bi = datagen.int8_uniform((K, N), seed=2, stream=1)
     a, b = torch.from_numpy(ai).to(dev), torch.from_numpy(bi).to(dev)
     acc = torch.zeros((M, N), dtype=torch.int32, device=dev)
-    q.gemm(a, b, acc, b_kmajor=False, tuning=q.Tuning(128, 4, 0, 0, -1, 0))
-    need = q.workspace_query(q.INT8, q.B_ROW_MAJOR, M, N, K, q.Tuning(128, 4, 0, 0, -1, 0))
-    assert need >= N * K + 4 * M * 1032 * 4
+    # three slices: not a cluster size, so the partial sums go through scratch
+    q.gemm(a, b, acc, b_kmajor=False, tuning=q.Tuning(128, 3, 0, 0, -1, 0))
+    need = q.workspace_query(q.INT8, q.B_ROW_MAJOR, M, N, K, q.Tuning(128, 3, 0, 0, -1, 0))
+    assert need >= N * K + 3 * M * 1032 * 4
     assert q.lib().qgemm_workspace_bytes() >= need
     assert np.array_equal(acc.cpu().numpy(), oracle.gemm_i8(ai, bi, False))
     q.shutdown()

@@ -1,4 +1,4 @@
-"""Split-K inside one launch (gemm_sm100_kcluster.cuh): the K slices of a 64-wide tile run on the CTAs of one
+"""Split-K inside one launch (gemm_sm100_kcluster.cuh): the K slices of a 64- or 128-wide tile run on the CTAs of one
 cluster, and the partial sums are added up through distributed shared memory in slice order -- the order in which
 splitk_reduce_kernel adds the slabs of the two-launch form. So the two forms must agree BIT FOR BIT for every input
 type, and both are checked against the oracle at their tier. QGEMM_KCLUSTER=0 (read when the library reads its
@@ -28,18 +28,19 @@ def _two_launch(q, fn):
         q.lib().qgemm_reload_env()
 
 
-def _tuning(q, slices):
-    return q.Tuning(64, slices, 0, 0, -1, 0)
+def _tuning(q, slices, bn=64):
+    return q.Tuning(bn, slices, 0, 0, -1, 0)
 
 
-def _expect_cluster(q, in_dt, out_dt, M, N, K, slices):
+def _expect_cluster(q, in_dt, out_dt, M, N, K, slices, bn=64):
     """Whether the one-launch form applies: the slices must be non-empty and the clusters fit the SMs in one wave."""
     elem = 2 if in_dt in (q.BF16, q.FP16) else 1
     kb = -(-K // (128 // elem))
     kbps = -(-kb // slices)
     real = -(-kb // kbps)
-    tiles = -(-M // 128) * -(-N // 64)
-    plan = q.plan_query(in_dt, out_dt, q.B_K_MAJOR, M, N, K, _tuning(q, slices))
+    tiles = -(-M // 128) * -(-N // bn)
+    plan = q.plan_query(in_dt, out_dt, q.B_K_MAJOR, M, N, K, _tuning(q, slices, bn))
+    assert plan["tile_n"] == bn
     # how many clusters run at once is the device's answer (a cluster's CTAs share a GPC): well below the SM count the
     # one-launch form must be taken, above it it cannot be
     if real != slices or tiles * slices > 148:
@@ -50,21 +51,22 @@ def _expect_cluster(q, in_dt, out_dt, M, N, K, slices):
         want = plan["cluster_slices"]
         assert want in (0, slices), plan
     assert plan["cluster_slices"] == want, (plan, want)
-    assert _two_launch(q, lambda: q.plan_query(in_dt, out_dt, q.B_K_MAJOR, M, N, K, _tuning(q, slices)))[
+    assert _two_launch(q, lambda: q.plan_query(in_dt, out_dt, q.B_K_MAJOR, M, N, K, _tuning(q, slices, bn)))[
         "cluster_slices"] == 0
     return want
 
 
+@pytest.mark.parametrize("bn", [64, 128])
 @pytest.mark.parametrize("slices", [2, 4, 8])
 @pytest.mark.parametrize("M,N,K", SHAPES)
-def test_int8_accumulator_and_scaled_output(qlib, oracle, dev, M, N, K, slices):
+def test_int8_accumulator_and_scaled_output(qlib, oracle, dev, M, N, K, slices, bn):
     q = qlib
     ai = datagen.int8_uniform((M, K), seed=M + K, stream=0)
     bi = datagen.int8_uniform((N, K), seed=M + K, stream=1)
     a, b = torch.from_numpy(ai).to(dev), torch.from_numpy(bi).to(dev)
-    _expect_cluster(q, q.INT8, q.INT32, M, N, K, slices)
+    _expect_cluster(q, q.INT8, q.INT32, M, N, K, slices, bn)
     acc = torch.full((M, N), -7, dtype=torch.int32, device=dev)
-    q.gemm(a, b, acc, b_kmajor=True, tuning=_tuning(q, slices))
+    q.gemm(a, b, acc, b_kmajor=True, tuning=_tuning(q, slices, bn))
     ref = oracle.gemm_i8(ai, bi, True)
     assert np.array_equal(acc.cpu().numpy(), ref)
     sa, sb = datagen.scale_pair(3)
@@ -72,21 +74,22 @@ def test_int8_accumulator_and_scaled_output(qlib, oracle, dev, M, N, K, slices):
     for dt in (torch.bfloat16, torch.float16, torch.float32):
         c1 = torch.full((M, N), -3, dtype=dt, device=dev)
         c2 = torch.full((M, N), -4, dtype=dt, device=dev)
-        q.mix_gemm(a, b, tsa, tsb, c1, b_kmajor=True, tuning=_tuning(q, slices))
-        _two_launch(q, lambda: q.mix_gemm(a, b, tsa, tsb, c2, b_kmajor=True, tuning=_tuning(q, slices)))
+        q.mix_gemm(a, b, tsa, tsb, c1, b_kmajor=True, tuning=_tuning(q, slices, bn))
+        _two_launch(q, lambda: q.mix_gemm(a, b, tsa, tsb, c2, b_kmajor=True, tuning=_tuning(q, slices, bn)))
         assert torch.equal(c1.view(torch.uint8), c2.view(torch.uint8)), dt
     c = torch.zeros((M, N), dtype=torch.bfloat16, device=dev)
-    q.mix_gemm(a, b, tsa, tsb, c, b_kmajor=True, tuning=_tuning(q, slices))
+    q.mix_gemm(a, b, tsa, tsb, c, b_kmajor=True, tuning=_tuning(q, slices, bn))
     bits = c.view(torch.int16).cpu().numpy().view(np.uint16)
     assert oracle.bf16_ulp_distance(bits, oracle.scale_cast(ref, float(sa), float(sb), oracle.OUT_BF16)) <= 1
     rc, st = q.device_status()
     assert rc == 0, st
 
 
+@pytest.mark.parametrize("bn", [64, 128])
 @pytest.mark.parametrize("slices", [2, 4, 8])
 @pytest.mark.parametrize("kind", ["bf16", "fp16", "fp8"])
 @pytest.mark.parametrize("M,N,K", SHAPES)
-def test_float_kinds_match_two_launch_form_bit_for_bit(qlib, oracle, dev, M, N, K, kind, slices):
+def test_float_kinds_match_two_launch_form_bit_for_bit(qlib, oracle, dev, M, N, K, kind, slices, bn):
     q = qlib
     a32, b32 = datagen.normal((M, K), M + N, 0), datagen.normal((N, K), M + N, 1)
     if kind == "fp8":
@@ -99,12 +102,12 @@ def test_float_kinds_match_two_launch_form_bit_for_bit(qlib, oracle, dev, M, N, 
         in_dt = q.BF16 if kind == "bf16" else q.FP16
     ref = oracle.gemm_f32(a.float().numpy(), b.float().numpy(), True)
     a, b = a.to(dev), b.to(dev)
-    _expect_cluster(q, in_dt, q.FP32, M, N, K, slices)
+    _expect_cluster(q, in_dt, q.FP32, M, N, K, slices, bn)
     for dt in (torch.float32, torch.bfloat16):
         c1 = torch.full((M, N), -3, dtype=dt, device=dev)
         c2 = torch.full((M, N), -4, dtype=dt, device=dev)
-        q.gemm(a, b, c1, b_kmajor=True, tuning=_tuning(q, slices))
-        _two_launch(q, lambda: q.gemm(a, b, c2, b_kmajor=True, tuning=_tuning(q, slices)))
+        q.gemm(a, b, c1, b_kmajor=True, tuning=_tuning(q, slices, bn))
+        _two_launch(q, lambda: q.gemm(a, b, c2, b_kmajor=True, tuning=_tuning(q, slices, bn)))
         assert torch.equal(c1.view(torch.uint8), c2.view(torch.uint8)), dt
         got = c1.float().cpu().numpy()
         if kind == "fp8":
