@@ -19,7 +19,8 @@ The ONE JSON line printed by rank 0 also carries
     (strong scaling): GEMM-only time, and for N > 1 the NCCL all-gather of the C slices and the variant whose
     epilogue stores every tile to all ranks' full matrices over NVLink;
   * `configs` (N = 1): a short measurement of each other configuration -- FP16 1024^3, int8 and FP8 8192^3, the
-    FP8 skinny-to-square sweep with the library's scaled GEMM timed beside it, the block-scaled FP8 GEMM, the
+    FP8 skinny-to-square sweep and two few-tiles-long-K shapes (split-K inside one launch) with the library's GEMM
+    timed beside them, the block-scaled FP8 GEMM, the
     1- and 2-byte transpose and the quantise pre-pass -- each with its own roofline fraction and oracle check;
   * `cpu_baseline` (N = 1): the CPU restatement of the reference semantics (the reference ships no CPU GEMM).
 
@@ -46,6 +47,7 @@ NCU_TRAFFIC_BYTES = {
     "c2_bf16_8192": 883.1e6 + 120.8e6,
     "c3_int8_8192": 237.3e6 + 115.2e6,
     "c4_fp8_16": 14.74e6,
+    "d1_fp8_deep": 35.67e6,
     "f1_fp8_blockscale": 131.1e6 + 40.1e6,
 }
 
@@ -70,11 +72,14 @@ WORKLOADS = {
     "f1_fp8_blockscale": ("fp8", "bf16", 4096, 7168, 7168, True,
                           "FP8 e4m3 GEMM with block scales (per row x 128-K block of A, per 128x128 block of B), "
                           "M=4096 N=K=7168, bf16 out: the reference's fp8_mm semantics"),
+    "d1_fp8_deep": ("fp8", "bf16", 128, 2048, 16384, True,
+                    "FP8 e4m3 M=128 N=2048 K=16384 (few tiles, long K: split-K inside one launch), bf16 out"),
+    "d2_bf16_deep": ("bf16", "bf16", 32, 2048, 8192, True, "BF16 M=32 N=2048 K=8192 (few tiles, long K), bf16 out"),
     "c5_int8_sharded": ("int8", "bf16", 32768, 32768, 8192, True,
                         "int8 mixed GEMM 32768x32768x8192, B/C column-sharded over the ranks (strong scaling)"),
 }
 CONFIG_BLOCK = ["c1_fp16_1024", "c3_int8_8192", "c3_fp8_8192", "c4_fp8_16", "c4_fp8_64", "c4_fp8_256", "c4_fp8_1024",
-                "c4_fp8_6144", "f1_fp8_blockscale"]
+                "c4_fp8_6144", "d1_fp8_deep", "d2_bf16_deep", "f1_fp8_blockscale"]
 
 
 _REAL_STDOUT = None
@@ -531,7 +536,7 @@ def roofline_of(ctx, ops, kernel_ms, plan, kernel_name):
 def kernel_name_of(ops, plan):
     if ops["blockscale"]:
         return "fp8_blockscale_kernel"
-    if plan.get("k_cluster", 0) > 1:
+    if plan.get("cluster_slices", 0) > 1:
         return "gemm_tcgen05_kcluster_kernel"
     return ("gemm_tcgen05_wide_pair_kernel" if plan["tile_m"] == 512 else
             "gemm_tcgen05_pair_kernel" if plan["ctas_per_tile"] == 2 else "gemm_tcgen05_kernel")
@@ -923,7 +928,8 @@ def run_c5(ctx, args):
 def run_config(ctx, args, name):
     """A short measurement of one configuration on one GPU: the step through the public call (graph replay over
     rotating operand sets when the operands fit in L2), its roofline fraction, plan, clocks and oracle check; for
-    the FP8 sweep the library's scaled GEMM (torch._scaled_mm, cuBLASLt) timed the same way beside it."""
+    the FP8 sweep and the two long-K shapes the library's GEMM (torch._scaled_mm / torch.matmul) timed the same way
+    beside it."""
     torch, q = ctx.torch, ctx.q
     ops = make_operands(ctx, name, 0 if name == "c1_fp16_1024" else args.seed, pin=False)
     sets, set_bytes = rotating_sets(ctx, ops)
@@ -950,19 +956,23 @@ def run_config(ctx, args, name):
     out = {"description": WORKLOADS[name][6], "shape": [ops["M"], ops["N"], ops["K"]], "us": best * 1e3,
            "tflops": roof.get("tflops", roof["achieved"]), "roofline": roof, "sm_mhz": mhz, "steps": steps,
            "timed_loop": ("CUDA graph replay over %d rotating operand sets" % nsets) if use_graph else "direct launches"}
-    if name.startswith("c4_") or name == "c3_fp8_8192":
+    if name.startswith(("c4_", "d1_", "d2_")) or name == "c3_fp8_8192":
         try:
             lcnt = [0]
 
             def lib_call():
-                a_, b_, _ = sets[lcnt[0] % nsets]
+                a_, b_, c_ = sets[lcnt[0] % nsets]
                 lcnt[0] += 1
-                torch._scaled_mm(a_, b_.t(), scale_a=ops["sa"], scale_b=ops["sb"], out_dtype=torch.bfloat16)
+                if ops["in_name"] == "fp8":
+                    torch._scaled_mm(a_, b_.t(), scale_a=ops["sa"], scale_b=ops["sb"], out_dtype=torch.bfloat16)
+                else:
+                    torch.matmul(a_, b_.t(), out=c_)
 
             for _ in range(3):
                 lib_call()
             lbest = min(ctx.timed(lib_call, steps, use_graph, sync_ranks=False)[0] / steps for _ in range(2))
             out["library_scaled_mm_us"] = lbest * 1e3
+            out["library"] = "torch._scaled_mm (cuBLASLt)" if ops["in_name"] == "fp8" else "torch.matmul (cuBLAS)"
             out["vs_library"] = lbest / best
         except Exception as exc:
             out["library_scaled_mm_us"] = None
