@@ -237,6 +237,7 @@ int g_test_skip_kb = -1;
 // 2560 x 2048 x 4096 (80 tiles on 74 clusters) 61 -> 51 us; with R = 34 (4096^3) the split gains nothing, because
 // the part runs at its power cap and a half-empty last wave simply runs at a higher clock.
 constexpr double kPairTimePerKb = 0.93;
+constexpr double kPair128TimePerKb = 0.45;  // 256 x 128 pair tiles against 0.56 for a lone 128 x 128 tile
 constexpr double kTailOverhead = 16.0;
 bool tail_split(long long tiles, int clusters, int kb_total, int* tail_tiles, int* slices, int* kb_per_slice) {
     if (clusters <= 0 || tiles <= clusters) return false;
@@ -269,13 +270,14 @@ double estimate(int bn, bool pair, int splits, size_t M, size_t N, int kb_total,
     const long long waves = (units + slots - 1) / slots;
     // time per K block of one unit, and pipeline fill + epilogue drain per unit
     double t_kb, fill;
-    if (pair) { t_kb = kPairTimePerKb; fill = 6.0; }
+    if (pair && bn == 128) { t_kb = kPair128TimePerKb; fill = 7.0; }
+    else if (pair) { t_kb = kPairTimePerKb; fill = 6.0; }
     else if (bn == 256) { t_kb = 1.0; fill = 6.0; }
     else if (bn == 128) { t_kb = 0.56; fill = 4.5; }   // narrower tiles re-read A relatively more often
     else { t_kb = 0.33; fill = 4.0; }
     double t = static_cast<double>(waves) * (kbps * t_kb + fill);
     int tt = 0, ts = 0, tk = 0;
-    if (pair && real_splits == 1 && allow_tail && tail_split(units, slots, kb_total, &tt, &ts, &tk))
+    if (pair && bn == kPairTileN && real_splits == 1 && allow_tail && tail_split(units, slots, kb_total, &tt, &ts, &tk))
         t = static_cast<double>(waves - 1) * (kbps * t_kb + fill) + (tk * t_kb + fill) + kTailOverhead;
     if (real_splits > 1 && in_cluster) {
         // full 128-row tiles have four times the partial sums of a 32-row problem to put through shared memory
@@ -299,7 +301,7 @@ int kcluster_capacity(int slices, int sms) {
 
 Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuning_t* tuning, int min_bn = 64,
                      bool allow_tail = false, int elem_bytes = 1, bool allow_balance = false,
-                     bool allow_kcluster = false) {
+                     bool allow_kcluster = false, bool allow_pair128 = false) {
     int want_bn = tuning ? tuning->tile_n : 0;
     int want_split = tuning ? tuning->split_k : 0;
     int want_group = tuning ? tuning->group_m : 0;
@@ -312,9 +314,20 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
     Config best{256, 1, kb_total, 16, false, false, kBM, 0, 0, 0, 0};
     double best_t = 1e300;
     struct Cand { int bn; bool pair; };
-    const Cand cands[] = {{256, true}, {256, false}, {128, false}, {64, false}};
+    const Cand cands[] = {{256, true}, {128, true}, {256, false}, {128, false}, {64, false}};
     for (const Cand& c : cands) {
-        if (c.pair && (want_pair < 0 || (want_bn && want_bn != 256))) continue;
+        if (c.pair && (want_pair < 0 || (want_bn && want_bn != c.bn))) continue;
+        // 256 x 128 pair tiles: K-major B in memory, one destination, not with the 512 x 256 override, and (unless
+        // the caller asks for them) only when all tiles run in one wave -- that is where they were measured against one
+        // wave of lone 128 x 128 tiles (us, graph replay over cold operands): BF16 1024 x 2048 x 8192 31.5 / 35.5, 2048 x
+        // 1024 x 4096 16.8 / 17.8, 1280 x 1280 x 4096 15.8 / 17.9; FP8 1024 x 2048 x 8192 17.4 / 18.3, 1536 x 1536 x 6144
+        // 14.5 / 15.0; over several waves the 256 x 256 pairs win (FP8 4096^3 56.0 against 67.2).
+        if (c.pair && c.bn == 128) {
+            if (!allow_pair128 || want_pair == 2) continue;
+            const long long tiles128 = static_cast<long long>((M + kPairTileM - 1) / kPairTileM) *
+                                       static_cast<long long>((N + 127) / 128);
+            if (!(want_pair > 0 && want_bn == 128) && tiles128 > sms / 2) continue;
+        }
         if (!c.pair && want_pair > 0) continue;
         if (want_bn && c.bn != want_bn) continue;
         if (c.bn < min_bn) continue;
@@ -404,7 +417,7 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
     const long long wide_tiles = static_cast<long long>((M + kWideTileM - 1) / kWideTileM) *
                                  static_cast<long long>((N + kWideTileN - 1) / kWideTileN);
     const bool auto_wide = want_pair == 0 && elem_bytes == 2 && kb_total >= 96 && wide_tiles >= 6ll * (sms / 2);
-    best.wide = (want_pair == 2 || auto_wide) && best.pair && best.splits == 1;
+    best.wide = (want_pair == 2 || auto_wide) && best.pair && best.bn == 256 && best.splits == 1;
     const long long panel_rows = (32ll << 20) / (static_cast<long long>(kb_total) * 128);
     const int tile_m = best.wide ? kWideTileM : (best.pair ? kPairTileM : kBM);
     const int auto_group = static_cast<int>(std::max<long long>(4, std::min<long long>(4096, panel_rows / tile_m)));
@@ -474,14 +487,14 @@ int make_plan(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, siz
                  g_env.split_k == 0 && g_env.max_ctas == 0 && g_env.direct_store == 0 && g_env.tail_split_off == 0;
     p->cfg = choose_config(M, N, std::max(p->kb_total, 1), sms, tuning,
                            (b_direct && p->ti.elem_bytes == 1) ? 128 : 64, allow_tail, p->ti.elem_bytes,
-                           allow_balance && !b_direct, !b_direct);
+                           allow_balance && !b_direct, !b_direct, !b_direct && allow_balance);
     p->ld_relayout = round_up(K, 16 / p->ti.elem_bytes);
     p->relayout_bytes =
         (b_layout == QGEMM_B_ROW_MAJOR && !b_direct) ? round_up(N * p->ld_relayout * p->ti.elem_bytes, 256) : 0;
     p->ldw = round_up(N, 4);
     p->partial_bytes = (p->cfg.splits > 1 && p->cfg.kcluster == 0) ? static_cast<size_t>(p->cfg.splits) * M * p->ldw * 4 : 0;
     p->tail_tiles = p->tail_slices = p->tail_kb_per_slice = 0;
-    if (allow_tail && p->cfg.pair && !p->cfg.wide && p->cfg.splits == 1) {
+    if (allow_tail && p->cfg.pair && p->cfg.bn == kPairTileN && !p->cfg.wide && p->cfg.splits == 1) {
         const long long tiles = static_cast<long long>((M + kPairTileM - 1) / kPairTileM) *
                                 static_cast<long long>((N + kPairTileN - 1) / kPairTileN);
         if (tail_split(tiles, sms / 2, p->kb_total, &p->tail_tiles, &p->tail_slices, &p->tail_kb_per_slice))
@@ -577,7 +590,7 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
         rc = make_operand_map(B, K, N, ldb, in_dtype, 128u / static_cast<uint32_t>(es), &tb);
     else
         rc = make_operand_map(b_kmajor, N, K, ldb_k, in_dtype,
-                              cfg.pair ? 128u : (cfg.bal_tiles > 0 ? static_cast<uint32_t>(cfg.bal_units * 16)
+                              cfg.pair ? static_cast<uint32_t>(cfg.bn / 2) : (cfg.bal_tiles > 0 ? static_cast<uint32_t>(cfg.bal_units * 16)
                                                                    : static_cast<uint32_t>(cfg.bn)), &tb);
     if (rc != QGEMM_OK) return rc;
 
@@ -694,9 +707,9 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
         int clusters = static_cast<int>(std::min<long long>(p.total_work, st->sm_count / 2));
         if (cap > 0) clusters = std::min(clusters, std::max(1, cap / 2));
         switch (plan.ti.kind) {
-            case ptx::KIND_F16: e = launch_gemm_pair_f16(launch_out, ta, tb, tc, tws, extra_arg, p, clusters, stream); break;
-            case ptx::KIND_I8: e = launch_gemm_pair_i8(launch_out, ta, tb, tc, tws, extra_arg, p, clusters, stream); break;
-            default: e = launch_gemm_pair_f8(launch_out, ta, tb, tc, tws, extra_arg, p, clusters, stream); break;
+            case ptx::KIND_F16: e = launch_gemm_pair_f16(cfg.bn, launch_out, ta, tb, tc, tws, extra_arg, p, clusters, stream); break;
+            case ptx::KIND_I8: e = launch_gemm_pair_i8(cfg.bn, launch_out, ta, tb, tc, tws, extra_arg, p, clusters, stream); break;
+            default: e = launch_gemm_pair_f8(cfg.bn, launch_out, ta, tb, tc, tws, extra_arg, p, clusters, stream); break;
         }
     } else if (cfg.kcluster > 0) {
         switch (plan.ti.kind) {

@@ -88,12 +88,12 @@ cudaError_t launch_kind(int bn, int out, int am, const CUtensorMap& ta, const CU
 // keep resident at once (queried once per device). `extra` non-null selects the variant whose epilogue also
 // stores every tile to p.n_extra_dst further destinations; `tws` is the tensor map of the last-wave scratch slots
 // (read only when p.tail_begin > 0).
-template <int KIND, int OUT, bool GATHER>
+template <int KIND, int OUT, bool GATHER, int BN = kPairTileN>
 cudaError_t launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tws,
                             const typename ExtraDstParam<GATHER>::type& extra, const GemmParams& p, int clusters,
                             cudaStream_t stream) {
-    auto kernel = gemm_tcgen05_pair_kernel<KIND, OUT, GATHER>;
-    constexpr int smem = PairSmem::kDynamicBytes;
+    auto kernel = gemm_tcgen05_pair_kernel<KIND, OUT, GATHER, BN>;
+    constexpr int smem = PairSmemT<BN>::kDynamicBytes;
     static bool configured[64] = {};
     static int max_clusters[64] = {};
     int dev = 0;
@@ -127,11 +127,22 @@ cudaError_t launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const 
     return launch_pdl(kernel, dim3(2 * clusters), dim3(kGemmThreads), smem, stream, ta, tb, tc, tws, extra, p);
 }
 
+// `bn` = 256, or 128 for the 256 x 128 tiles (one destination only).
 template <int KIND>
-cudaError_t launch_pair_kind(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+cudaError_t launch_pair_kind(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
                              const CUtensorMap& tws, const ExtraDst* extra, const GemmParams& p, int clusters,
                              cudaStream_t stream) {
     const NoExtraDst none = {0};
+    if (bn == 128) {
+        if (extra != nullptr) return cudaErrorInvalidValue;
+        switch (out) {
+            case OUT_F32: return launch_pair_one<KIND, OUT_F32, false, 128>(ta, tb, tc, tws, none, p, clusters, stream);
+            case OUT_BF16: return launch_pair_one<KIND, OUT_BF16, false, 128>(ta, tb, tc, tws, none, p, clusters, stream);
+            case OUT_F16: return launch_pair_one<KIND, OUT_F16, false, 128>(ta, tb, tc, tws, none, p, clusters, stream);
+            case OUT_RAW32: return launch_pair_one<KIND, OUT_RAW32, false, 128>(ta, tb, tc, tws, none, p, clusters, stream);
+            default: return cudaErrorInvalidValue;
+        }
+    }
 #define QGEMM_PAIR_CASE(OUT_)                                                                            \
     case OUT_:                                                                                           \
         return extra ? launch_pair_one<KIND, OUT_, true>(ta, tb, tc, tws, *extra, p, clusters, stream)        \
@@ -204,13 +215,13 @@ cudaError_t launch_gemm_wide_i8(int out, const CUtensorMap& ta, const CUtensorMa
 cudaError_t launch_gemm_wide_f8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                                 int clusters, cudaStream_t stream);
 
-cudaError_t launch_gemm_pair_f16(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tws,
+cudaError_t launch_gemm_pair_f16(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tws,
                                  const ExtraDst* extra, const GemmParams& p,
                                  int clusters, cudaStream_t stream);
-cudaError_t launch_gemm_pair_i8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tws,
+cudaError_t launch_gemm_pair_i8(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tws,
                                  const ExtraDst* extra, const GemmParams& p,
                                 int clusters, cudaStream_t stream);
-cudaError_t launch_gemm_pair_f8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tws,
+cudaError_t launch_gemm_pair_f8(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tws,
                                  const ExtraDst* extra, const GemmParams& p,
                                 int clusters, cudaStream_t stream);
 

@@ -19,20 +19,25 @@
 
 namespace qgemm {
 
-constexpr int kPairStages = 6;
 constexpr int kPairTileM = 256;
 constexpr int kPairTileN = 256;
 
-struct PairSmem {
+// BN = tile width: 256, or 128 (256 x 128 tiles: a CTA then loads 128 rows of A and 64 rows of B, 24 KB per K block for
+// its 128 x 128 share of the output where a lone CTA on a 128 x 128 tile loads 32 KB; eight stages fit).
+template <int BN>
+struct PairSmemT {
+    static constexpr int kStages = BN == 256 ? 6 : 8;
     static constexpr int kAStage = 128 * 128;
-    static constexpr int kBStage = 128 * 128;
-    static constexpr int kTiles = kPairStages * (kAStage + kBStage);
+    static constexpr int kBStage = (BN / 2) * 128;
+    static constexpr int kTiles = kStages * (kAStage + kBStage);
     static constexpr int kOutOffset = kTiles;  // epilogue staging (see epilogue_tma)
     static constexpr int kBarOffset = kTiles + kEpilogueStagingBytes;
-    static constexpr int kMiscOffset = kBarOffset + (2 * kPairStages + 4) * 8;
+    static constexpr int kMiscOffset = kBarOffset + (2 * kStages + 4) * 8;
     static constexpr int kTotal = kMiscOffset + 16;
     static constexpr int kDynamicBytes = kTotal + 1024;
 };
+using PairSmem = PairSmemT<kPairTileN>;
+constexpr int kPairStages = PairSmem::kStages;
 
 template <bool GATHER>
 struct ExtraDstParam {
@@ -43,20 +48,21 @@ struct ExtraDstParam<true> {
     using type = ExtraDst;
 };
 
-// p.m_tiles / p.n_tiles count 256 x 256 pair tiles; the grid is 2 * (number of clusters).
+// p.m_tiles / p.n_tiles count 256 x BN pair tiles; the grid is 2 * (number of clusters). BN = 128 takes a K-major B
+// only and has no last-wave split.
 // GATHER: the epilogue also stores every tile to the p.n_extra_dst destinations of `extra` (see ExtraDst).
 
-template <int KIND, int OUT, bool GATHER = false>
+template <int KIND, int OUT, bool GATHER = false, int BN = kPairTileN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_ws,
                          const __grid_constant__ typename ExtraDstParam<GATHER>::type extra, const GemmParams p) {
-    using L = PairSmem;
-    constexpr int STAGES = kPairStages;
+    using L = PairSmemT<BN>;
+    static_assert(BN == 256 || BN == 128, "pair tile width");
+    constexpr int STAGES = L::kStages;
     constexpr int ELT = (KIND == ptx::KIND_F16) ? 2 : 1;
     constexpr int BK = 128 / ELT;
-    constexpr int BN = kPairTileN;
-    constexpr uint32_t TMEM_COLS = 512;
+    constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulators
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -125,7 +131,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 const TileCoord t = item.t;
                 const int kb0 = item.kb0, kb1 = item.kb1;
                 const int row_a = (t.m_blk * 2 + static_cast<int>(rank)) * 128;
-                const int row_b = t.n_blk * BN + static_cast<int>(rank) * 128;
+                const int row_b = t.n_blk * BN + static_cast<int>(rank) * (BN / 2);
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, p.status, ROLE_PRODUCER, kb, peer_abort)) {
                         ok = false;
@@ -143,9 +149,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     const uint32_t leader_full = ptx::mapa_shared(bar_full + stage * 8, 0);
                     ptx::tma_load_2d_pair(smem_a + stage * L::kAStage, &tmap_a, leader_full, kb * BK, row_a);
                     if (p.b_mn_major) {
-                        constexpr int CHUNK = 128 / ELT;  // this CTA's 128 columns of B: 128-byte chunks of N
+                        constexpr int CHUNK = 128 / ELT;  // this CTA's BN / 2 columns of B: 128-byte chunks of N
 #pragma unroll
-                        for (int j = 0; j < 128 / CHUNK; ++j)
+                        for (int j = 0; j < (BN / 2) / CHUNK; ++j)
                             ptx::tma_load_2d_pair(smem_b + stage * L::kBStage + j * (BK * 128), &tmap_b, leader_full,
                                                   row_b + j * CHUNK, kb * BK);
                     } else {
