@@ -113,10 +113,12 @@ struct MapKeyHash {
 std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
 
 // K-major operand [rows, cols=K] with leading dimension ld (elements); box = 128 bytes of K x box_rows,
-// 128-byte swizzle, zero fill outside the tensor.
+// 128-byte swizzle, zero fill outside the tensor. kgroup > 1 (cols a whole number of 128-byte blocks): the
+// three-dimensional view [128 bytes][rows][K blocks] with a box of kgroup K blocks, which lands in shared memory as
+// kgroup consecutive [box_rows][128 bytes] tiles (see GemmParams::kgroup).
 int make_operand_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, int in_dtype, uint32_t box_rows,
-                     CUtensorMap* out) {
-    const MapKey key{ptr, rows, cols, ld, box_rows, static_cast<uint32_t>(in_dtype)};
+                     CUtensorMap* out, uint32_t kgroup = 1) {
+    const MapKey key{ptr, rows, cols, ld, box_rows, static_cast<uint32_t>(in_dtype) + 1000u * kgroup};
     auto it = g_maps.find(key);
     if (it != g_maps.end()) {
         *out = it->second;
@@ -129,14 +131,23 @@ int make_operand_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
         case QGEMM_DTYPE_FP16: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; es = 2; break;
         default: dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; es = 1; break;
     }
-    const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {ld * es};
-    const cuuint32_t box[2] = {128u / es, box_rows};
-    const cuuint32_t estr[2] = {1, 1};
     CUtensorMap m;
-    const CUresult r = g_encode(&m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r;
+    if (kgroup > 1) {
+        const cuuint64_t dims[3] = {128u / es, rows, cols * es / 128u};
+        const cuuint64_t strides[2] = {ld * es, 128u};
+        const cuuint32_t box[3] = {128u / es, box_rows, kgroup};
+        const cuuint32_t estr[3] = {1, 1, 1};
+        r = g_encode(&m, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        const cuuint64_t dims[2] = {cols, rows};
+        const cuuint64_t strides[1] = {ld * es};
+        const cuuint32_t box[2] = {128u / es, box_rows};
+        const cuuint32_t estr[2] = {1, 1};
+        r = g_encode(&m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
     if (r != CUDA_SUCCESS) return QGEMM_ERR_CUDA;
     if (g_maps.size() > 4096) g_maps.clear();
     g_maps.emplace(key, m);
@@ -216,6 +227,7 @@ EnvSettings read_env() {
     e.prefetch_force = (pf != nullptr && pf[0] == '1') ? 1 : 0;  // experiments: hints wherever the kernel can issue them
     const char* kc = std::getenv("QGEMM_KCLUSTER");
     e.kcluster_off = (kc != nullptr && kc[0] == '0') ? 1 : 0;
+    e.kgroup = std::max(0, env_int("QGEMM_KGROUP"));  // 0 = the library's choice, 1 = off, 2 / 4 / 8 = K blocks per load
     e.host_bands = std::max(0, env_int("QGEMM_HOST_BANDS"));
     e.host_bands_n = std::max(0, env_int("QGEMM_HOST_BANDS_N"));
     return e;
@@ -583,15 +595,28 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
                           g_env.direct_store != 0))
         plan.cfg.wide = false;
     const Config& cfg = plan.cfg;
+    // K-grouped loads (GemmParams::kgroup): the lone-CTA kernels on K-major operands whose K is a whole number of
+    // 128-byte blocks; by default two blocks per TMA instruction with the 64-wide tile. Measured on B200 (graph replay
+    // over cold operands, us; 1 / 2 / 4 / 8 blocks per instruction): FP8 16 x 7168 x 2048 6.70 / 6.19 / 6.57 / 6.78, BF16
+    // 16 x 7168 x 2048 10.13 / 8.73 / 8.94 / 9.67, FP8 1024 x 1024 x 4096 10.25 / 8.87 / 10.43 / 13.09, BF16 1024^3 6.78 /
+    // 6.14 / 6.75 / 7.74: two halve the instruction count, more make the barriers too coarse for the pipeline. With the
+    // 128-wide tile (16 KB boxes, six stages) it does not pay: FP8 256 x 7168 x 2048 8.08 / 8.41.
+    uint32_t kgroup = 1;
+    if (!cfg.pair && !b_direct && cfg.bal_tiles == 0 && (K * es) % 128 == 0) {
+        const int stages = std::min(16, (192 * 1024) / ((cfg.am + cfg.bn) * 128));
+        kgroup = g_env.kgroup > 0 ? static_cast<uint32_t>(g_env.kgroup) : (cfg.bn == 64 ? 2u : 1u);
+        if (kgroup != 2 && kgroup != 4 && kgroup != 8) kgroup = 1;
+        while (kgroup > 1 && stages % static_cast<int>(kgroup) != 0) kgroup /= 2;
+    }
     CUtensorMap ta, tb;
-    rc = make_operand_map(A, M, K, lda, in_dtype, cfg.wide ? 256u : static_cast<uint32_t>(cfg.am), &ta);
+    rc = make_operand_map(A, M, K, lda, in_dtype, cfg.wide ? 256u : static_cast<uint32_t>(cfg.am), &ta, kgroup);
     if (rc != QGEMM_OK) return rc;
     if (b_direct)  // [K rows, N columns]; one box = 128 bytes of N x one 128-byte K block of rows
         rc = make_operand_map(B, K, N, ldb, in_dtype, 128u / static_cast<uint32_t>(es), &tb);
     else
         rc = make_operand_map(b_kmajor, N, K, ldb_k, in_dtype,
                               cfg.pair ? static_cast<uint32_t>(cfg.bn / 2) : (cfg.bal_tiles > 0 ? static_cast<uint32_t>(cfg.bal_units * 16)
-                                                                   : static_cast<uint32_t>(cfg.bn)), &tb);
+                                                                   : static_cast<uint32_t>(cfg.bn)), &tb, kgroup);
     if (rc != QGEMM_OK) return rc;
 
     GemmParams p;
@@ -612,6 +637,7 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
                               static_cast<uint32_t>(cfg.bn), b_direct ? 1u : 0u);
     p.b_mn_major = b_direct ? 1 : 0;
     p.test_skip_kb = take_test_skip_kb();
+    p.kgroup = static_cast<int>(kgroup);
     p.status = st->status;
 
     int launch_out = plan.out_kind;
@@ -673,7 +699,8 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
     // 128 x 8192 x 2048: 6.89 us without, 7.37 with): 128-wide tiles only.
     {
         const int stages = std::min(16, (192 * 1024) / ((cfg.am + cfg.bn) * 128));
-        const bool can = !cfg.pair && !b_direct && cfg.bal_tiles == 0 && cfg.kcluster == 0 && work <= st->sm_count;
+        const bool can = !cfg.pair && !b_direct && cfg.bal_tiles == 0 && cfg.kcluster == 0 && kgroup == 1 &&
+                         work <= st->sm_count;
         if (can && (g_env.prefetch_force != 0 || (cfg.splits == 1 && cfg.bn == 128 && cfg.kb_per_split > stages &&
                                                   cfg.kb_per_split <= 16 && g_env.prefetch_off == 0)))
             p.prefetch_b = 1;

@@ -69,6 +69,12 @@ struct GemmParams {
     // Single-wave problems whose K loop is a little longer than the ring (one tile per CTA): before the dependency wait,
     // while the predecessor in the stream is still running, the CTA asks for its B tile to be brought into L2. 0 = off.
     int prefetch_b;
+    // K-grouped loads (lone-CTA kernel, K-major A and B, K a whole number of 128-byte blocks): kgroup > 1 makes tmap_a
+    // and tmap_b three-dimensional views [128 bytes][rows][K blocks] of the operands, and one TMA instruction brings
+    // kgroup consecutive K blocks of a tile into kgroup consecutive ring slots, completing on the first slot's barrier.
+    // The TMA unit retires small boxes at a fixed rate per instruction (about 120 cycles each on B200, whatever their
+    // size up to several KB), which bounds a skinny problem's 2 KB + 8 KB stages; fewer, larger boxes lift that.
+    int kgroup;
     int test_skip_kb;  // failure-detection test hook: the producer leaves out the loads of this K block (-1 = none),
                        // so the consumer's bounded wait runs out and the kernel returns through its error path
 };
@@ -462,15 +468,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
                 int col0, width;
                 tile_columns(p, t.n_blk, BN, col0, width);
-                for (int kb = kb0; kb < kb1; ++kb) {
+                const int G = p.kgroup > 1 ? p.kgroup : 1;
+                for (int kb = kb0; kb < kb1; kb += G) {
                     if (!wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, p.status, ROLE_PRODUCER, kb)) {
                         ok = false;
                         break;
                     }
-                    load_stage(t, col0, width, kb, stage);
+                    if (G == 1) {
+                        load_stage(t, col0, width, kb, stage);
+                    } else if (!(p.test_skip_kb >= kb && p.test_skip_kb < kb + G)) {  // test hook: a group never filled
+                        // G K blocks per instruction into slots stage .. stage + G - 1 (blocks past the end of K are
+                        // zero-filled by the copy and never multiplied)
+                        const uint32_t full = bar_full + stage * 8;
+                        ptx::mbar_arrive_expect_tx(full, G * (L::kAStage + L::kBStage));
+                        ptx::tma_load_3d(smem_a + stage * L::kAStage, &tmap_a, full, 0, t.m_blk * kBM, kb);
+                        ptx::tma_load_3d(smem_b + stage * L::kBStage, &tmap_b, full, 0, col0, kb);
+                    }
                     if (kb == kb0) QGEMM_STAMP(2);
-                    if (kb == kb1 - 1) QGEMM_STAMP(3);
-                    if (++stage == STAGES) {
+                    if (kb + G >= kb1) QGEMM_STAMP(3);
+                    stage += G;
+                    if (stage >= STAGES) {
                         stage = 0;
                         phase ^= 1u;
                     }
@@ -498,28 +515,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     tile_columns(p, t.n_blk, BN, col0, width);
                     idesc = (idesc & ~(0x3fu << 17)) | (static_cast<uint32_t>(width >> 3) << 17);
                 }
-                for (int kb = kb0; kb < kb1; ++kb) {
+                const int G = p.kgroup > 1 ? p.kgroup : 1;
+                for (int kb = kb0; kb < kb1; kb += G) {
                     if (!wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status, ROLE_MMA, kb)) {
                         ok = false;
                         break;
                     }
                     ptx::tc_fence_after();
                     if (kb == kb0) QGEMM_STAMP(4);
-                    if (kb == kb1 - 1) QGEMM_STAMP(5);
-                    const uint64_t a_desc = ptx::make_kmajor_sw128_desc(smem_a + stage * L::kAStage);
-                    const uint64_t b_desc =
-                        p.b_mn_major ? ptx::make_mnmajor_sw128_desc(smem_b + stage * L::kBStage, BK * 128)
-                                     : ptx::make_kmajor_sw128_desc(smem_b + stage * L::kBStage);
-                    // K step of one MMA in 16-byte units: 32 bytes inside a K-major row, or (32 / ELT) rows of
-                    // 128 bytes for an MN-major tile
-                    const uint32_t b_step = p.b_mn_major ? static_cast<uint32_t>((32 / ELT) * 128 / 16) : 2u;
+                    if (kb + G >= kb1) QGEMM_STAMP(5);
+                    const int blocks = min(G, kb1 - kb);  // the K blocks of this barrier: slots stage .. stage + blocks - 1
+                    for (int j = 0; j < blocks; ++j) {
+                        const uint64_t a_desc = ptx::make_kmajor_sw128_desc(smem_a + (stage + j) * L::kAStage);
+                        const uint64_t b_desc =
+                            p.b_mn_major ? ptx::make_mnmajor_sw128_desc(smem_b + (stage + j) * L::kBStage, BK * 128)
+                                         : ptx::make_kmajor_sw128_desc(smem_b + (stage + j) * L::kBStage);
+                        // K step of one MMA in 16-byte units: 32 bytes inside a K-major row, or (32 / ELT) rows of
+                        // 128 bytes for an MN-major tile
+                        const uint32_t b_step = p.b_mn_major ? static_cast<uint32_t>((32 / ELT) * 128 / 16) : 2u;
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per 128-byte block
-                        ptx::umma_ss<KIND>(d_tmem, a_desc + 2u * k, b_desc + b_step * k, idesc,
-                                           (kb > kb0 || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per 128-byte block
+                            ptx::umma_ss<KIND>(d_tmem, a_desc + 2u * k, b_desc + b_step * k, idesc,
+                                               (kb + j > kb0 || k > 0) ? 1u : 0u);
+                        }
                     }
                     ptx::tc_commit(bar_empty + stage * 8);
-                    if (++stage == STAGES) {
+                    stage += G;
+                    if (stage >= STAGES) {
                         stage = 0;
                         phase ^= 1u;
                     }

@@ -98,18 +98,25 @@ gemm_tcgen05_kcluster_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
         // ------------------------------------------------------------ TMA producer
         if (ptx::elect_one()) {
             uint32_t stage = 0, phase = 0;
-            for (int kb = kb0; kb < kb1; ++kb) {
+            const int G = p.kgroup > 1 ? p.kgroup : 1;  // K blocks per TMA instruction (GemmParams::kgroup)
+            for (int kb = kb0; kb < kb1; kb += G) {
                 if (!wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, p.status, ROLE_PRODUCER, kb)) {
                     raise_peers();
                     break;
                 }
                 const uint32_t full = bar_full + stage * 8;
-                if (kb != p.test_skip_kb) {  // test hook: a slot that is never filled
-                    ptx::mbar_arrive_expect_tx(full, L::kAStage + L::kBStage);
-                    ptx::tma_load_2d(smem_a + stage * L::kAStage, &tmap_a, full, kb * BK, t.m_blk * kBM);
-                    ptx::tma_load_2d(smem_b + stage * L::kBStage, &tmap_b, full, kb * BK, t.n_blk * BN);
+                if (!(p.test_skip_kb >= kb && p.test_skip_kb < kb + G)) {  // test hook: a slot that is never filled
+                    ptx::mbar_arrive_expect_tx(full, G * (L::kAStage + L::kBStage));
+                    if (G == 1) {
+                        ptx::tma_load_2d(smem_a + stage * L::kAStage, &tmap_a, full, kb * BK, t.m_blk * kBM);
+                        ptx::tma_load_2d(smem_b + stage * L::kBStage, &tmap_b, full, kb * BK, t.n_blk * BN);
+                    } else {
+                        ptx::tma_load_3d(smem_a + stage * L::kAStage, &tmap_a, full, 0, t.m_blk * kBM, kb);
+                        ptx::tma_load_3d(smem_b + stage * L::kBStage, &tmap_b, full, 0, t.n_blk * BN, kb);
+                    }
                 }
-                if (++stage == STAGES) {
+                stage += G;
+                if (stage >= STAGES) {
                     stage = 0;
                     phase ^= 1u;
                 }
@@ -120,20 +127,26 @@ gemm_tcgen05_kcluster_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
         if (ptx::elect_one()) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (int kb = kb0; kb < kb1; ++kb) {
+            const int G = p.kgroup > 1 ? p.kgroup : 1;
+            for (int kb = kb0; kb < kb1; kb += G) {
                 if (!wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status, ROLE_MMA, kb)) {
                     raise_peers();
                     ok = false;
                     break;
                 }
                 ptx::tc_fence_after();
-                const uint64_t a_desc = ptx::make_kmajor_sw128_desc(smem_a + stage * L::kAStage);
-                const uint64_t b_desc = ptx::make_kmajor_sw128_desc(smem_b + stage * L::kBStage);
+                const int blocks = min(G, kb1 - kb);
+                for (int j = 0; j < blocks; ++j) {
+                    const uint64_t a_desc = ptx::make_kmajor_sw128_desc(smem_a + (stage + j) * L::kAStage);
+                    const uint64_t b_desc = ptx::make_kmajor_sw128_desc(smem_b + (stage + j) * L::kBStage);
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    ptx::umma_ss<KIND>(tmem_base, a_desc + 2u * k, b_desc + 2u * k, p.idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < 4; ++k)
+                        ptx::umma_ss<KIND>(tmem_base, a_desc + 2u * k, b_desc + 2u * k, p.idesc,
+                                           (kb + j > kb0 || k > 0) ? 1u : 0u);
+                }
                 ptx::tc_commit(bar_empty + stage * 8);
-                if (++stage == STAGES) {
+                stage += G;
+                if (stage >= STAGES) {
                     stage = 0;
                     phase ^= 1u;
                 }

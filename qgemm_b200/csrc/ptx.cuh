@@ -82,6 +82,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
         : "memory");
 }
 
+// Three-dimensional form: x is the innermost coordinate (same 16-byte rule), y and z have no alignment rule.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap* tmap, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
 // Hint: bring one box of a tensor into L2 (no shared memory, no completion to wait for). L2 is the GPU's point of
 // coherence, so a box prefetched before its producer has written it is simply updated there: the hint can be issued
 // ahead of griddepcontrol.wait.
