@@ -413,16 +413,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             ptx::tma_load_2d(smem_b + stage * L::kBStage, &tmap_b, full, kb * BK, col0);
         }
     };
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            ptx::mbar_init(bar_full + s * 8, 1);
-            ptx::mbar_init(bar_empty + s * 8, 1);
+    if (warp == 0) {  // the barriers are set up by the lanes of one warp side by side
+        static_assert(STAGES <= 32, "one lane per ring slot");
+        if (lane < STAGES) {
+            ptx::mbar_init(bar_full + lane * 8, 1);
+            ptx::mbar_init(bar_empty + lane * 8, 1);
         }
-        for (int a = 0; a < 2; ++a) {
-            ptx::mbar_init(bar_tfull + a * 8, 1);
-            ptx::mbar_init(bar_tempty + a * 8, 4);
+        if (lane < 2) {
+            ptx::mbar_init(bar_tfull + lane * 8, 1);
+            ptx::mbar_init(bar_tempty + lane * 8, 4);
         }
-        *abort_flag = 0;
+        if (lane == 0) *abort_flag = 0;
         ptx::fence_barrier_init();
     }
     if (warp == 0 && lane == 0) {
@@ -444,6 +445,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // is one tile per CTA, and its whole body is a few microseconds).
     const TileCoord first_tile =
         static_cast<int>(blockIdx.x) < total_work ? decode_tile(blockIdx.x, p) : TileCoord{0, 0, 0};
+    // Likewise everything else the producer needs for its first loads: read from the parameters (constant memory, a
+    // miss on first touch) and computed now, so that only the loads themselves follow the dependency wait.
+    const int group = p.kgroup > 1 ? p.kgroup : 1;
+    const int first_kb0 = first_tile.split * p.kb_per_split;
+    const int first_kb1 = min(p.kb_total, first_kb0 + p.kb_per_split);
+    int first_col0, first_width;
+    tile_columns(p, first_tile.n_blk, BN, first_col0, first_width);
+    const int skip_kb = p.test_skip_kb;
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
         ptx::tmem_relinquish();
@@ -461,22 +470,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         // ------------------------------------------------------------ TMA producer
         if (ptx::elect_one()) {
             uint32_t stage = 0, phase = 0;
+            uint32_t filled = 0;  // ring slots handed out so far: the first STAGES are free without asking
             bool ok = true;
             for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
-                const TileCoord t = (w == static_cast<int>(blockIdx.x)) ? first_tile : decode_tile(w, p);
-                const int kb0 = t.split * p.kb_per_split;
-                const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
-                int col0, width;
-                tile_columns(p, t.n_blk, BN, col0, width);
-                const int G = p.kgroup > 1 ? p.kgroup : 1;
+                const bool first = w == static_cast<int>(blockIdx.x);
+                const TileCoord t = first ? first_tile : decode_tile(w, p);
+                int kb0 = first_kb0, kb1 = first_kb1, col0 = first_col0, width = first_width;
+                if (!first) {
+                    kb0 = t.split * p.kb_per_split;
+                    kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                    tile_columns(p, t.n_blk, BN, col0, width);
+                }
+                const int G = group;
                 for (int kb = kb0; kb < kb1; kb += G) {
-                    if (!wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, p.status, ROLE_PRODUCER, kb)) {
+                    if (filled >= static_cast<uint32_t>(STAGES) &&
+                        !wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, p.status, ROLE_PRODUCER, kb)) {
                         ok = false;
                         break;
                     }
+                    if (filled < static_cast<uint32_t>(STAGES)) filled += G;
                     if (G == 1) {
                         load_stage(t, col0, width, kb, stage);
-                    } else if (!(p.test_skip_kb >= kb && p.test_skip_kb < kb + G)) {  // test hook: a group never filled
+                    } else if (!(skip_kb >= kb && skip_kb < kb + G)) {  // test hook: a group never filled
                         // G K blocks per instruction into slots stage .. stage + G - 1 (blocks past the end of K are
                         // zero-filled by the copy and never multiplied)
                         const uint32_t full = bar_full + stage * 8;
