@@ -227,6 +227,8 @@ EnvSettings read_env() {
     e.prefetch_force = (pf != nullptr && pf[0] == '1') ? 1 : 0;  // experiments: hints wherever the kernel can issue them
     const char* kc = std::getenv("QGEMM_KCLUSTER");
     e.kcluster_off = (kc != nullptr && kc[0] == '0') ? 1 : 0;
+    const char* eg = std::getenv("QGEMM_EARLY_GROUPS");  // experiments: loads issued ahead of the CTA-wide barrier
+    e.early_groups = eg != nullptr ? std::max(0, std::atoi(eg)) : -1;
     e.kgroup = std::max(0, env_int("QGEMM_KGROUP"));  // 0 = the library's choice, 1 = off, 2 / 4 / 8 = K blocks per load
     e.host_bands = std::max(0, env_int("QGEMM_HOST_BANDS"));
     e.host_bands_n = std::max(0, env_int("QGEMM_HOST_BANDS_N"));
@@ -638,6 +640,7 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
     p.b_mn_major = b_direct ? 1 : 0;
     p.test_skip_kb = take_test_skip_kb();
     p.kgroup = static_cast<int>(kgroup);
+    p.early_groups = g_env.early_groups >= 0 ? g_env.early_groups : 2;
     p.status = st->status;
 
     int launch_out = plan.out_kind;

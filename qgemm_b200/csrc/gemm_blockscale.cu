@@ -276,7 +276,7 @@ fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                                               u[4 * j + 1], u[4 * j + 2], u[4 * j + 3]);
                         ptx::fence_proxy_async_smem();
                         __syncwarp();
-                        if (lane == 0) {
+                        if (ptx::elect_one()) {
                             ptx::tma_store_3d(&tmap_c, stage_base, n0, row0, 0);
                             ptx::tma_store_commit();
                         }

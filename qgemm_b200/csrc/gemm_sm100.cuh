@@ -75,6 +75,7 @@ struct GemmParams {
     // The TMA unit retires small boxes at a fixed rate per instruction (about 120 cycles each on B200, whatever their
     // size up to several KB), which bounds a skinny problem's 2 KB + 8 KB stages; fewer, larger boxes lift that.
     int kgroup;
+    int early_groups;  // groups of loads the producer issues ahead of the CTA-wide barrier (lone-CTA kernel), 0 = none
     int test_skip_kb;  // failure-detection test hook: the producer leaves out the loads of this K block (-1 = none),
                        // so the consumer's bounded wait runs out and the kernel returns through its error path
 };
@@ -294,7 +295,7 @@ __device__ __forceinline__ void epilogue_tma(const CUtensorMap* tmap_c, uint32_t
         ptx::tmem_ld_32x32b_x32(t_addr + c * CW, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
         if constexpr (CW == 64) ptx::tmem_ld_32x32b_x32(t_addr + c * CW + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
         // the buffer about to be overwritten was handed to a TMA store two chunks ago: wait until it was read
-        if (lane == 0) ptx::tma_store_wait_read<1>();
+        if (ptx::elect_one()) ptx::tma_store_wait_read<1>();
         __syncwarp();
         ptx::tmem_ld_wait();
         uint32_t u[32];  // 8 sixteen-byte units of this row
@@ -331,7 +332,7 @@ __device__ __forceinline__ void epilogue_tma(const CUtensorMap* tmap_c, uint32_t
                               u[4 * j + 2], u[4 * j + 3]);
         ptx::fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) {
+        if (ptx::elect_one()) {  // one lane, named so that the compiler keeps the TMA operands in uniform registers
             ptx::tma_store_3d(tmap_c, stage_base + buf * 4096u, n0, row0, split);
             // the same staged box goes to every further destination; one bulk group covers them all
             for (int d = 0; d < n_extra; ++d) ptx::tma_store_3d(extra + d, stage_base + buf * 4096u, n0, row0, split);
@@ -385,6 +386,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int lane = static_cast<int>(threadIdx.x) & 31;
     const int total_work = p.m_tiles * p.n_tiles * p.splits;
     if (threadIdx.x == 0) QGEMM_STAMP(0);
+    // The successor in the stream may start its own set-up now (it waits for this grid's completion before it touches
+    // global memory): every thread says so at once, so that no warp's later work delays it.
+    ptx::pdl_launch_dependents();
 
     // The loads of one K block of one tile into ring slot `stage`.
     auto load_stage = [&](const TileCoord& t, int col0, int width, int kb, uint32_t stage) {
@@ -453,6 +457,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     int first_col0, first_width;
     tile_columns(p, first_tile.n_blk, BN, first_col0, first_width);
     const int skip_kb = p.test_skip_kb;
+    // The loads of `group` K blocks starting at kb into ring slots stage .. stage + group - 1.
+    auto load_group = [&](const TileCoord& t, int col0, int width, int kb, uint32_t stage) {
+        if (group == 1) {
+            load_stage(t, col0, width, kb, stage);
+        } else if (!(skip_kb >= kb && skip_kb < kb + group)) {  // test hook: a group never filled
+            // one instruction per operand (blocks past the end of K are zero-filled by the copy and never multiplied)
+            const uint32_t full = bar_full + stage * 8;
+            ptx::mbar_arrive_expect_tx(full, group * (L::kAStage + L::kBStage));
+            ptx::tma_load_3d(smem_a + stage * L::kAStage, &tmap_a, full, 0, t.m_blk * kBM, kb);
+            ptx::tma_load_3d(smem_b + stage * L::kBStage, &tmap_b, full, 0, col0, kb);
+        }
+    };
+    // The producer (lane 0 of warp 0) does not wait for the rest of the CTA: its barriers are ready (its own warp set
+    // them up), the ring is empty, so as soon as the predecessor in the stream is done it sends the first tile's first
+    // loads on their way and only then joins the barrier below. Tensor-memory allocation and the barrier itself then
+    // overlap the first bytes' flight from HBM (about a microsecond for cold operands) instead of preceding it. Two
+    // groups only: issuing a whole ring-full takes longer than that flight (the TMA unit accepts only so many boxes at
+    // a time), and the MMA issuer, held at the barrier meanwhile, would start late. The loop state is carried over
+    // into the producer's main loop.
+    uint32_t prod_stage = 0, prod_phase = 0, prod_filled = 0;
+    int prod_kb = first_kb0;
+    if (warp == 0) {
+        __syncwarp();  // the other lanes' barrier set-up
+        // elect_one() names the same lane every time for a full warp, and lets the compiler keep the TMA operands in
+        // uniform registers (a plain lane test does not, and the one-block-per-load path issues a fifth slower)
+        if (static_cast<int>(blockIdx.x) < total_work && ptx::elect_one()) {
+            ptx::pdl_wait();
+            QGEMM_STAMP(1);
+            while (prod_kb < first_kb1 && prod_filled < static_cast<uint32_t>(min(STAGES, p.early_groups * group))) {
+                load_group(first_tile, first_col0, first_width, prod_kb, prod_stage);
+                if (prod_kb == first_kb0) QGEMM_STAMP(2);
+                if (prod_kb + group >= first_kb1) QGEMM_STAMP(3);
+                prod_kb += group;
+                prod_filled += group;
+                prod_stage += group;
+                if (prod_stage >= static_cast<uint32_t>(STAGES)) {
+                    prod_stage = 0;
+                    prod_phase ^= 1u;
+                }
+            }
+        }
+        __syncwarp();
+    }
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
         ptx::tmem_relinquish();
@@ -461,21 +508,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // Everything above touched no global memory; from here on the predecessor's results are needed.
-    ptx::pdl_launch_dependents();
+    // From here on every thread may touch global memory: the predecessor's results are needed (and must not be
+    // overwritten early).
     ptx::pdl_wait();
-    if (threadIdx.x == 0) QGEMM_STAMP(1);
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (ptx::elect_one()) {
-            uint32_t stage = 0, phase = 0;
-            uint32_t filled = 0;  // ring slots handed out so far: the first STAGES are free without asking
+            uint32_t stage = prod_stage, phase = prod_phase;
+            uint32_t filled = prod_filled;  // ring slots handed out so far: the first STAGES are free without asking
             bool ok = true;
             for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
                 const bool first = w == static_cast<int>(blockIdx.x);
                 const TileCoord t = first ? first_tile : decode_tile(w, p);
-                int kb0 = first_kb0, kb1 = first_kb1, col0 = first_col0, width = first_width;
+                int kb0 = prod_kb, kb1 = first_kb1, col0 = first_col0, width = first_width;  // the first tile: resumed
                 if (!first) {
                     kb0 = t.split * p.kb_per_split;
                     kb1 = min(p.kb_total, kb0 + p.kb_per_split);
@@ -489,17 +535,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         break;
                     }
                     if (filled < static_cast<uint32_t>(STAGES)) filled += G;
-                    if (G == 1) {
-                        load_stage(t, col0, width, kb, stage);
-                    } else if (!(skip_kb >= kb && skip_kb < kb + G)) {  // test hook: a group never filled
-                        // G K blocks per instruction into slots stage .. stage + G - 1 (blocks past the end of K are
-                        // zero-filled by the copy and never multiplied)
-                        const uint32_t full = bar_full + stage * 8;
-                        ptx::mbar_arrive_expect_tx(full, G * (L::kAStage + L::kBStage));
-                        ptx::tma_load_3d(smem_a + stage * L::kAStage, &tmap_a, full, 0, t.m_blk * kBM, kb);
-                        ptx::tma_load_3d(smem_b + stage * L::kBStage, &tmap_b, full, 0, col0, kb);
-                    }
-                    if (kb == kb0) QGEMM_STAMP(2);
+                    load_group(t, col0, width, kb, stage);
                     if (kb + G >= kb1) QGEMM_STAMP(3);
                     stage += G;
                     if (stage >= STAGES) {

@@ -53,7 +53,7 @@ def test_cta_pair_leaves_together_when_a_wait_runs_out(qlib, oracle, dev):
     a = torch.from_numpy(a_bits.view(np.int16)).to(dev).view(torch.bfloat16)
     b = torch.from_numpy(b_bits.view(np.int16)).to(dev).view(torch.bfloat16)
     c = torch.zeros((M, N), dtype=torch.float32, device=dev)
-    pair = q.Tuning(0, 1, 0, 0, 1, 0)
+    pair = q.Tuning(256, 1, 0, 0, 1, 0)  # one 256 x 256 tile = one cluster (256 x 128 tiles would make two)
     assert q.plan_query(q.BF16, q.FP32, q.B_K_MAJOR, M, N, K, pair)["ctas_per_tile"] == 2
     q.gemm(a, b, c, b_kmajor=True, tuning=pair)  # warm: module load and attribute set-up are not part of the timing
     assert q.device_status()[0] == q.OK
