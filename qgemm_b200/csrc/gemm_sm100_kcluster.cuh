@@ -58,31 +58,70 @@ gemm_tcgen05_kcluster_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
     const uint32_t rank = ptx::cluster_ctarank();
     const int tile = static_cast<int>(blockIdx.x) / S;  // one tile per cluster
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            ptx::mbar_init(bar_full + s * 8, 1);
-            ptx::mbar_init(bar_empty + s * 8, 1);
+    ptx::pdl_launch_dependents();  // the successor may start its set-up; it waits for this grid before touching memory
+    if (warp == 0) {  // the barriers are set up by the lanes of one warp side by side
+        static_assert(STAGES <= 32, "one lane per ring slot");
+        if (lane < STAGES) {
+            ptx::mbar_init(bar_full + lane * 8, 1);
+            ptx::mbar_init(bar_empty + lane * 8, 1);
         }
-        ptx::mbar_init(bar_tfull, 1);
-        *abort_flag = 0;
+        if (lane == 0) {
+            ptx::mbar_init(bar_tfull, 1);
+            *abort_flag = 0;
+            ptx::prefetch_tensormap(&tmap_a);
+            ptx::prefetch_tensormap(&tmap_b);
+        }
         ptx::fence_barrier_init();
     }
-    if (warp == 0 && lane == 0) {
-        ptx::prefetch_tensormap(&tmap_a);
-        ptx::prefetch_tensormap(&tmap_b);
+    const TileCoord t = decode_tile(tile, p);  // p.splits == 1: work item == tile
+    const int kb0 = static_cast<int>(rank) * p.kb_per_split;
+    const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+    const int group = p.kgroup > 1 ? p.kgroup : 1;  // K blocks per TMA instruction (GemmParams::kgroup)
+    const int skip_kb = p.test_skip_kb;
+    // The loads of `group` K blocks starting at kb into ring slots stage .. stage + group - 1.
+    auto load_group = [&](int kb, uint32_t stage) {
+        const uint32_t full = bar_full + stage * 8;
+        if (!(skip_kb >= kb && skip_kb < kb + group)) {  // test hook: a slot that is never filled
+            ptx::mbar_arrive_expect_tx(full, group * (L::kAStage + L::kBStage));
+            if (group == 1) {
+                ptx::tma_load_2d(smem_a + stage * L::kAStage, &tmap_a, full, kb * BK, t.m_blk * kBM);
+                ptx::tma_load_2d(smem_b + stage * L::kBStage, &tmap_b, full, kb * BK, t.n_blk * BN);
+            } else {
+                ptx::tma_load_3d(smem_a + stage * L::kAStage, &tmap_a, full, 0, t.m_blk * kBM, kb);
+                ptx::tma_load_3d(smem_b + stage * L::kBStage, &tmap_b, full, 0, t.n_blk * BN, kb);
+            }
+        }
+    };
+    // As in gemm_tcgen05_kernel: the producer lane sends the first two groups of loads on their way as soon as the
+    // predecessor in the stream is done, before the CTA-wide barrier (tensor-memory allocation and the barrier then
+    // overlap the first bytes' flight); its loop state is carried into the main loop.
+    uint32_t prod_stage = 0, prod_phase = 0, prod_filled = 0;
+    int prod_kb = kb0;
+    if (warp == 0) {
+        __syncwarp();  // the other lanes' barrier set-up
+        if (ptx::elect_one()) {
+            ptx::pdl_wait();
+            while (prod_kb < kb1 && prod_filled < static_cast<uint32_t>(min(STAGES, p.early_groups * group))) {
+                load_group(prod_kb, prod_stage);
+                prod_kb += group;
+                prod_filled += group;
+                prod_stage += group;
+                if (prod_stage >= static_cast<uint32_t>(STAGES)) {
+                    prod_stage = 0;
+                    prod_phase ^= 1u;
+                }
+            }
+        }
+        __syncwarp();
     }
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
         ptx::tmem_relinquish();
     }
-    const TileCoord t = decode_tile(tile, p);  // p.splits == 1: work item == tile
-    const int kb0 = static_cast<int>(rank) * p.kb_per_split;
-    const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    ptx::pdl_launch_dependents();
     ptx::pdl_wait();
 
     // A wait that runs out raises the abort flag of every CTA of the cluster, so that all of them stop waiting and
@@ -97,25 +136,17 @@ gemm_tcgen05_kcluster_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (ptx::elect_one()) {
-            uint32_t stage = 0, phase = 0;
-            const int G = p.kgroup > 1 ? p.kgroup : 1;  // K blocks per TMA instruction (GemmParams::kgroup)
-            for (int kb = kb0; kb < kb1; kb += G) {
-                if (!wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, p.status, ROLE_PRODUCER, kb)) {
+            uint32_t stage = prod_stage, phase = prod_phase, filled = prod_filled;
+            for (int kb = prod_kb; kb < kb1; kb += group) {
+                // the first STAGES slots are free without asking
+                if (filled >= static_cast<uint32_t>(STAGES) &&
+                    !wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, p.status, ROLE_PRODUCER, kb)) {
                     raise_peers();
                     break;
                 }
-                const uint32_t full = bar_full + stage * 8;
-                if (!(p.test_skip_kb >= kb && p.test_skip_kb < kb + G)) {  // test hook: a slot that is never filled
-                    ptx::mbar_arrive_expect_tx(full, G * (L::kAStage + L::kBStage));
-                    if (G == 1) {
-                        ptx::tma_load_2d(smem_a + stage * L::kAStage, &tmap_a, full, kb * BK, t.m_blk * kBM);
-                        ptx::tma_load_2d(smem_b + stage * L::kBStage, &tmap_b, full, kb * BK, t.n_blk * BN);
-                    } else {
-                        ptx::tma_load_3d(smem_a + stage * L::kAStage, &tmap_a, full, 0, t.m_blk * kBM, kb);
-                        ptx::tma_load_3d(smem_b + stage * L::kBStage, &tmap_b, full, 0, t.n_blk * BN, kb);
-                    }
-                }
-                stage += G;
+                if (filled < static_cast<uint32_t>(STAGES)) filled += group;
+                load_group(kb, stage);
+                stage += group;
                 if (stage >= STAGES) {
                     stage = 0;
                     phase ^= 1u;
