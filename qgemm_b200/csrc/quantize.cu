@@ -108,21 +108,74 @@ amax_kernel(const TIn* __restrict__ in, long long ld, int rows, int cols, float*
     }
 }
 
+// round_to_nearest_even(fl(x / scale)) as an integer, clamped to +-qmax -- the division's result without the division
+// wherever that is provably the same. x * (1 / scale) is within 2^-23 relative, i.e. within 3e-5 for |q| <= 256, of
+// the true quotient, and so is the correctly rounded quotient (1.5e-5); unless the product lies within 1e-4 of k + 1/2
+// both round to the same integer. The rounding itself is the add-a-large-constant form (2^23 + 2^22: the sum's low
+// mantissa bits are the integer, rounded to nearest even by the addition), so the common path has neither a division
+// nor a float <-> int conversion, both of which issue at a fraction of the FP32 rate and bounded this pass below the
+// HBM rate (bf16 -> int8: 3.97 TB/s of 6.5). The product is clamped just inside +-(qmax + 1/2) first, which saturates
+// and keeps the constant trick in range; anything the clamp moved, ties, NaNs and scales whose reciprocal is not a
+// normal number (the reciprocal is then set to NaN) fail the distance test and take the exact path.
+struct QuotientRounder {
+    float scale, rcp;
+    __device__ __forceinline__ explicit QuotientRounder(float s) {
+        scale = s;
+        rcp = (s >= 1e-30f && s <= 1e30f) ? __fdiv_rn(1.0f, s) : __int_as_float(0x7fc00000);
+    }
+    // Returns a word whose LOW BYTE is the two's-complement result (the constant's own low byte is zero, so the sum's
+    // bit pattern can be used as it is: no subtraction, no conversion).
+    template <int QMAX>
+    __device__ __forceinline__ uint32_t round_low_byte(float x) const {
+        constexpr float kMagic = 12582912.0f;  // 2^23 + 2^22 = 0x4B400000
+        constexpr float kLim = static_cast<float>(QMAX) + 0.49f;
+        const float qf = x * rcp;
+        const float t = fminf(fmaxf(qf, -kLim), kLim) + kMagic;
+        const float n = t - kMagic;  // exact: the clamped product rounded to an integer in [-QMAX, QMAX]
+        if (fabsf(qf - n) < 0.4999f) return __float_as_uint(t);
+        return static_cast<uint32_t>(max(-QMAX, min(QMAX, __float2int_rn(__fdiv_rn(x, scale)))));
+    }
+    // Four int8 results packed into a word. Fused multiply-adds: t = RN(x * rcp + 2^23 + 2^22) carries the integer
+    // nearest to the product, d = RN(x * rcp - n) its distance from it (one rounding each). No clamp: the scale is
+    // amax / 127 of this very matrix (the library's own first pass), so |x * rcp| <= 127 (1 + 2^-22) and the integer
+    // is within +-127 by construction; a NaN among the four fails the comparison and sends the quad down the exact path.
+    __device__ __forceinline__ uint32_t round_quad_int8(const float (&x)[4]) const {
+        constexpr float kMagic = 12582912.0f;
+        float t[4];
+        bool ok = true;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            t[j] = __fmaf_rn(x[j], rcp, kMagic);
+            const float n = t[j] - kMagic;
+            ok = ok && (fabsf(__fmaf_rn(x[j], rcp, -n)) < 0.4999f);
+        }
+        if (ok) {  // the four low bytes gathered with three byte permutes
+            const uint32_t lo = __byte_perm(__float_as_uint(t[0]), __float_as_uint(t[1]), 0x0040);
+            const uint32_t hi = __byte_perm(__float_as_uint(t[2]), __float_as_uint(t[3]), 0x0040);
+            return __byte_perm(lo, hi, 0x5410);
+        }
+        uint32_t w = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            w |= (static_cast<uint32_t>(max(-127, min(127, __float2int_rn(__fdiv_rn(x[j], scale))))) & 0xffu) << (8 * j);
+        return w;
+    }
+};
+
 template <bool FP8>
-__device__ __forceinline__ uint8_t quantize_one(float x, float scale) {
-    const float q = __fdiv_rn(x, scale);
+__device__ __forceinline__ uint8_t quantize_one(float x, const QuotientRounder& qr) {
     if constexpr (FP8) {
-        return static_cast<uint8_t>(__nv_cvt_float_to_fp8(q, __NV_SATFINITE, __NV_E4M3));
+        return static_cast<uint8_t>(__nv_cvt_float_to_fp8(__fdiv_rn(x, qr.scale), __NV_SATFINITE, __NV_E4M3));
     } else {
         // round to nearest even straight to an integer (what rintf + cast does), then saturate to +-127
-        const int r = max(-127, min(127, __float2int_rn(q)));
-        return static_cast<uint8_t>(r & 0xff);
+        return static_cast<uint8_t>(qr.round_low_byte<127>(x) & 0xffu);
     }
 }
 
 // Four quantised values packed into one 32-bit word.
 template <bool FP8>
-__device__ __forceinline__ uint32_t quantize_quad(const float (&x)[4], float scale) {
+__device__ __forceinline__ uint32_t quantize_quad(const float (&x)[4], const QuotientRounder& qr) {
+    const float scale = qr.scale;
     if constexpr (FP8) {
         // two values per conversion instruction (same rounding and saturation as the scalar form)
         const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(x[0], scale), __fdiv_rn(x[1], scale)),
@@ -131,8 +184,7 @@ __device__ __forceinline__ uint32_t quantize_quad(const float (&x)[4], float sca
                                                      __NV_SATFINITE, __NV_E4M3);
         return lo | (hi << 16);
     } else {
-        return quantize_one<FP8>(x[0], scale) | (quantize_one<FP8>(x[1], scale) << 8) |
-               (quantize_one<FP8>(x[2], scale) << 16) | (static_cast<uint32_t>(quantize_one<FP8>(x[3], scale)) << 24);
+        return qr.round_quad_int8(x);
     }
 }
 
@@ -148,6 +200,7 @@ quantize_kernel(const TIn* __restrict__ in, long long ld_in, uint8_t* __restrict
     const float qmax = FP8 ? 448.0f : 127.0f;
     const float scale = amax > 0.0f ? __fdiv_rn(amax, qmax) : 1.0f;
     if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
+    const QuotientRounder qr(scale);
     const int quads_per_row = (cols + 3) / 4;
     const int chunks_per_row = (quads_per_row + kChunkQuads - 1) / kChunkQuads;
     const long long items = static_cast<long long>(chunks_per_row) * rows;
@@ -164,7 +217,7 @@ quantize_kernel(const TIn* __restrict__ in, long long ld_in, uint8_t* __restrict
             for (int u = 0; u < U; ++u) {
                 float x[4];
                 Quad<TIn>::to_float(v[u], x);
-                *reinterpret_cast<uint32_t*>(dst_row + (q0 + u * kQuantThreads) * 4) = quantize_quad<FP8>(x, scale);
+                *reinterpret_cast<uint32_t*>(dst_row + (q0 + u * kQuantThreads) * 4) = quantize_quad<FP8>(x, qr);
             }
             continue;
         }
@@ -174,10 +227,10 @@ quantize_kernel(const TIn* __restrict__ in, long long ld_in, uint8_t* __restrict
             if (vec_ok && c + 4 <= cols) {
                 float x[4];
                 Quad<TIn>::to_float(Quad<TIn>::load(src_row + c), x);
-                *reinterpret_cast<uint32_t*>(dst_row + c) = quantize_quad<FP8>(x, scale);
+                *reinterpret_cast<uint32_t*>(dst_row + c) = quantize_quad<FP8>(x, qr);
             } else {
                 for (int e = 0; e < 4 && c + e < cols; ++e)
-                    dst_row[c + e] = quantize_one<FP8>(load_as_float(src_row + c + e), scale);
+                    dst_row[c + e] = quantize_one<FP8>(load_as_float(src_row + c + e), qr);
             }
         }
     }
@@ -185,8 +238,8 @@ quantize_kernel(const TIn* __restrict__ in, long long ld_in, uint8_t* __restrict
 
 // INT4 output: eight consecutive elements of a row become four packed bytes (one 32-bit store). Same (row, chunk)
 // decomposition as quantize_kernel, a chunk being kQuantThreads x U groups of eight.
-__device__ __forceinline__ uint32_t quantize_nibble(float x, float scale) {
-    return static_cast<uint32_t>(max(-7, min(7, __float2int_rn(__fdiv_rn(x, scale))))) & 0xfu;
+__device__ __forceinline__ uint32_t quantize_nibble(float x, const QuotientRounder& qr) {
+    return qr.round_low_byte<7>(x) & 0xfu;
 }
 
 template <typename TIn>
@@ -200,6 +253,7 @@ quantize_int4_kernel(const TIn* __restrict__ in, long long ld_in, uint8_t* __res
     const float amax = __ldg(amax_in);
     const float scale = amax > 0.0f ? __fdiv_rn(amax, 7.0f) : 1.0f;
     if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
+    const QuotientRounder qr(scale);
     const int octs_per_row = (cols + 7) / 8;
     const int chunks_per_row = (octs_per_row + kChunkOcts - 1) / kChunkOcts;
     const long long items = static_cast<long long>(chunks_per_row) * rows;
@@ -223,8 +277,8 @@ quantize_int4_kernel(const TIn* __restrict__ in, long long ld_in, uint8_t* __res
                 uint32_t w = 0;
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    w |= quantize_nibble(x[e], scale) << (4 * e);
-                    w |= quantize_nibble(y[e], scale) << (16 + 4 * e);
+                    w |= quantize_nibble(x[e], qr) << (4 * e);
+                    w |= quantize_nibble(y[e], qr) << (16 + 4 * e);
                 }
                 *reinterpret_cast<uint32_t*>(dst_row + (o0 + u * kQuantThreads) * 4) = w;
             }
@@ -234,8 +288,8 @@ quantize_int4_kernel(const TIn* __restrict__ in, long long ld_in, uint8_t* __res
             const int c = (o0 + u * kQuantThreads) * 8;
             if (c >= cols) break;
             for (int e = 0; e < 8 && c + e < cols; e += 2) {  // cols is even: pairs are whole
-                const uint32_t q0 = quantize_nibble(load_as_float(src_row + c + e), scale);
-                const uint32_t q1 = quantize_nibble(load_as_float(src_row + c + e + 1), scale);
+                const uint32_t q0 = quantize_nibble(load_as_float(src_row + c + e), qr);
+                const uint32_t q1 = quantize_nibble(load_as_float(src_row + c + e + 1), qr);
                 dst_row[(c + e) >> 1] = static_cast<uint8_t>(q0 | (q1 << 4));
             }
         }

@@ -64,3 +64,42 @@ def test_quantize_then_mix_gemm_end_to_end(qlib, oracle, dev):
     assert oracle.max_rel(c.float().cpu().numpy(), ref) <= 1e-2
     # and against the unquantised product
     assert oracle.rel_l2(c.float().cpu().numpy(), oracle.gemm_f32(a32, b32, True)) <= 6e-2
+
+
+@pytest.mark.parametrize("target", ["int8", "int4"])
+def test_quantize_integer_rounding_at_and_around_ties(qlib, oracle, dev, target):
+    """The integer quantisers round x / scale without a division wherever the product with the reciprocal is provably
+    far enough from k + 1/2; inputs built to sit exactly on, and a few ulps either side of, every tie k + 1/2 (and
+    on the integers themselves) must still come out bit for bit as the oracle's divide-then-round."""
+    q = qlib
+    qmax = 127 if target == "int8" else 7
+    rng = np.random.default_rng(17)
+    for amax in (1.0, 3.1415927, 0.001953125, 1234.5677, 6.1e-5):
+        scale = np.float32(np.float32(amax) / np.float32(qmax))
+        k = np.arange(-qmax - 2, qmax + 2, dtype=np.float32)
+        base = np.concatenate([(k + np.float32(0.5)) * scale, k * scale, (k + np.float32(0.4999)) * scale,
+                               (k + np.float32(0.5001)) * scale]).astype(np.float32)
+        vals = [base]
+        for ulps in (1, 2, 3, 8, 64):
+            up = base.copy()
+            dn = base.copy()
+            for _ in range(ulps):
+                up = np.nextafter(up, np.float32(np.inf), dtype=np.float32)
+                dn = np.nextafter(dn, np.float32(-np.inf), dtype=np.float32)
+            vals += [up, dn]
+        x = np.concatenate(vals + [rng.standard_normal(4096).astype(np.float32) * np.float32(amax / 3)])
+        x = np.clip(x, -np.float32(amax), np.float32(amax)).astype(np.float32)
+        x[0] = np.float32(amax)  # pins the matrix's amax, hence the scale
+        if x.size % 16:
+            x = np.concatenate([x, np.zeros(16 - x.size % 16, np.float32)])
+        x = x.reshape(8, -1)  # an even number of columns (int4 packs pairs)
+        xt = torch.from_numpy(x).to(dev)
+        if target == "int8":
+            got, s = q.quantize(xt, torch.int8)
+            ref, s_ref = oracle.quantize_int8(x)
+            assert np.array_equal(got.cpu().numpy(), ref), amax
+        else:
+            got, s = q.quantize_int4(xt)
+            ref, s_ref = oracle.quantize_int4(x)
+            assert np.array_equal(got.cpu().numpy(), ref), amax
+        assert float(s) == s_ref
