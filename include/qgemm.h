@@ -173,9 +173,11 @@ int qgemm_plan_query(int in_dtype, int out_dtype, int b_layout, size_t M, size_t
  *   [8] rows of A loaded per pipeline stage; [9] CTAs launched;
  *   [10] CTAs per cluster when the K slices of [3] are added up inside one launch through distributed shared memory
  *        (2 or 4), 0 when they go through scratch and a second kernel. QGEMM_KCLUSTER=0 in the environment turns the
- *        one-launch form off.
+ *        one-launch form off;
+ *   [11] K blocks (128 bytes of K each) brought in by one TMA instruction: 2 with the 64-wide tile when K is a whole
+ *        number of blocks and both operands are K-major in memory, else 1 (QGEMM_KGROUP overrides).
  */
-#define QGEMM_PLAN_FIELDS 11
+#define QGEMM_PLAN_FIELDS 12
 int qgemm_plan_query_ex(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, size_t K,
                         const qgemm_tuning_t* tuning, int* out, int n_out);
 

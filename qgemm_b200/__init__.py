@@ -456,13 +456,13 @@ def plan_query(in_dtype: int, out_dtype: int, b_layout: int, M: int, N: int, K: 
     """The kernel configuration the library would use for this shape (qgemm_plan_query_ex): tile_m, tile_n,
     ctas_per_tile, split_k, tail_tiles, tail_slices, balanced_tiles (tile columns of the balanced tiling, 0 = equal
     tiles), min_tile_n, a_rows_per_stage, ctas, cluster_slices (CTAs per cluster when the K slices are added up inside
-    one launch, else 0)."""
-    n = 11
+    one launch, else 0), k_blocks_per_load."""
+    n = 12
     out = (C.c_int * n)()
     _check(lib().qgemm_plan_query_ex(in_dtype, out_dtype, b_layout, M, N, K, C.byref(tuning) if tuning else None, out,
                                      n), "qgemm_plan_query_ex")
     keys = ("tile_m", "tile_n", "ctas_per_tile", "split_k", "tail_tiles", "tail_slices", "balanced_tiles",
-            "min_tile_n", "a_rows_per_stage", "ctas", "cluster_slices")
+            "min_tile_n", "a_rows_per_stage", "ctas", "cluster_slices", "k_blocks_per_load")
     return dict(zip(keys, list(out)))
 
 

@@ -481,7 +481,23 @@ struct Plan {
     int tail_tiles;         // last-wave split (see tail_split): tiles of the last wave, 0 = off
     int tail_slices;
     int tail_kb_per_slice;
+    int kgroup;             // K blocks per TMA instruction (GemmParams::kgroup), 1 = one block per load
 };
+
+// K-grouped loads (GemmParams::kgroup): the lone-CTA kernels on K-major operands whose K is a whole number of 128-byte
+// blocks; by default two blocks per TMA instruction with the 64-wide tile. Measured on B200 (graph replay over cold
+// operands, us; 1 / 2 / 4 / 8 blocks per instruction): FP8 16 x 7168 x 2048 6.70 / 6.19 / 6.57 / 6.78, BF16 16 x 7168 x
+// 2048 10.13 / 8.73 / 8.94 / 9.67, FP8 1024 x 1024 x 4096 10.25 / 8.87 / 10.43 / 13.09, BF16 1024^3 6.78 / 6.14 / 6.75 /
+// 7.74: two halve the instruction count, more make the barriers too coarse for the pipeline. With the 128-wide tile
+// (16 KB boxes, six stages) it does not pay: FP8 256 x 7168 x 2048 8.08 / 8.41.
+int choose_kgroup(const Config& cfg, bool b_direct, size_t K, int elem_bytes) {
+    if (cfg.pair || b_direct || cfg.bal_tiles != 0 || (K * elem_bytes) % 128 != 0) return 1;
+    const int stages = std::min(16, (192 * 1024) / ((cfg.am + cfg.bn) * 128));
+    int g = g_env.kgroup > 0 ? g_env.kgroup : (cfg.bn == 64 ? 2 : 1);
+    if (g != 2 && g != 4 && g != 8) g = 1;
+    while (g > 1 && stages % g != 0) g /= 2;
+    return g;
+}
 
 int make_plan(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, size_t K, int sms,
               const qgemm_tuning_t* tuning, Plan* p, bool b_direct = false, bool allow_tail = true,
@@ -508,6 +524,7 @@ int make_plan(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, siz
     p->ldw = round_up(N, 4);
     p->partial_bytes = (p->cfg.splits > 1 && p->cfg.kcluster == 0) ? static_cast<size_t>(p->cfg.splits) * M * p->ldw * 4 : 0;
     p->tail_tiles = p->tail_slices = p->tail_kb_per_slice = 0;
+    p->kgroup = choose_kgroup(p->cfg, b_direct, K, p->ti.elem_bytes);
     if (allow_tail && p->cfg.pair && p->cfg.bn == kPairTileN && !p->cfg.wide && p->cfg.splits == 1) {
         const long long tiles = static_cast<long long>((M + kPairTileM - 1) / kPairTileM) *
                                 static_cast<long long>((N + kPairTileN - 1) / kPairTileN);
@@ -597,19 +614,7 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
                           g_env.direct_store != 0))
         plan.cfg.wide = false;
     const Config& cfg = plan.cfg;
-    // K-grouped loads (GemmParams::kgroup): the lone-CTA kernels on K-major operands whose K is a whole number of
-    // 128-byte blocks; by default two blocks per TMA instruction with the 64-wide tile. Measured on B200 (graph replay
-    // over cold operands, us; 1 / 2 / 4 / 8 blocks per instruction): FP8 16 x 7168 x 2048 6.70 / 6.19 / 6.57 / 6.78, BF16
-    // 16 x 7168 x 2048 10.13 / 8.73 / 8.94 / 9.67, FP8 1024 x 1024 x 4096 10.25 / 8.87 / 10.43 / 13.09, BF16 1024^3 6.78 /
-    // 6.14 / 6.75 / 7.74: two halve the instruction count, more make the barriers too coarse for the pipeline. With the
-    // 128-wide tile (16 KB boxes, six stages) it does not pay: FP8 256 x 7168 x 2048 8.08 / 8.41.
-    uint32_t kgroup = 1;
-    if (!cfg.pair && !b_direct && cfg.bal_tiles == 0 && (K * es) % 128 == 0) {
-        const int stages = std::min(16, (192 * 1024) / ((cfg.am + cfg.bn) * 128));
-        kgroup = g_env.kgroup > 0 ? static_cast<uint32_t>(g_env.kgroup) : (cfg.bn == 64 ? 2u : 1u);
-        if (kgroup != 2 && kgroup != 4 && kgroup != 8) kgroup = 1;
-        while (kgroup > 1 && stages % static_cast<int>(kgroup) != 0) kgroup /= 2;
-    }
+    const uint32_t kgroup = static_cast<uint32_t>(plan.kgroup);
     CUtensorMap ta, tb;
     rc = make_operand_map(A, M, K, lda, in_dtype, cfg.wide ? 256u : static_cast<uint32_t>(cfg.am), &ta, kgroup);
     if (rc != QGEMM_OK) return rc;
@@ -1047,7 +1052,8 @@ int qgemm_plan_query_ex(int in_dtype, int out_dtype, int b_layout, size_t M, siz
     const long long ctas = static_cast<long long>((M + tile_m - 1) / tile_m) * tiles_n * c.splits * (c.pair ? 2 : 1);
     const int vals[QGEMM_PLAN_FIELDS] = {
         tile_m, c.bn, c.pair ? 2 : 1, c.splits, plan.tail_tiles, plan.tail_slices, c.bal_tiles,
-        c.bal_tiles > 0 ? c.bal_units * 16 : c.bn, c.am, static_cast<int>(std::min<long long>(ctas, sms)), c.kcluster};
+        c.bal_tiles > 0 ? c.bal_units * 16 : c.bn, c.am, static_cast<int>(std::min<long long>(ctas, sms)), c.kcluster,
+        plan.kgroup};
     for (int i = 0; i < n_out && i < QGEMM_PLAN_FIELDS; ++i) out[i] = vals[i];
     return QGEMM_OK;
 }

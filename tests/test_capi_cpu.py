@@ -146,3 +146,35 @@ def test_plan_in_cluster_split_k(qlib):
         del os.environ["QGEMM_KCLUSTER"]
         q.lib().qgemm_reload_env()
     assert q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 32, 2048, 8192)["cluster_slices"] == 4
+
+
+def test_plan_k_grouped_loads_and_narrow_pairs(qlib):
+    """Two more planning rules that can be asked without a GPU: K blocks per TMA instruction (two with the 64-wide
+    tile when K is a whole number of 128-byte blocks and B is K-major; QGEMM_KGROUP overrides), and 256 x 128 tiles on
+    CTA pairs for mid-size problems whose tiles run in one wave."""
+    import os
+    q = qlib
+    skinny = q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 16, 7168, 2048)
+    assert (skinny["tile_n"], skinny["k_blocks_per_load"]) == (64, 2), skinny
+    assert q.plan_query(q.BF16, q.BF16, q.B_K_MAJOR, 16, 7168, 2040)["k_blocks_per_load"] == 1  # K * 2 % 128 != 0
+    assert q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 256, 7168, 2048)["k_blocks_per_load"] == 1  # 128-wide tile
+    assert q.plan_query(q.BF16, q.BF16, q.B_K_MAJOR, 8192, 8192, 8192)["k_blocks_per_load"] == 1  # CTA pairs
+    deep = q.plan_query(q.BF16, q.BF16, q.B_K_MAJOR, 32, 2048, 8192)  # the in-cluster split-K kernel groups too
+    assert (deep["cluster_slices"], deep["k_blocks_per_load"]) == (4, 2), deep
+    os.environ["QGEMM_KGROUP"] = "1"
+    try:
+        q.lib().qgemm_reload_env()
+        assert q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 16, 7168, 2048)["k_blocks_per_load"] == 1
+        os.environ["QGEMM_KGROUP"] = "8"  # 12 stages with 64 rows of A: 8 does not divide them, 4 does
+        q.lib().qgemm_reload_env()
+        assert q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 64, 7168, 2048)["k_blocks_per_load"] == 4
+    finally:
+        del os.environ["QGEMM_KGROUP"]
+        q.lib().qgemm_reload_env()
+    for dt in (q.BF16, q.FP8_E4M3):
+        mid = q.plan_query(dt, q.BF16, q.B_K_MAJOR, 1024, 2048, 8192)
+        assert (mid["tile_m"], mid["tile_n"], mid["ctas_per_tile"], mid["split_k"], mid["ctas"]) == (256, 128, 2, 1, 128), mid
+        big = q.plan_query(dt, q.BF16, q.B_K_MAJOR, 4096, 4096, 4096)  # several waves: 256 x 256 pairs
+        assert (big["tile_m"], big["tile_n"]) == (256, 256), big
+    forced = q.plan_query(q.INT8, q.INT32, q.B_K_MAJOR, 4096, 4096, 4096, q.Tuning(128, 1, 0, 0, 1, 0))
+    assert (forced["tile_m"], forced["tile_n"], forced["ctas_per_tile"]) == (256, 128, 2), forced
