@@ -19,8 +19,8 @@ The ONE JSON line printed by rank 0 also carries
     (strong scaling): GEMM-only time, and for N > 1 the NCCL all-gather of the C slices and the variant whose
     epilogue stores every tile to all ranks' full matrices over NVLink;
   * `configs` (N = 1): a short measurement of each other configuration -- FP16 1024^3, int8 and FP8 8192^3, the
-    FP8 skinny-to-square sweep and two few-tiles-long-K shapes (split-K inside one launch) with the library's GEMM
-    timed beside them, the block-scaled FP8 GEMM, the
+    FP8 skinny-to-square sweep, two few-tiles-long-K shapes (split-K inside one launch) and one mid-size shape with the
+    library's GEMM timed beside them, the block-scaled FP8 GEMM, the
     1- and 2-byte transpose and the quantise pre-pass -- each with its own roofline fraction and oracle check;
   * `cpu_baseline` (N = 1): the CPU restatement of the reference semantics (the reference ships no CPU GEMM).
 
@@ -75,11 +75,13 @@ WORKLOADS = {
     "d1_fp8_deep": ("fp8", "bf16", 128, 2048, 16384, True,
                     "FP8 e4m3 M=128 N=2048 K=16384 (few tiles, long K: split-K inside one launch), bf16 out"),
     "d2_bf16_deep": ("bf16", "bf16", 32, 2048, 8192, True, "BF16 M=32 N=2048 K=8192 (few tiles, long K), bf16 out"),
+    "m1_bf16_mid": ("bf16", "bf16", 1024, 2048, 8192, True,
+                    "BF16 M=1024 N=2048 K=8192 (one wave of mid-size tiles: 256 x 128 tiles on CTA pairs), bf16 out"),
     "c5_int8_sharded": ("int8", "bf16", 32768, 32768, 8192, True,
                         "int8 mixed GEMM 32768x32768x8192, B/C column-sharded over the ranks (strong scaling)"),
 }
 CONFIG_BLOCK = ["c1_fp16_1024", "c3_int8_8192", "c3_fp8_8192", "c4_fp8_16", "c4_fp8_64", "c4_fp8_256", "c4_fp8_1024",
-                "c4_fp8_6144", "d1_fp8_deep", "d2_bf16_deep", "f1_fp8_blockscale"]
+                "c4_fp8_6144", "d1_fp8_deep", "d2_bf16_deep", "m1_bf16_mid", "f1_fp8_blockscale"]
 
 
 _REAL_STDOUT = None
@@ -956,7 +958,7 @@ def run_config(ctx, args, name):
     out = {"description": WORKLOADS[name][6], "shape": [ops["M"], ops["N"], ops["K"]], "us": best * 1e3,
            "tflops": roof.get("tflops", roof["achieved"]), "roofline": roof, "sm_mhz": mhz, "steps": steps,
            "timed_loop": ("CUDA graph replay over %d rotating operand sets" % nsets) if use_graph else "direct launches"}
-    if name.startswith(("c4_", "d1_", "d2_")) or name == "c3_fp8_8192":
+    if name.startswith(("c4_", "d1_", "d2_", "m1_")) or name == "c3_fp8_8192":
         try:
             lcnt = [0]
 
