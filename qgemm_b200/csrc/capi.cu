@@ -714,6 +714,9 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
             p.prefetch_b = 1;
     }
 
+    // One 128-wide tile per CTA: the kernel variant whose staging buffers lie over the ring, with a seventh stage.
+    const bool one_tile = !cfg.pair && cfg.kcluster == 0 && cfg.bn == 128 && cfg.am == kBM && cfg.bal_tiles == 0 &&
+                          kgroup == 1 && work == static_cast<long long>(grid);
     cudaError_t e;
     const bool tail = cfg.pair && !cfg.wide && plan.tail_tiles > 0 && p.c_tma_ok && n_extra == 0;
     p.total_work = static_cast<int>(work);
@@ -754,9 +757,9 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
         }
     } else {
         switch (plan.ti.kind) {
-            case ptx::KIND_F16: e = launch_gemm_f16(cfg.bn, launch_out, cfg.am, ta, tb, tc, p, grid, stream); break;
-            case ptx::KIND_I8: e = launch_gemm_i8(cfg.bn, launch_out, cfg.am, ta, tb, tc, p, grid, stream); break;
-            default: e = launch_gemm_f8(cfg.bn, launch_out, cfg.am, ta, tb, tc, p, grid, stream); break;
+            case ptx::KIND_F16: e = launch_gemm_f16(cfg.bn, launch_out, cfg.am, ta, tb, tc, p, grid, stream, one_tile); break;
+            case ptx::KIND_I8: e = launch_gemm_i8(cfg.bn, launch_out, cfg.am, ta, tb, tc, p, grid, stream, one_tile); break;
+            default: e = launch_gemm_f8(cfg.bn, launch_out, cfg.am, ta, tb, tc, p, grid, stream, one_tile); break;
         }
     }
     if (e != cudaSuccess) return QGEMM_ERR_CUDA;

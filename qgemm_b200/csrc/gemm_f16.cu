@@ -3,8 +3,8 @@
 
 namespace qgemm {
 cudaError_t launch_gemm_f16(int bn, int out, int am, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
-                           int grid, cudaStream_t stream) {
-    return launch_kind<ptx::KIND_F16>(bn, out, am, ta, tb, tc, p, grid, stream);
+                            int grid, cudaStream_t stream, bool one) {
+    return launch_kind<ptx::KIND_F16>(bn, out, am, ta, tb, tc, p, grid, stream, one);
 }
 cudaError_t launch_gemm_pair_f16(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tws,
                                  const ExtraDst* extra,

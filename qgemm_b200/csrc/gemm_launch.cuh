@@ -43,12 +43,14 @@ struct StagesFor {
     static constexpr int value = kFit > 16 ? 16 : kFit;
 };
 
-template <int KIND, int BN, int OUT, int AM = kBM>
+// ONE: one tile per CTA (grid == number of tiles): the staging buffers lie over the ring and one more stage fits.
+template <int KIND, int BN, int OUT, int AM = kBM, bool ONE = false>
 cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
                        cudaStream_t stream) {
-    constexpr int STAGES = StagesFor<BN, AM>::value;
-    auto kernel = gemm_tcgen05_kernel<KIND, BN, STAGES, OUT, AM>;
-    constexpr int smem = GemmSmem<BN, STAGES, AM>::kDynamicBytes;
+    constexpr int STAGES = StagesFor<BN, AM>::value + (ONE ? 1 : 0);
+    auto kernel = gemm_tcgen05_kernel<KIND, BN, STAGES, OUT, AM, ONE>;
+    constexpr int smem = GemmSmem<BN, STAGES, AM, ONE>::kDynamicBytes;
+    static_assert(smem <= 227 * 1024, "dynamic shared memory of one CTA");
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -62,10 +64,20 @@ cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     return launch_pdl(kernel, dim3(grid), dim3(kGemmThreads), smem, stream, ta, tb, tc, p);
 }
 
-// `am` = rows of A loaded per stage: 128, or 64 / 32 / 16 with the 64-wide tile for small M.
+// `am` = rows of A loaded per stage: 128, or 64 / 32 / 16 with the 64-wide tile for small M. `one` (128-wide tiles, one
+// tile per CTA): the layout with a seventh stage.
 template <int KIND>
 cudaError_t launch_kind(int bn, int out, int am, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
-                        const GemmParams& p, int grid, cudaStream_t stream) {
+                        const GemmParams& p, int grid, cudaStream_t stream, bool one = false) {
+    if (one && bn == 128 && am == 128) {
+        switch (out) {
+            case OUT_F32: return launch_one<KIND, 128, OUT_F32, 128, true>(ta, tb, tc, p, grid, stream);
+            case OUT_BF16: return launch_one<KIND, 128, OUT_BF16, 128, true>(ta, tb, tc, p, grid, stream);
+            case OUT_F16: return launch_one<KIND, 128, OUT_F16, 128, true>(ta, tb, tc, p, grid, stream);
+            case OUT_RAW32: return launch_one<KIND, 128, OUT_RAW32, 128, true>(ta, tb, tc, p, grid, stream);
+            default: return cudaErrorInvalidValue;
+        }
+    }
 #define QGEMM_CASE(BN_, OUT_, AM_) \
     if (bn == BN_ && out == OUT_ && am == AM_) return launch_one<KIND, BN_, OUT_, AM_>(ta, tb, tc, p, grid, stream);
 #define QGEMM_CASES(BN_, AM_)        \
@@ -88,12 +100,13 @@ cudaError_t launch_kind(int bn, int out, int am, const CUtensorMap& ta, const CU
 // keep resident at once (queried once per device). `extra` non-null selects the variant whose epilogue also
 // stores every tile to p.n_extra_dst further destinations; `tws` is the tensor map of the last-wave scratch slots
 // (read only when p.tail_begin > 0).
-template <int KIND, int OUT, bool GATHER, int BN = kPairTileN>
+template <int KIND, int OUT, bool GATHER, int BN = kPairTileN, bool ONE = false>
 cudaError_t launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tws,
                             const typename ExtraDstParam<GATHER>::type& extra, const GemmParams& p, int clusters,
                             cudaStream_t stream) {
-    auto kernel = gemm_tcgen05_pair_kernel<KIND, OUT, GATHER, BN>;
-    constexpr int smem = PairSmemT<BN>::kDynamicBytes;
+    auto kernel = gemm_tcgen05_pair_kernel<KIND, OUT, GATHER, BN, ONE>;
+    constexpr int smem = PairSmemT<BN, ONE>::kDynamicBytes;
+    static_assert(smem <= 227 * 1024, "dynamic shared memory of one CTA");
     static bool configured[64] = {};
     static int max_clusters[64] = {};
     int dev = 0;
@@ -124,6 +137,10 @@ cudaError_t launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const 
     }
     if (clusters > max_clusters[dev]) clusters = max_clusters[dev];
     if (clusters < 1) clusters = 1;
+    if constexpr (ONE) {  // fewer clusters than tiles after all: the layout that allows several tiles per cluster
+        if (clusters < p.total_work)
+            return launch_pair_one<KIND, OUT, GATHER, BN, false>(ta, tb, tc, tws, extra, p, clusters, stream);
+    }
     return launch_pdl(kernel, dim3(2 * clusters), dim3(kGemmThreads), smem, stream, ta, tb, tc, tws, extra, p);
 }
 
@@ -133,6 +150,16 @@ cudaError_t launch_pair_kind(int bn, int out, const CUtensorMap& ta, const CUten
                              const CUtensorMap& tws, const ExtraDst* extra, const GemmParams& p, int clusters,
                              cudaStream_t stream) {
     const NoExtraDst none = {0};
+    if (bn == 128 && p.total_work <= clusters) {  // one tile per cluster: the nine-stage layout
+        if (extra != nullptr) return cudaErrorInvalidValue;
+        switch (out) {
+            case OUT_F32: return launch_pair_one<KIND, OUT_F32, false, 128, true>(ta, tb, tc, tws, none, p, clusters, stream);
+            case OUT_BF16: return launch_pair_one<KIND, OUT_BF16, false, 128, true>(ta, tb, tc, tws, none, p, clusters, stream);
+            case OUT_F16: return launch_pair_one<KIND, OUT_F16, false, 128, true>(ta, tb, tc, tws, none, p, clusters, stream);
+            case OUT_RAW32: return launch_pair_one<KIND, OUT_RAW32, false, 128, true>(ta, tb, tc, tws, none, p, clusters, stream);
+            default: return cudaErrorInvalidValue;
+        }
+    }
     if (bn == 128) {
         if (extra != nullptr) return cudaErrorInvalidValue;
         switch (out) {
@@ -262,10 +289,10 @@ int kcluster_max_clusters(int slices);
 
 // Defined one per translation unit so the kinds compile in parallel.
 cudaError_t launch_gemm_f16(int bn, int out, int am, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
-                            int grid, cudaStream_t stream);
+                            int grid, cudaStream_t stream, bool one = false);
 cudaError_t launch_gemm_i8(int bn, int out, int am, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
-                           int grid, cudaStream_t stream);
+                            int grid, cudaStream_t stream, bool one = false);
 cudaError_t launch_gemm_f8(int bn, int out, int am, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
-                           int grid, cudaStream_t stream);
+                            int grid, cudaStream_t stream, bool one = false);
 
 }  // namespace qgemm

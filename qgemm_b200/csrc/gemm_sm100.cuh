@@ -344,23 +344,27 @@ __device__ __forceinline__ void epilogue_tma(const CUtensorMap* tmap_c, uint32_t
 
 // AM = rows of A actually loaded per stage (128, or 64 / 32 when M is that small: the MMA still reads 128 rows,
 // the rest being whatever follows in shared memory, which only reaches accumulator rows that are never stored).
-template <int BN, int STAGES, int AM = kBM>
+// ONE = the CTA is launched for exactly one tile: the epilogue's staging buffers then lie over the start of the ring
+// (idle once the tile's last MMA has completed) instead of behind it, and the 32 KB saved hold one more stage -- for
+// one wave of tiles what a CTA can have in flight, divided by the latency of a load, is what sets its pace.
+template <int BN, int STAGES, int AM = kBM, bool ONE = false>
 struct GemmSmem {
     static constexpr int kAStage = AM * 128;
     static constexpr int kBStage = BN * 128;
     static constexpr int kTiles = STAGES * (kAStage + kBStage);
-    static constexpr int kOutOffset = kTiles;                    // epilogue staging: 4 warps x 2 buffers x 4 KB
-    static constexpr int kBarOffset = kTiles + kEpilogueStagingBytes;  // full[STAGES], empty[STAGES], tfull[2], tempty[2]
+    static_assert(!ONE || kTiles >= kEpilogueStagingBytes, "the staging buffers fit over the ring");
+    static constexpr int kOutOffset = ONE ? 0 : kTiles;          // epilogue staging: 4 warps x 2 buffers x 4 KB
+    static constexpr int kBarOffset = kTiles + (ONE ? 0 : kEpilogueStagingBytes);  // full[STAGES], empty[STAGES], tfull[2], tempty[2]
     static constexpr int kMiscOffset = kBarOffset + (2 * STAGES + 4) * 8;  // tmem base, abort flag
     static constexpr int kTotal = kMiscOffset + 16;
     static constexpr int kDynamicBytes = kTotal + 1024;          // slack for the 1024-byte alignment
 };
 
-template <int KIND, int BN, int STAGES, int OUT, int AM = kBM>
+template <int KIND, int BN, int STAGES, int OUT, int AM = kBM, bool ONE = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
-    using L = GemmSmem<BN, STAGES, AM>;
+    using L = GemmSmem<BN, STAGES, AM, ONE>;
     static_assert(STAGES * L::kAStage + (kBM - AM) * 128 <= L::kTiles, "the MMA's 128-row read of A stays inside the tile area");
     constexpr int ELT = (KIND == ptx::KIND_F16) ? 2 : 1;
     constexpr int BK = 128 / ELT;  // elements per 128-byte K block

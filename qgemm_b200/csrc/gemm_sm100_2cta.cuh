@@ -24,14 +24,17 @@ constexpr int kPairTileN = 256;
 
 // BN = tile width: 256, or 128 (256 x 128 tiles: a CTA then loads 128 rows of A and 64 rows of B, 24 KB per K block for
 // its 128 x 128 share of the output where a lone CTA on a 128 x 128 tile loads 32 KB; eight stages fit).
-template <int BN>
+// ONE (256 x 128 tiles only) = one tile per cluster: the epilogue's staging buffers lie over the start of the ring,
+// which is idle by then in both CTAs, and a ninth stage takes their place (see GemmSmem).
+template <int BN, bool ONE = false>
 struct PairSmemT {
-    static constexpr int kStages = BN == 256 ? 6 : 8;
+    static_assert(!ONE || BN == 128, "one-tile layout: 256 x 128 tiles");
+    static constexpr int kStages = BN == 256 ? 6 : (ONE ? 9 : 8);
     static constexpr int kAStage = 128 * 128;
     static constexpr int kBStage = (BN / 2) * 128;
     static constexpr int kTiles = kStages * (kAStage + kBStage);
-    static constexpr int kOutOffset = kTiles;  // epilogue staging (see epilogue_tma)
-    static constexpr int kBarOffset = kTiles + kEpilogueStagingBytes;
+    static constexpr int kOutOffset = ONE ? 0 : kTiles;  // epilogue staging (see epilogue_tma)
+    static constexpr int kBarOffset = kTiles + (ONE ? 0 : kEpilogueStagingBytes);
     static constexpr int kMiscOffset = kBarOffset + (2 * kStages + 4) * 8;
     static constexpr int kTotal = kMiscOffset + 16;
     static constexpr int kDynamicBytes = kTotal + 1024;
@@ -52,12 +55,12 @@ struct ExtraDstParam<true> {
 // only and has no last-wave split.
 // GATHER: the epilogue also stores every tile to the p.n_extra_dst destinations of `extra` (see ExtraDst).
 
-template <int KIND, int OUT, bool GATHER = false, int BN = kPairTileN>
+template <int KIND, int OUT, bool GATHER = false, int BN = kPairTileN, bool ONE = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_ws,
                          const __grid_constant__ typename ExtraDstParam<GATHER>::type extra, const GemmParams p) {
-    using L = PairSmemT<BN>;
+    using L = PairSmemT<BN, ONE>;
     static_assert(BN == 256 || BN == 128, "pair tile width");
     constexpr int STAGES = L::kStages;
     constexpr int ELT = (KIND == ptx::KIND_F16) ? 2 : 1;
