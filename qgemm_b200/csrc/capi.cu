@@ -229,6 +229,8 @@ EnvSettings read_env() {
     e.kcluster_off = (kc != nullptr && kc[0] == '0') ? 1 : 0;
     const char* eg = std::getenv("QGEMM_EARLY_GROUPS");  // experiments: loads issued ahead of the CTA-wide barrier
     e.early_groups = eg != nullptr ? std::max(0, std::atoi(eg)) : -1;
+    const char* ot = std::getenv("QGEMM_ONE_TILE");  // 0: never the one-tile-per-CTA kernel variants
+    e.one_tile_off = (ot != nullptr && ot[0] == '0') ? 1 : 0;
     e.kgroup = std::max(0, env_int("QGEMM_KGROUP"));  // 0 = the library's choice, 1 = off, 2 / 4 / 8 = K blocks per load
     e.host_bands = std::max(0, env_int("QGEMM_HOST_BANDS"));
     e.host_bands_n = std::max(0, env_int("QGEMM_HOST_BANDS_N"));
@@ -715,7 +717,7 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
     }
 
     // One 128-wide tile per CTA: the kernel variant whose staging buffers lie over the ring, with a seventh stage.
-    const bool one_tile = !cfg.pair && cfg.kcluster == 0 && cfg.bn == 128 && cfg.am == kBM && cfg.bal_tiles == 0 &&
+    const bool one_tile = g_env.one_tile_off == 0 && !cfg.pair && cfg.kcluster == 0 && cfg.bn == 128 && cfg.am == kBM && cfg.bal_tiles == 0 &&
                           kgroup == 1 && work == static_cast<long long>(grid);
     cudaError_t e;
     const bool tail = cfg.pair && !cfg.wide && plan.tail_tiles > 0 && p.c_tma_ok && n_extra == 0;
@@ -745,9 +747,9 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
         int clusters = static_cast<int>(std::min<long long>(p.total_work, st->sm_count / 2));
         if (cap > 0) clusters = std::min(clusters, std::max(1, cap / 2));
         switch (plan.ti.kind) {
-            case ptx::KIND_F16: e = launch_gemm_pair_f16(cfg.bn, launch_out, ta, tb, tc, tws, extra_arg, p, clusters, stream); break;
-            case ptx::KIND_I8: e = launch_gemm_pair_i8(cfg.bn, launch_out, ta, tb, tc, tws, extra_arg, p, clusters, stream); break;
-            default: e = launch_gemm_pair_f8(cfg.bn, launch_out, ta, tb, tc, tws, extra_arg, p, clusters, stream); break;
+            case ptx::KIND_F16: e = launch_gemm_pair_f16(cfg.bn, launch_out, ta, tb, tc, tws, extra_arg, p, clusters, stream, g_env.one_tile_off == 0); break;
+            case ptx::KIND_I8: e = launch_gemm_pair_i8(cfg.bn, launch_out, ta, tb, tc, tws, extra_arg, p, clusters, stream, g_env.one_tile_off == 0); break;
+            default: e = launch_gemm_pair_f8(cfg.bn, launch_out, ta, tb, tc, tws, extra_arg, p, clusters, stream, g_env.one_tile_off == 0); break;
         }
     } else if (cfg.kcluster > 0) {
         switch (plan.ti.kind) {

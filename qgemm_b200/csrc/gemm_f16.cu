@@ -8,8 +8,8 @@ cudaError_t launch_gemm_f16(int bn, int out, int am, const CUtensorMap& ta, cons
 }
 cudaError_t launch_gemm_pair_f16(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tws,
                                  const ExtraDst* extra,
-                                 const GemmParams& p, int clusters, cudaStream_t stream) {
-    return launch_pair_kind<ptx::KIND_F16>(bn, out, ta, tb, tc, tws, extra, p, clusters, stream);
+                                 const GemmParams& p, int clusters, cudaStream_t stream, bool one_ok) {
+    return launch_pair_kind<ptx::KIND_F16>(bn, out, ta, tb, tc, tws, extra, p, clusters, stream, one_ok);
 }
 cudaError_t launch_gemm_wide_f16(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                                  int clusters, cudaStream_t stream) {

@@ -8,8 +8,8 @@ cudaError_t launch_gemm_i8(int bn, int out, int am, const CUtensorMap& ta, const
 }
 cudaError_t launch_gemm_pair_i8(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tws,
                                  const ExtraDst* extra,
-                                 const GemmParams& p, int clusters, cudaStream_t stream) {
-    return launch_pair_kind<ptx::KIND_I8>(bn, out, ta, tb, tc, tws, extra, p, clusters, stream);
+                                 const GemmParams& p, int clusters, cudaStream_t stream, bool one_ok) {
+    return launch_pair_kind<ptx::KIND_I8>(bn, out, ta, tb, tc, tws, extra, p, clusters, stream, one_ok);
 }
 cudaError_t launch_gemm_wide_i8(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                                  int clusters, cudaStream_t stream) {

@@ -148,9 +148,9 @@ cudaError_t launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const 
 template <int KIND>
 cudaError_t launch_pair_kind(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
                              const CUtensorMap& tws, const ExtraDst* extra, const GemmParams& p, int clusters,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, bool one_ok = true) {
     const NoExtraDst none = {0};
-    if (bn == 128 && p.total_work <= clusters) {  // one tile per cluster: the nine-stage layout
+    if (bn == 128 && one_ok && p.total_work <= clusters) {  // one tile per cluster: the nine-stage layout
         if (extra != nullptr) return cudaErrorInvalidValue;
         switch (out) {
             case OUT_F32: return launch_pair_one<KIND, OUT_F32, false, 128, true>(ta, tb, tc, tws, none, p, clusters, stream);
@@ -244,13 +244,13 @@ cudaError_t launch_gemm_wide_f8(int out, const CUtensorMap& ta, const CUtensorMa
 
 cudaError_t launch_gemm_pair_f16(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tws,
                                  const ExtraDst* extra, const GemmParams& p,
-                                 int clusters, cudaStream_t stream);
+                                 int clusters, cudaStream_t stream, bool one_ok = true);
 cudaError_t launch_gemm_pair_i8(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tws,
                                  const ExtraDst* extra, const GemmParams& p,
-                                int clusters, cudaStream_t stream);
+                                int clusters, cudaStream_t stream, bool one_ok = true);
 cudaError_t launch_gemm_pair_f8(int bn, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tws,
                                  const ExtraDst* extra, const GemmParams& p,
-                                int clusters, cudaStream_t stream);
+                                int clusters, cudaStream_t stream, bool one_ok = true);
 
 // Block-scaled FP8 GEMM (gemm_blockscale.cu): 128 x 128 tiles, one partial accumulator per 128-wide K block.
 struct BlockScaleParams {
