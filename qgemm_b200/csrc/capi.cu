@@ -227,6 +227,7 @@ EnvSettings read_env() {
     e.prefetch_force = (pf != nullptr && pf[0] == '1') ? 1 : 0;  // experiments: hints wherever the kernel can issue them
     const char* kc = std::getenv("QGEMM_KCLUSTER");
     e.kcluster_off = (kc != nullptr && kc[0] == '0') ? 1 : 0;
+    e.kcluster_pair_off = (kc != nullptr && kc[0] == '1') ? 1 : 0;  // 1: the lone-CTA form only, not the CTA-pair form
     const char* eg = std::getenv("QGEMM_EARLY_GROUPS");  // experiments: loads issued ahead of the CTA-wide barrier
     e.early_groups = eg != nullptr ? std::max(0, std::atoi(eg)) : -1;
     const char* ot = std::getenv("QGEMM_ONE_TILE");  // 0: never the one-tile-per-CTA kernel variants
@@ -274,6 +275,7 @@ bool tail_split(long long tiles, int clusters, int kb_total, int* tail_tiles, in
 // `in_cluster` = the K slices of a tile run on the CTAs of one cluster and are added up through distributed shared
 // memory (gemm_sm100_kcluster.cuh): no slabs in global memory, no second kernel.
 constexpr double kClusterReduceCost = 2.0;
+constexpr double kPairClusterReduceCost = 4.0;  // a pair's CTA has 128 x 128 partial sums to put through shared memory
 double estimate(int bn, bool pair, int splits, size_t M, size_t N, int kb_total, int sms, int* kbps_out,
                 bool allow_tail = false, bool in_cluster = false) {
     const int tile_m = pair ? kPairTileM : kBM;
@@ -298,7 +300,7 @@ double estimate(int bn, bool pair, int splits, size_t M, size_t N, int kb_total,
     if (real_splits > 1 && in_cluster) {
         // full 128-row tiles have four times the partial sums of a 32-row problem to put through shared memory
         // (measured: FP8 1024 x 512 x 2048 in two slices 6.9 us against 6.0 unsplit, so the split must not be taken there)
-        t += M > 64 ? 2.0 * kClusterReduceCost : kClusterReduceCost;
+        t += pair ? kPairClusterReduceCost : (M > 64 ? 2.0 * kClusterReduceCost : kClusterReduceCost);
     } else if (real_splits > 1) {
         // partial slabs are written once and read once by the second pass (~1.75 MB per unit of time)
         const double slab_bytes = static_cast<double>(real_splits) * M * N * 4.0;
@@ -366,17 +368,22 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
             // tile (which always loads 128 rows of A) only when M has more than 64 rows or the caller asked for it. Measured on B200 against the two-launch form at
             // the same split (graph replay over cold operands, us): FP8 32 x 2048 x 8192 7.5 / 8.7, 128 x 2048 x 16384
             // 11.6 / 12.9, 128 x 1024 x 4096 6.1 / 6.9; BF16 32 x 2048 x 8192 10.1 / 11.7, 256 x 1024 x 8192 10.9 / 12.4.
-            if (allow_kcluster && g_env.kcluster_off == 0 && g_env.balance == 0 && !c.pair && (c.bn == 64 || (c.bn == 128 && (M > 64 || want_bn == 128))) && (s == 2 || s == 4 || s == 8) &&
+            // CTA pairs on 256 x 128 tiles likewise (gemm_sm100_2cta_kcluster.cuh): 2 or 4 pairs per cluster.
+            const bool lone_ok = !c.pair && (c.bn == 64 || (c.bn == 128 && (M > 64 || want_bn == 128))) &&
+                                 (s == 2 || s == 4 || s == 8);
+            const bool pair_ok = c.pair && c.bn == 128 && (s == 2 || s == 4) && g_env.kcluster_pair_off == 0;
+            if (allow_kcluster && g_env.kcluster_off == 0 && g_env.balance == 0 && (lone_ok || pair_ok) &&
                 (kb_total + kbps - 1) / kbps == s && !(tuning && tuning->max_ctas != 0) && g_env.max_ctas == 0) {
+                const int tm = c.pair ? kPairTileM : kBM;
                 const long long tiles =
-                    static_cast<long long>((M + kBM - 1) / kBM) * static_cast<long long>((N + c.bn - 1) / c.bn);
-                if (tiles <= kcluster_capacity(s, sms)) {
+                    static_cast<long long>((M + tm - 1) / tm) * static_cast<long long>((N + c.bn - 1) / c.bn);
+                if (tiles <= kcluster_capacity(c.pair ? 2 * s : s, sms)) {
                     int kbps2 = 0;
-                    const double tc = estimate(c.bn, false, s, M, N, kb_total, sms, &kbps2, false, true);
+                    const double tc = estimate(c.bn, c.pair, s, M, N, kb_total, sms, &kbps2, false, true);
                     if (tc < best_t) {
                         best_t = tc;
                         best.bn = c.bn;
-                        best.pair = false;
+                        best.pair = c.pair;
                         best.kb_per_split = kbps2;
                         best.splits = s;
                         best.kcluster = s;
@@ -722,7 +729,13 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
     cudaError_t e;
     const bool tail = cfg.pair && !cfg.wide && plan.tail_tiles > 0 && p.c_tma_ok && n_extra == 0;
     p.total_work = static_cast<int>(work);
-    if (cfg.wide) {
+    if (cfg.kcluster > 0 && cfg.pair) {
+        switch (plan.ti.kind) {
+            case ptx::KIND_F16: e = launch_gemm_pair_kcluster_f16(launch_out, cfg.kcluster, ta, tb, p, static_cast<int>(work), stream); break;
+            case ptx::KIND_I8: e = launch_gemm_pair_kcluster_i8(launch_out, cfg.kcluster, ta, tb, p, static_cast<int>(work), stream); break;
+            default: e = launch_gemm_pair_kcluster_f8(launch_out, cfg.kcluster, ta, tb, p, static_cast<int>(work), stream); break;
+        }
+    } else if (cfg.wide) {
         if (!p.c_tma_ok) return QGEMM_ERR_CUDA;
         int clusters = static_cast<int>(std::min<long long>(work, st->sm_count / 2));
         if (cap > 0) clusters = std::min(clusters, std::max(1, cap / 2));

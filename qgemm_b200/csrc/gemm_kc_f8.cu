@@ -6,6 +6,10 @@ cudaError_t launch_gemm_kcluster_f8(int bn, int out, int am, int slices, const C
                                     const GemmParams& p, int tiles, cudaStream_t stream) {
     return launch_kcluster_kind<ptx::KIND_F8>(bn, out, am, slices, ta, tb, p, tiles, stream);
 }
+cudaError_t launch_gemm_pair_kcluster_f8(int out, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
+                                         const GemmParams& p, int tiles, cudaStream_t stream) {
+    return launch_pair_kcluster_kind<ptx::KIND_F8>(out, slices, ta, tb, p, tiles, stream);
+}
 
 // How many clusters of `slices` CTAs of this kernel the current device keeps resident at once (a cluster needs its
 // CTAs on SMs of one GPC, so this is less than SMs / slices); 0 when it cannot be asked (no device). Asked once per

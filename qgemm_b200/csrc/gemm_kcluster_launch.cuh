@@ -1,6 +1,7 @@
 // Host-side launch of the in-cluster split-K kernel (gemm_sm100_kcluster.cuh); one translation unit per kind.
 #pragma once
 #include "gemm_launch.cuh"
+#include "gemm_sm100_2cta_kcluster.cuh"
 #include "gemm_sm100_kcluster.cuh"
 
 namespace qgemm {
@@ -68,6 +69,57 @@ cudaError_t launch_kcluster_kind(int bn, int out, int am, int slices, const CUte
     QGEMM_KC_CASES(64, 16, 8)
 #undef QGEMM_KC_CASES
 #undef QGEMM_KC_CASE
+    return cudaErrorInvalidValue;
+}
+
+
+// CTA pairs (gemm_sm100_2cta_kcluster.cuh): `tiles` clusters of 2 * `slices` CTAs, one 256 x 128 tile each.
+template <int KIND, int OUT, int S>
+cudaError_t launch_pair_kcluster_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int tiles,
+                                     cudaStream_t stream) {
+    auto kernel = gemm_tcgen05_pair_kcluster_kernel<KIND, OUT, S>;
+    constexpr int smem = PairSmemT<128>::kDynamicBytes;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!configured[dev]) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(tiles) * 2 * S);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2 * S;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, ta, tb, p);
+}
+
+template <int KIND>
+cudaError_t launch_pair_kcluster_kind(int out, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
+                                      const GemmParams& p, int tiles, cudaStream_t stream) {
+#define QGEMM_PKC_CASE(OUT_, S_) \
+    if (out == OUT_ && slices == S_) return launch_pair_kcluster_one<KIND, OUT_, S_>(ta, tb, p, tiles, stream);
+#define QGEMM_PKC_CASES(S_)       \
+    QGEMM_PKC_CASE(OUT_F32, S_)   \
+    QGEMM_PKC_CASE(OUT_BF16, S_)  \
+    QGEMM_PKC_CASE(OUT_F16, S_)   \
+    QGEMM_PKC_CASE(OUT_RAW32, S_)
+    QGEMM_PKC_CASES(2)
+    QGEMM_PKC_CASES(4)
+#undef QGEMM_PKC_CASES
+#undef QGEMM_PKC_CASE
     return cudaErrorInvalidValue;
 }
 

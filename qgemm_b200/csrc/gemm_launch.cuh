@@ -284,6 +284,13 @@ cudaError_t launch_gemm_kcluster_i8(int bn, int out, int am, int slices, const C
                                     const GemmParams& p, int tiles, cudaStream_t stream);
 cudaError_t launch_gemm_kcluster_f8(int bn, int out, int am, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
                                     const GemmParams& p, int tiles, cudaStream_t stream);
+// The same for CTA pairs on 256 x 128 tiles (gemm_sm100_2cta_kcluster.cuh): `tiles` clusters of 2 * `slices` CTAs.
+cudaError_t launch_gemm_pair_kcluster_f16(int out, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
+                                          const GemmParams& p, int tiles, cudaStream_t stream);
+cudaError_t launch_gemm_pair_kcluster_i8(int out, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
+                                         const GemmParams& p, int tiles, cudaStream_t stream);
+cudaError_t launch_gemm_pair_kcluster_f8(int out, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
+                                         const GemmParams& p, int tiles, cudaStream_t stream);
 // Clusters of `slices` CTAs the current device keeps resident at once; 0 = unknown (no device).
 int kcluster_max_clusters(int slices);
 
