@@ -78,7 +78,7 @@ template <int KIND, int OUT, int S>
 cudaError_t launch_pair_kcluster_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int tiles,
                                      cudaStream_t stream) {
     auto kernel = gemm_tcgen05_pair_kcluster_kernel<KIND, OUT, S>;
-    constexpr int smem = PairSmemT<128>::kDynamicBytes;
+    constexpr int smem = PairSmemT<128, true>::kDynamicBytes;
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);

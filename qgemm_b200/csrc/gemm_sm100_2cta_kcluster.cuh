@@ -28,7 +28,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_pair_kcluster_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                                   const GemmParams p) {
     constexpr int BN = 128;
-    using L = PairSmemT<BN>;
+    using L = PairSmemT<BN, true>;  // no staging buffers (results are stored from registers): nine stages
     static_assert(S == 2 || S == 4, "pairs per cluster");
     constexpr int STAGES = L::kStages;
     constexpr int ELT = (KIND == ptx::KIND_F16) ? 2 : 1;
