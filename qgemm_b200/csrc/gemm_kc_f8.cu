@@ -23,9 +23,9 @@ static int max_clusters_of() {
         return 0;
     }
     if (cached[dev] != 0) return cached[dev];
-    constexpr int STAGES = StagesFor<128, 128>::value;
+    constexpr int STAGES = StagesFor<128, 128>::value + 1;
     auto kernel = gemm_tcgen05_kcluster_kernel<ptx::KIND_F8, 128, STAGES, OUT_BF16, 128, S>;
-    constexpr int smem = GemmSmem<128, STAGES, 128>::kDynamicBytes;
+    constexpr int smem = GemmSmem<128, STAGES, 128, true>::kDynamicBytes;
     int n = 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(S * 32);

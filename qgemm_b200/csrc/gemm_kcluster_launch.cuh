@@ -9,9 +9,12 @@ namespace qgemm {
 template <int KIND, int BN, int OUT, int AM, int S>
 cudaError_t launch_kcluster_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int tiles,
                                 cudaStream_t stream) {
-    constexpr int STAGES = StagesFor<BN, AM>::value;
+    // the kernel has no staging buffers, which leaves room for a seventh stage of the 128-wide tile (the 64-wide
+    // tile keeps its even stage count for the two-blocks-per-load grouping)
+    constexpr int STAGES = StagesFor<BN, AM>::value + (BN == 128 ? 1 : 0);
     auto kernel = gemm_tcgen05_kcluster_kernel<KIND, BN, STAGES, OUT, AM, S>;
-    constexpr int smem = GemmSmem<BN, STAGES, AM>::kDynamicBytes;
+    constexpr int smem = GemmSmem<BN, STAGES, AM, true>::kDynamicBytes;
+    static_assert(smem <= 227 * 1024, "dynamic shared memory of one CTA");
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);

@@ -30,7 +30,7 @@ template <int KIND, int BN, int STAGES, int OUT, int AM, int S>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kcluster_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                              const GemmParams p) {
-    using L = GemmSmem<BN, STAGES, AM>;
+    using L = GemmSmem<BN, STAGES, AM, true>;  // no staging buffers: results are stored from registers
     static_assert(S == 2 || S == 4 || S == 8, "cluster size (8 is the largest portable one)");
     static_assert(BN == 64 || BN == 128, "BN / 4 threads x four columns cover a row of the tile");
     static_assert(kBM * (BN + kKcPad) * 4 <= L::kTiles, "the partial tile fits in the pipeline's ring");
