@@ -19,7 +19,7 @@ The ONE JSON line printed by rank 0 also carries
     (strong scaling): GEMM-only time, and for N > 1 the NCCL all-gather of the C slices and the variant whose
     epilogue stores every tile to all ranks' full matrices over NVLink;
   * `configs` (N = 1): a short measurement of each other configuration -- FP16 1024^3, int8 and FP8 8192^3, the
-    FP8 skinny-to-square sweep, two few-tiles-long-K shapes (split-K inside one launch) and one mid-size shape with the
+    FP8 skinny-to-square sweep, two few-tiles-long-K shapes (split-K inside one launch) and two mid-size shapes with the
     library's GEMM timed beside them, the block-scaled FP8 GEMM, the
     1- and 2-byte transpose and the quantise pre-pass -- each with its own roofline fraction and oracle check;
   * `cpu_baseline` (N = 1): the CPU restatement of the reference semantics (the reference ships no CPU GEMM).
@@ -77,11 +77,14 @@ WORKLOADS = {
     "d2_bf16_deep": ("bf16", "bf16", 32, 2048, 8192, True, "BF16 M=32 N=2048 K=8192 (few tiles, long K), bf16 out"),
     "m1_bf16_mid": ("bf16", "bf16", 1024, 2048, 8192, True,
                     "BF16 M=1024 N=2048 K=8192 (one wave of mid-size tiles: 256 x 128 tiles on CTA pairs), bf16 out"),
+    "m2_bf16_mid_deep": ("bf16", "bf16", 1024, 1024, 8192, True,
+                         "BF16 M=N=1024 K=8192 (mid-size tiles, long K: K slices of 256 x 128 pair tiles inside one "
+                         "launch), bf16 out"),
     "c5_int8_sharded": ("int8", "bf16", 32768, 32768, 8192, True,
                         "int8 mixed GEMM 32768x32768x8192, B/C column-sharded over the ranks (strong scaling)"),
 }
 CONFIG_BLOCK = ["c1_fp16_1024", "c3_int8_8192", "c3_fp8_8192", "c4_fp8_16", "c4_fp8_64", "c4_fp8_256", "c4_fp8_1024",
-                "c4_fp8_6144", "d1_fp8_deep", "d2_bf16_deep", "m1_bf16_mid", "f1_fp8_blockscale"]
+                "c4_fp8_6144", "d1_fp8_deep", "d2_bf16_deep", "m1_bf16_mid", "m2_bf16_mid_deep", "f1_fp8_blockscale"]
 
 
 _REAL_STDOUT = None
@@ -539,7 +542,7 @@ def kernel_name_of(ops, plan):
     if ops["blockscale"]:
         return "fp8_blockscale_kernel"
     if plan.get("cluster_slices", 0) > 1:
-        return "gemm_tcgen05_kcluster_kernel"
+        return "gemm_tcgen05_pair_kcluster_kernel" if plan.get("ctas_per_tile") == 2 else "gemm_tcgen05_kcluster_kernel"
     return ("gemm_tcgen05_wide_pair_kernel" if plan["tile_m"] == 512 else
             "gemm_tcgen05_pair_kernel" if plan["ctas_per_tile"] == 2 else "gemm_tcgen05_kernel")
 
@@ -958,7 +961,7 @@ def run_config(ctx, args, name):
     out = {"description": WORKLOADS[name][6], "shape": [ops["M"], ops["N"], ops["K"]], "us": best * 1e3,
            "tflops": roof.get("tflops", roof["achieved"]), "roofline": roof, "sm_mhz": mhz, "steps": steps,
            "timed_loop": ("CUDA graph replay over %d rotating operand sets" % nsets) if use_graph else "direct launches"}
-    if name.startswith(("c4_", "d1_", "d2_", "m1_")) or name == "c3_fp8_8192":
+    if name.startswith(("c4_", "d1_", "d2_", "m1_", "m2_")) or name == "c3_fp8_8192":
         try:
             lcnt = [0]
 

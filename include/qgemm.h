@@ -172,8 +172,9 @@ int qgemm_plan_query(int in_dtype, int out_dtype, int b_layout, size_t M, size_t
  *   [7] the narrowest tile's width in columns (the widest is 16 more when N / 16 does not divide evenly);
  *   [8] rows of A loaded per pipeline stage; [9] CTAs launched;
  *   [10] CTAs per cluster when the K slices of [3] are added up inside one launch through distributed shared memory
- *        (2 or 4), 0 when they go through scratch and a second kernel. QGEMM_KCLUSTER=0 in the environment turns the
- *        one-launch form off;
+ *        (2, 4 or 8; with [2] == 2 the slices run on CTA pairs and the cluster has twice as many CTAs), 0 when they go
+ *        through scratch and a second kernel. QGEMM_KCLUSTER=0 in the environment turns the one-launch form off,
+ *        QGEMM_KCLUSTER=1 its CTA-pair variant only;
  *   [11] K blocks (128 bytes of K each) brought in by one TMA instruction: 2 with the 64-wide tile when K is a whole
  *        number of blocks and both operands are K-major in memory, else 1 (QGEMM_KGROUP overrides).
  */
