@@ -275,7 +275,7 @@ bool tail_split(long long tiles, int clusters, int kb_total, int* tail_tiles, in
 // `in_cluster` = the K slices of a tile run on the CTAs of one cluster and are added up through distributed shared
 // memory (gemm_sm100_kcluster.cuh): no slabs in global memory, no second kernel.
 constexpr double kClusterReduceCost = 2.0;
-constexpr double kPairClusterReduceCost = 4.0;  // a pair's CTA has 128 x 128 partial sums to put through shared memory
+constexpr double kPairClusterReduceCost = 3.0;  // a pair's CTA has 128 x 128 partial sums to put through shared memory
 double estimate(int bn, bool pair, int splits, size_t M, size_t N, int kb_total, int sms, int* kbps_out,
                 bool allow_tail = false, bool in_cluster = false) {
     const int tile_m = pair ? kPairTileM : kBM;
