@@ -193,7 +193,7 @@ struct Config {
     int bn, splits, kb_per_split, group_m;
     bool pair;  // two CTAs per 256x256 tile (bn is then 256 and tiles are counted in 256-row units)
     bool wide;  // pair with 512x256 tiles, both accumulators of a CTA in use (gemm_sm100_2cta_wide.cuh)
-    int am;     // rows of A loaded per stage (128; 64 or 32 with the 64-wide tile when M is that small)
+    int am;     // rows of A loaded per stage (128; 64, 32 or 16 with the lone-CTA kernels when M is that small)
     // Balanced column tiling (GemmParams::bal_units): bal_tiles tile columns of bal_units (+1 for the first
     // bal_wide) sixteen-column units instead of ceil(N / bn) equal ones. bal_tiles == 0: equal tiles.
     int bal_tiles, bal_units, bal_wide;
@@ -398,8 +398,6 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
         best.splits = 1;
         best.kb_per_split = kb_total;
     }
-    // Small M with the narrow tile: load only the rows of A that exist, which leaves room for up to 16 stages so
-    // that a short K is wholly in flight at once.
     // Fewer equal tiles than SMs (skinny M: 16 x 7168 x 2048 has 112 tiles of 64 columns for 148 SMs): deal the
     // sixteen-column units of N out over as many tile columns as there are SMs per tile row, so that every SM pulls
     // the same share of B. Off unless QGEMM_BALANCE=1: measured on B200 (FP8, N = 7168, K = 2048, graph replay over
@@ -425,8 +423,20 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
             }
         }
     }
+    // Rows of A loaded per stage. The lone-CTA kernels load only the rows that exist, rounded up to 16 / 32 / 64 (the
+    // MMA still reads 128 rows; what lies behind the loaded ones only reaches accumulator rows that are never stored):
+    // the stages get smaller, so more of them fit and more bytes are in flight, and, what weighs more, the TMA unit
+    // does not zero-fill rows beyond M -- with 16 rows or fewer in a 128-row box that fill, not the memory system, sets
+    // the pace. Measured on B200 (graph replay over cold operands, us; full box / existing rows): 128-wide tiles FP8
+    // 16 x 11008 x 4096 18.0 / 11.2, 1 x 11008 x 4096 18.9 / 11.1, 32 rows 11.7 / 11.2; 256-wide tiles BF16 1 x 28672 x
+    // 8192 117.2 / 76.5, 8 x 28672 x 4096 54.5 / 38.7, FP8 1 x 32768 x 8192 54.0 / 43.5, 24 x 28672 x 4096 28.3 / 21.1,
+    // BF16 32 x 11008 x 8192 (three K slices) 35.4 / 33.7. With 256-wide tiles 64 rows leave the stage count at four, so
+    // that form keeps the full box there. The in-cluster split-K kernel on 128-wide tiles always loads 128 rows.
     best.am = kBM;
-    if (!best.pair && best.bn == 64 && g_env.full_a_tile == 0) best.am = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : kBM));
+    if (!best.pair && g_env.full_a_tile == 0) {
+        if (best.bn == 64 || (best.bn == 128 && best.kcluster == 0)) best.am = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : kBM));
+        else if (best.bn == 256) best.am = M <= 16 ? 16 : (M <= 32 ? 32 : kBM);
+    }
     // Tile rows per scheduling group: as many as keep the group's A panel (rows x K bytes) near 32 MiB, so that
     // it stays in L2 while the B panels stream past it.
     // 512 x 256 tiles per CTA pair instead of 256 x 256: a quarter fewer operand bytes from L2 per flop (clock, on a

@@ -64,7 +64,7 @@ cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     return launch_pdl(kernel, dim3(grid), dim3(kGemmThreads), smem, stream, ta, tb, tc, p);
 }
 
-// `am` = rows of A loaded per stage: 128, or 64 / 32 / 16 with the 64-wide tile for small M. `one` (128-wide tiles, one
+// `am` = rows of A loaded per stage: 128, or 64 / 32 / 16 for small M (64- and 128-wide tiles; 32 / 16 with 256-wide ones). `one` (128-wide tiles, one
 // tile per CTA): the layout with a seventh stage.
 template <int KIND>
 cudaError_t launch_kind(int bn, int out, int am, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
@@ -86,7 +86,12 @@ cudaError_t launch_kind(int bn, int out, int am, const CUtensorMap& ta, const CU
     QGEMM_CASE(BN_, OUT_F16, AM_)   \
     QGEMM_CASE(BN_, OUT_RAW32, AM_)
     QGEMM_CASES(256, 128)
+    QGEMM_CASES(256, 32)
+    QGEMM_CASES(256, 16)
     QGEMM_CASES(128, 128)
+    QGEMM_CASES(128, 64)
+    QGEMM_CASES(128, 32)
+    QGEMM_CASES(128, 16)
     QGEMM_CASES(64, 128)
     QGEMM_CASES(64, 64)
     QGEMM_CASES(64, 32)
