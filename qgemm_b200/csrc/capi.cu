@@ -364,12 +364,16 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
                 best.kcluster = 0;
             }
             // The same slices inside one launch: 2, 4 or 8 non-empty slices of 64- or 128-wide tiles, as many clusters as the
-            // device runs at once (one wave), K-major B, no CTA cap, balanced tiling not switched on; the 128-wide
-            // tile (which always loads 128 rows of A) only when M has more than 64 rows or the caller asked for it. Measured on B200 against the two-launch form at
+            // device runs at once (one wave), K-major B, no CTA cap, balanced tiling not switched on. With 64 rows or fewer
+            // the 128-wide tile only in four or eight slices (or when the caller asks for it): against 64-wide tiles in half as
+            // many slices, the same number of CTAs each pull a quarter fewer bytes (A is shared by twice the columns). Measured
+            // over 240 skinny shapes (time of the 128-wide form / the 64-wide one, median): 4 against 2 slices 0.94, 8 against 4
+            // 0.91 (BF16) and 0.94 (FP8), with FP8 16 x 3072 x 16384 15.1 -> 12.6 us; 2 slices against one wave of unsplit
+            // 64-wide tiles 0.98-0.99 with a spread of +-10 %, so that form is left out. Measured on B200 against the two-launch form at
             // the same split (graph replay over cold operands, us): FP8 32 x 2048 x 8192 7.5 / 8.7, 128 x 2048 x 16384
             // 11.6 / 12.9, 128 x 1024 x 4096 6.1 / 6.9; BF16 32 x 2048 x 8192 10.1 / 11.7, 256 x 1024 x 8192 10.9 / 12.4.
             // CTA pairs on 256 x 128 tiles likewise (gemm_sm100_2cta_kcluster.cuh): 2 or 4 pairs per cluster.
-            const bool lone_ok = !c.pair && (c.bn == 64 || (c.bn == 128 && (M > 64 || want_bn == 128))) &&
+            const bool lone_ok = !c.pair && (c.bn == 64 || (c.bn == 128 && (M > 64 || want_bn == 128 || s >= 4))) &&
                                  (s == 2 || s == 4 || s == 8);
             const bool pair_ok = c.pair && c.bn == 128 && (s == 2 || s == 4) && g_env.kcluster_pair_off == 0;
             if (allow_kcluster && g_env.kcluster_off == 0 && g_env.balance == 0 && (lone_ok || pair_ok) &&
@@ -431,10 +435,10 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
     // 16 x 11008 x 4096 18.0 / 11.2, 1 x 11008 x 4096 18.9 / 11.1, 32 rows 11.7 / 11.2; 256-wide tiles BF16 1 x 28672 x
     // 8192 117.2 / 76.5, 8 x 28672 x 4096 54.5 / 38.7, FP8 1 x 32768 x 8192 54.0 / 43.5, 24 x 28672 x 4096 28.3 / 21.1,
     // BF16 32 x 11008 x 8192 (three K slices) 35.4 / 33.7. With 256-wide tiles 64 rows leave the stage count at four, so
-    // that form keeps the full box there. The in-cluster split-K kernel on 128-wide tiles always loads 128 rows.
+    // that form keeps the full box there.
     best.am = kBM;
     if (!best.pair && g_env.full_a_tile == 0) {
-        if (best.bn == 64 || (best.bn == 128 && best.kcluster == 0)) best.am = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : kBM));
+        if (best.bn == 64 || best.bn == 128) best.am = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : kBM));
         else if (best.bn == 256) best.am = M <= 16 ? 16 : (M <= 32 ? 32 : kBM);
     }
     // Tile rows per scheduling group: as many as keep the group's A panel (rows x K bytes) near 32 MiB, so that

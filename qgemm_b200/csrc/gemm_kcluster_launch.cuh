@@ -42,7 +42,7 @@ cudaError_t launch_kcluster_one(const CUtensorMap& ta, const CUtensorMap& tb, co
     return cudaLaunchKernelEx(&cfg, kernel, ta, tb, p);
 }
 
-// `bn` = tile width (64 or 128), `am` = rows of A loaded per stage (128, or 64 / 32 / 16 with the 64-wide tile),
+// `bn` = tile width (64 or 128), `am` = rows of A loaded per stage (128, or 64 / 32 / 16 for small M),
 // `slices` = CTAs per cluster = K slices (2, 4 or 8).
 template <int KIND>
 cudaError_t launch_kcluster_kind(int bn, int out, int am, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
@@ -58,6 +58,15 @@ cudaError_t launch_kcluster_kind(int bn, int out, int am, int slices, const CUte
     QGEMM_KC_CASES(128, 128, 2)
     QGEMM_KC_CASES(128, 128, 4)
     QGEMM_KC_CASES(128, 128, 8)
+    QGEMM_KC_CASES(128, 64, 2)
+    QGEMM_KC_CASES(128, 64, 4)
+    QGEMM_KC_CASES(128, 64, 8)
+    QGEMM_KC_CASES(128, 32, 2)
+    QGEMM_KC_CASES(128, 32, 4)
+    QGEMM_KC_CASES(128, 32, 8)
+    QGEMM_KC_CASES(128, 16, 2)
+    QGEMM_KC_CASES(128, 16, 4)
+    QGEMM_KC_CASES(128, 16, 8)
     QGEMM_KC_CASES(64, 128, 2)
     QGEMM_KC_CASES(64, 128, 4)
     QGEMM_KC_CASES(64, 128, 8)

@@ -128,8 +128,9 @@ def test_plan_in_cluster_split_k(qlib):
     for dt in (q.FP8_E4M3, q.BF16, q.INT8):
         deep = q.plan_query(dt, q.BF16, q.B_K_MAJOR, 32, 2048, 8192)  # 32 tiles: four slices = 128 CTAs
         assert (deep["tile_n"], deep["split_k"], deep["cluster_slices"], deep["ctas"]) == (64, 4, 4, 128), deep
-        two = q.plan_query(dt, q.BF16, q.B_K_MAJOR, 32, 4096, 4096)  # 64 tiles: two slices
-        assert (two["split_k"], two["cluster_slices"]) == (2, 2), two
+        # 64 tiles of 64 columns in two slices, or (taken: fewer bytes per CTA) 32 tiles of 128 columns in four
+        four = q.plan_query(dt, q.BF16, q.B_K_MAJOR, 32, 4096, 4096)
+        assert (four["tile_n"], four["split_k"], four["cluster_slices"], four["a_rows_per_stage"], four["ctas"]) == (128, 4, 4, 32, 128), four
         eight = q.plan_query(dt, q.BF16, q.B_K_MAJOR, 64, 512, 16384)  # 8 tiles: eight slices
         assert (eight["split_k"], eight["cluster_slices"]) == (8, 8), eight
     # more tiles than half the SMs, or a short K: no slices

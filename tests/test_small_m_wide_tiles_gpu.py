@@ -2,7 +2,7 @@
 256-wide tile) while the MMA still reads 128 rows; whatever lies behind the loaded rows must reach no stored element.
 Same K order as every other tiling, so int8 must agree bit for bit with the oracle and with the full-box form of the
 same tile (QGEMM_FULL_A_TILE=1); floating-point kinds are checked at their tier. Shapes cover every row class, ragged
-N and K, several tiles per CTA (persistent loop), K slices in two launches, and row-major B."""
+N and K, several tiles per CTA (persistent loop), K slices in two launches and inside one cluster, and row-major B."""
 import os
 
 import numpy as np
@@ -83,6 +83,57 @@ def test_float_kinds(qlib, oracle, dev, M, N, K, bn, kind):
             assert oracle.max_rel(got, ref) <= 1e-2  # fp8 tier: max relative error with an rms floor
         else:
             assert oracle.rel_l2(got, ref) <= (1e-3 if dt == torch.float32 else 4e-3)  # 16-bit tier
+    rc, st = q.device_status()
+    assert rc == 0, st
+
+
+# K a multiple of 8 x 128 bytes, so that 2, 4 and 8 slices are all non-empty and equal
+CLUSTER_SHAPES = [(1, 384, 2048), (16, 1000, 2048), (17, 640, 4096), (33, 520, 2048), (64, 203, 3072)]
+
+
+@pytest.mark.parametrize("slices", [2, 4, 8])
+@pytest.mark.parametrize("M,N,K", CLUSTER_SHAPES)
+def test_in_cluster_split_k_on_128_wide_tiles(qlib, oracle, dev, M, N, K, slices):
+    """The K slices of a 128-wide tile on the CTAs of one cluster, 16 / 32 / 64 rows of A per stage: int8 bit for bit
+    against the oracle and against the two-launch split at the same slice count; BF16 and FP8 at their tiers."""
+    q = qlib
+    tun = q.Tuning(128, slices, 0, 0, -1, 0)
+    plan = q.plan_query(q.INT8, q.INT32, q.B_K_MAJOR, M, N, K, tun)
+    assert (plan["tile_n"], plan["split_k"], plan["cluster_slices"], plan["a_rows_per_stage"]) == (128, slices, slices, _rows(M, 128)), plan
+    ai = datagen.int8_uniform((M, K), seed=M + N, stream=0)
+    bi = datagen.int8_uniform((N, K), seed=M + N, stream=1)
+    a, b = torch.from_numpy(ai).to(dev), torch.from_numpy(bi).to(dev)
+    acc = torch.full((M, N), -7, dtype=torch.int32, device=dev)
+    q.gemm(a, b, acc, b_kmajor=True, tuning=tun)
+    ref = oracle.gemm_i8(ai, bi, True)
+    assert np.array_equal(acc.cpu().numpy(), ref)
+    sa, sb = datagen.scale_pair(5)
+    tsa, tsb = torch.tensor([sa], device=dev), torch.tensor([sb], device=dev)
+    c = torch.zeros((M, N), dtype=torch.bfloat16, device=dev)
+    q.mix_gemm(a, b, tsa, tsb, c, b_kmajor=True, tuning=tun)
+    os.environ["QGEMM_KCLUSTER"] = "0"
+    try:
+        q.lib().qgemm_reload_env()
+        assert q.plan_query(q.INT8, q.INT32, q.B_K_MAJOR, M, N, K, tun)["cluster_slices"] == 0
+        c2 = torch.zeros((M, N), dtype=torch.bfloat16, device=dev)
+        q.mix_gemm(a, b, tsa, tsb, c2, b_kmajor=True, tuning=tun)
+    finally:
+        del os.environ["QGEMM_KCLUSTER"]
+        q.lib().qgemm_reload_env()
+    assert torch.equal(c.view(torch.int16), c2.view(torch.int16))  # same sums in the same order, same scale and cast
+    bits = c.view(torch.int16).cpu().numpy().view(np.uint16)
+    assert oracle.bf16_ulp_distance(bits, oracle.scale_cast(ref, float(sa), float(sb), oracle.OUT_BF16)) <= 1
+    for kind, tdt in (("bf16", torch.bfloat16), ("fp8", torch.float8_e4m3fn)):
+        a32, b32 = datagen.normal((M, K), M + K, 0), datagen.normal((N, K), M + K, 1)
+        fa, fb = torch.from_numpy(a32).to(tdt), torch.from_numpy(b32).to(tdt)
+        fref = oracle.gemm_f32(fa.float().numpy(), fb.float().numpy(), True)
+        out = torch.full((M, N), -3, dtype=torch.float32, device=dev)
+        q.gemm(fa.to(dev), fb.to(dev), out, b_kmajor=True, tuning=tun)
+        got = out.cpu().numpy()
+        if kind == "fp8":
+            assert oracle.max_rel(got, fref) <= 1e-2  # fp8 tier
+        else:
+            assert oracle.rel_l2(got, fref) <= 1e-3  # 16-bit tier, fp32 out
     rc, st = q.device_status()
     assert rc == 0, st
 
