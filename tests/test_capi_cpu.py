@@ -120,7 +120,7 @@ def test_plan_query_ex_and_environment_reload(qlib):
 
 
 def test_plan_in_cluster_split_k(qlib):
-    """Few 64-wide tiles and a long K: the planner cuts K into 2, 4 or 8 slices that the CTAs of one cluster add up
+    """Few 64- or 128-wide tiles and a long K: the planner cuts K into 2, 4 or 8 slices that the CTAs of one cluster add up
     inside one launch (cluster_slices), as many as still fit the device in one wave. Without a device the number of
     clusters that run at once is taken as seven eighths of SMs / slices."""
     import os
