@@ -256,14 +256,15 @@ int g_test_skip_kb = -1;
 constexpr double kPairTimePerKb = 0.93;
 constexpr double kPair128TimePerKb = 0.45;  // 256 x 128 pair tiles against 0.56 for a lone 128 x 128 tile
 constexpr double kTailOverhead = 16.0;
-bool tail_split(long long tiles, int clusters, int kb_total, int* tail_tiles, int* slices, int* kb_per_slice) {
+bool tail_split(long long tiles, int clusters, int kb_total, int* tail_tiles, int* slices, int* kb_per_slice,
+                double t_kb = kPairTimePerKb) {
     if (clusters <= 0 || tiles <= clusters) return false;
     const int r = static_cast<int>(tiles % clusters);
     if (r == 0 || 4 * r > clusters) return false;
     const int want = std::min(clusters / r, std::min(kb_total / 4, 16));  // at least 4 K blocks per slice
     if (want < 2) return false;
     const int kbps = (kb_total + want - 1) / want;
-    if ((kb_total - kbps) * kPairTimePerKb <= kTailOverhead) return false;
+    if ((kb_total - kbps) * t_kb <= kTailOverhead) return false;
     *tail_tiles = r;
     *kb_per_slice = kbps;
     *slices = (kb_total + kbps - 1) / kbps;
@@ -295,7 +296,7 @@ double estimate(int bn, bool pair, int splits, size_t M, size_t N, int kb_total,
     else { t_kb = 0.33; fill = 4.0; }
     double t = static_cast<double>(waves) * (kbps * t_kb + fill);
     int tt = 0, ts = 0, tk = 0;
-    if (pair && bn == kPairTileN && real_splits == 1 && allow_tail && tail_split(units, slots, kb_total, &tt, &ts, &tk))
+    if (pair && real_splits == 1 && allow_tail && tail_split(units, slots, kb_total, &tt, &ts, &tk, t_kb))
         t = static_cast<double>(waves - 1) * (kbps * t_kb + fill) + (tk * t_kb + fill) + kTailOverhead;
     if (real_splits > 1 && in_cluster) {
         // full 128-row tiles have four times the partial sums of a 32-row problem to put through shared memory
@@ -339,12 +340,21 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
         // the caller asks for them) only when all tiles run in one wave -- that is where they were measured against one
         // wave of lone 128 x 128 tiles (us, graph replay over cold operands): BF16 1024 x 2048 x 8192 31.5 / 35.5, 2048 x
         // 1024 x 4096 16.8 / 17.8, 1280 x 1280 x 4096 15.8 / 17.9; FP8 1024 x 2048 x 8192 17.4 / 18.3, 1536 x 1536 x 6144
-        // 14.5 / 15.0; over several waves the 256 x 256 pairs win (FP8 4096^3 56.0 against 67.2).
+        // 14.5 / 15.0; over several waves the 256 x 256 pairs win (FP8 4096^3 56.0 against 67.2). One wave and a short
+        // last one whose tiles are cut into K slices (tail_split) counts as one wave: such a problem has about 40 tiles of
+        // 256 x 256, which leave half the SMs idle. Measured (BF16, planner before / with this form, us): 768 x 3328 x 8192
+        // 45.7 / 37.6, 512 x 4864 x 8192 45.1 / 37.8, 1280 x 2048 x 8192 45.8 / 39.3, 1024 x 2560 x 4096 28.0 / 23.9,
+        // 512 x 5120 x 5120 30.5 / 28.1, but 256 x 10240 x 4096 26.4 / 28.5; FP8 768 x 3328 x 8192 25.7 / 23.4, 512 x 4864 x
+        // 8192 25.4 / 22.9, 1280 x 2048 x 8192 25.6 / 24.6 (with 148 CTAs on 24 KB per K block the L2-to-SM traffic, not the
+        // tensor pipe, sets the pace, so the gain is far from the factor the idle SMs suggest).
         if (c.pair && c.bn == 128) {
             if (!allow_pair128 || want_pair == 2) continue;
             const long long tiles128 = static_cast<long long>((M + kPairTileM - 1) / kPairTileM) *
                                        static_cast<long long>((N + 127) / 128);
-            if (!(want_pair > 0 && want_bn == 128) && tiles128 > sms / 2) continue;
+            int tt = 0, ts = 0, tk = 0;
+            const bool tail_fits = allow_tail && !want_split && tiles128 > sms / 2 && tiles128 < sms &&
+                                   tail_split(tiles128, sms / 2, kb_total, &tt, &ts, &tk, kPair128TimePerKb);
+            if (!(want_pair > 0 && want_bn == 128) && tiles128 > sms / 2 && !tail_fits) continue;
         }
         if (!c.pair && want_pair > 0) continue;
         if (want_bn && c.bn != want_bn) continue;
@@ -548,11 +558,12 @@ int make_plan(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, siz
     p->partial_bytes = (p->cfg.splits > 1 && p->cfg.kcluster == 0) ? static_cast<size_t>(p->cfg.splits) * M * p->ldw * 4 : 0;
     p->tail_tiles = p->tail_slices = p->tail_kb_per_slice = 0;
     p->kgroup = choose_kgroup(p->cfg, b_direct, K, p->ti.elem_bytes);
-    if (allow_tail && p->cfg.pair && p->cfg.bn == kPairTileN && !p->cfg.wide && p->cfg.splits == 1) {
+    if (allow_tail && p->cfg.pair && !p->cfg.wide && p->cfg.splits == 1) {
         const long long tiles = static_cast<long long>((M + kPairTileM - 1) / kPairTileM) *
-                                static_cast<long long>((N + kPairTileN - 1) / kPairTileN);
-        if (tail_split(tiles, sms / 2, p->kb_total, &p->tail_tiles, &p->tail_slices, &p->tail_kb_per_slice))
-            p->partial_bytes = static_cast<size_t>(p->tail_slices) * p->tail_tiles * kPairTileM * kPairTileN * 4;
+                                static_cast<long long>((N + p->cfg.bn - 1) / p->cfg.bn);
+        if (tail_split(tiles, sms / 2, p->kb_total, &p->tail_tiles, &p->tail_slices, &p->tail_kb_per_slice,
+                       p->cfg.bn == kPairTileN ? kPairTimePerKb : kPair128TimePerKb))
+            p->partial_bytes = static_cast<size_t>(p->tail_slices) * p->tail_tiles * kPairTileM * p->cfg.bn * 4;
         else
             p->tail_tiles = 0;
     }
@@ -767,8 +778,8 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
             p.tail_slices = plan.tail_slices;
             p.tail_kb_per_slice = plan.tail_kb_per_slice;
             p.total_work = p.tail_begin + plan.tail_tiles * plan.tail_slices;
-            rc = make_output_map(partials, static_cast<uint64_t>(plan.tail_tiles) * kPairTileM, kPairTileN, kPairTileN,
-                                 static_cast<uint64_t>(plan.tail_slices), OUT_RAW32, &tws);
+            rc = make_output_map(partials, static_cast<uint64_t>(plan.tail_tiles) * kPairTileM, static_cast<uint64_t>(cfg.bn),
+                                 static_cast<uint64_t>(cfg.bn), static_cast<uint64_t>(plan.tail_slices), OUT_RAW32, &tws);
             if (rc != QGEMM_OK) return rc;
         }
         int clusters = static_cast<int>(std::min<long long>(p.total_work, st->sm_count / 2));
@@ -799,7 +810,7 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
         tiles.tile_offset = p.tail_begin;
         rc = splitk_reduce_tiles_launch(partials, plan.tail_tiles, plan.tail_slices, plan.ti.acc_int, C,
                                         static_cast<long long>(ldc), p.M, p.N, plan.out_kind, scale_a, scale_b, tiles,
-                                        stream);
+                                        cfg.bn, stream);
         if (rc != QGEMM_OK) return rc;
     }
 

@@ -276,11 +276,11 @@ cudaError_t launch_fp8_blockscale(int out_kind, const CUtensorMap& ta, const CUt
                                   const BlockScaleParams& p, int grid, cudaStream_t stream);
 
 // Adds up the K slices of the last-wave tiles (splitk_reduce.cu): `slots` tiles stored as
-// [splits][slots * 256][256] 32-bit partial sums; `tiles` locates slot i in C (m_tiles, n_tiles, group_m,
-// tile_offset; splits = 1).
+// [splits][slots * 256][tile_n] 32-bit partial sums (tile_n = 256 or 128, the pair kernel's tile width); `tiles`
+// locates slot i in C (m_tiles, n_tiles, group_m, tile_offset; splits = 1).
 int splitk_reduce_tiles_launch(const void* partials, int slots, int splits, bool acc_is_int, void* C, long long ldc,
                                int M, int N, int out_kind, const float* scale_a, const float* scale_b,
-                               const GemmParams& tiles, cudaStream_t stream);
+                               const GemmParams& tiles, int tile_n, cudaStream_t stream);
 
 // In-cluster split-K (gemm_sm100_kcluster.cuh; gemm_kc_*.cu): `tiles` clusters of `slices` CTAs, 64- or 128-wide tiles.
 cudaError_t launch_gemm_kcluster_f16(int bn, int out, int am, int slices, const CUtensorMap& ta, const CUtensorMap& tb,

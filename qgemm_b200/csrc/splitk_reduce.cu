@@ -112,26 +112,27 @@ splitk_reduce_kernel(const uint32_t* __restrict__ partials, long long split_stri
                              scale_b, c_vec_ok);
 }
 
-// The same sum for tiles whose K slices were stored as compact 256 x 256 slots ([splits][slots * 256][256]):
-// blockIdx.y = slot; the tile's place in C comes from the GEMM's own tile order (`tiles` carries m_tiles, n_tiles,
-// group_m and tile_offset, with splits = 1).
+// The same sum for tiles whose K slices were stored as compact 256 x tile_n slots ([splits][slots * 256][tile_n],
+// tile_n = 256 or 128): blockIdx.y = slot; the tile's place in C comes from the GEMM's own tile order (`tiles`
+// carries m_tiles, n_tiles, group_m and tile_offset, with splits = 1).
 template <bool ACC_INT>
 __global__ void __launch_bounds__(256)
 splitk_reduce_tiles_kernel(const uint32_t* __restrict__ partials, long long split_stride, int splits,
                            void* __restrict__ C, long long ldc, int M, int N, int out_kind,
                            const float* __restrict__ scale_a, const float* __restrict__ scale_b, int c_vec_ok,
-                           const GemmParams tiles) {
+                           const GemmParams tiles, int tile_n) {
     ptx::pdl_launch_dependents();
     ptx::pdl_wait();
     const int slot = static_cast<int>(blockIdx.y);
     const TileCoord t = decode_tile(slot, tiles);
-    const int idx = static_cast<int>(blockIdx.x) * 256 + static_cast<int>(threadIdx.x);  // 256 rows x 64 quads
-    const int r = idx >> 6;
-    const int c = (idx & 63) * 4;
+    const int idx = static_cast<int>(blockIdx.x) * 256 + static_cast<int>(threadIdx.x);  // 256 rows x tile_n / 4 quads
+    const int quad_shift = tile_n == 256 ? 6 : 5;
+    const int r = idx >> quad_shift;
+    const int c = (idx & ((1 << quad_shift) - 1)) * 4;
     const long long row = static_cast<long long>(t.m_blk) * kPairTileM + r;
-    const int col = t.n_blk * kPairTileN + c;
+    const int col = t.n_blk * tile_n + c;
     if (r >= kPairTileM || row >= M || col >= N) return;
-    const uint32_t* src = partials + (static_cast<long long>(slot) * kPairTileM + r) * kPairTileN + c;
+    const uint32_t* src = partials + (static_cast<long long>(slot) * kPairTileM + r) * tile_n + c;
     reduce_quad<ACC_INT>(src, split_stride, splits, C, ldc, row, col, N, out_kind, scale_a, scale_b, c_vec_ok);
 }
 
@@ -139,20 +140,21 @@ splitk_reduce_tiles_kernel(const uint32_t* __restrict__ partials, long long spli
 
 int splitk_reduce_tiles_launch(const void* partials, int slots, int splits, bool acc_is_int, void* C, long long ldc,
                                int M, int N, int out_kind, const float* scale_a, const float* scale_b,
-                               const GemmParams& tiles, cudaStream_t stream) {
+                               const GemmParams& tiles, int tile_n, cudaStream_t stream) {
     if (slots <= 0) return QGEMM_OK;
+    if (tile_n != 256 && tile_n != 128) return QGEMM_ERR_INVALID_ARG;
     const int out_bytes = (out_kind == OUT_BF16 || out_kind == OUT_F16) ? 2 : 4;
     const int c_vec_ok = (reinterpret_cast<uintptr_t>(C) % 16 == 0) && ((ldc * out_bytes) % 16 == 0);
-    const long long split_stride = static_cast<long long>(slots) * kPairTileM * kPairTileN;
+    const long long split_stride = static_cast<long long>(slots) * kPairTileM * tile_n;
     const uint32_t* p = reinterpret_cast<const uint32_t*>(partials);
-    const dim3 grid(kPairTileM * (kPairTileN / 4) / 256, static_cast<unsigned>(slots));
+    const dim3 grid(kPairTileM * (tile_n / 4) / 256, static_cast<unsigned>(slots));
     cudaError_t e;
     if (acc_is_int)
         e = launch_pdl(splitk_reduce_tiles_kernel<true>, grid, dim3(256), 0, stream, p, split_stride, splits, C, ldc, M,
-                       N, out_kind, scale_a, scale_b, c_vec_ok, tiles);
+                       N, out_kind, scale_a, scale_b, c_vec_ok, tiles, tile_n);
     else
         e = launch_pdl(splitk_reduce_tiles_kernel<false>, grid, dim3(256), 0, stream, p, split_stride, splits, C, ldc,
-                       M, N, out_kind, scale_a, scale_b, c_vec_ok, tiles);
+                       M, N, out_kind, scale_a, scale_b, c_vec_ok, tiles, tile_n);
     return e == cudaSuccess ? QGEMM_OK : QGEMM_ERR_CUDA;
 }
 

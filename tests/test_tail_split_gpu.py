@@ -1,4 +1,4 @@
-"""The last-wave split of the CTA-pair kernel: when the number of 256 x 256 tiles leaves a short last wave, those
+"""The last-wave split of the CTA-pair kernel: when the number of 256 x 256 (or 256 x 128) tiles leaves a short last wave, those
 tiles' K ranges are cut into slices over all clusters (a second launch writing 32-bit partial sums into scratch
 slots) and added up by a small third kernel. Shapes here are chosen so that it triggers on a 148-SM part (74
 clusters): 10 x 8 = 80 tiles -> 6 tiles in the last wave, and K deep enough for the saving to beat the extra launch. Parity tiers as for the ordinary path: int8 exact,
@@ -124,4 +124,74 @@ def test_unaligned_c_falls_back_to_the_unsplit_kernel(qlib, oracle, dev):
     got = acc.cpu().numpy()
     for m0, m1 in ((0, 8), (M - 8, M)):
         assert np.array_equal(got[m0:m1], oracle.gemm_i8_rows(ai, bi, m0, m1))
+    _status_ok(q)
+
+
+# ---- the same split with 256 x 128 pair tiles (80 tiles on 74 clusters: six tiles in the last wave)
+
+def _narrow(q):
+    return q.Tuning(128, 0, 0, 0, 1, 0)
+
+
+def _narrow_no_split(q):
+    return q.Tuning(128, 1, 0, 0, 1, 0)
+
+
+@pytest.mark.parametrize("M,N,K", [(1280, 2048, 8192), (1250, 2000, 8208), (512, 5120, 12288)])
+def test_int8_exact_with_last_wave_split_of_narrow_pair_tiles(qlib, oracle, dev, M, N, K):
+    q = qlib
+    plan = q.plan_query(q.INT8, q.INT32, q.B_K_MAJOR, M, N, K, _narrow(q))
+    assert (plan["tile_m"], plan["tile_n"], plan["ctas_per_tile"], plan["tail_tiles"]) == (256, 128, 2, 6), plan
+    assert plan["tail_slices"] >= 2
+    need = q.workspace_query(q.INT8, q.B_K_MAJOR, M, N, K, _narrow(q))
+    assert need == plan["tail_slices"] * 6 * 256 * 128 * 4
+    assert q.workspace_query(q.INT8, q.B_K_MAJOR, M, N, K, _narrow_no_split(q)) == 0
+    ai = datagen.int8_uniform((M, K), seed=K, stream=0)
+    bi = datagen.int8_uniform((N, K), seed=K, stream=1)
+    a, b = torch.from_numpy(ai).to(dev), torch.from_numpy(bi).to(dev)
+    acc = torch.full((M, N), -1, dtype=torch.int32, device=dev)
+    ref = torch.full((M, N), -2, dtype=torch.int32, device=dev)
+    q.gemm(a, b, acc, b_kmajor=True, tuning=_narrow(q))
+    q.gemm(a, b, ref, b_kmajor=True, tuning=_narrow_no_split(q))
+    _status_ok(q)
+    assert torch.equal(acc, ref), "the split and the unsplit kernel must agree exactly"
+    got = acc.cpu().numpy()
+    for m0, m1 in ((0, 8), (M // 2, M // 2 + 8), (M - 8, M)):
+        assert np.array_equal(got[m0:m1], oracle.gemm_i8_rows(ai, bi, m0, m1))
+    sa, sb = torch.tensor([0.013], device=dev), torch.tensor([0.009], device=dev)
+    c1 = torch.zeros((M, N), dtype=torch.bfloat16, device=dev)
+    c2 = torch.zeros((M, N), dtype=torch.bfloat16, device=dev)
+    q.mix_gemm(a, b, sa, sb, c1, b_kmajor=True, tuning=_narrow(q))
+    q.mix_gemm(a, b, sa, sb, c2, b_kmajor=True, tuning=_narrow_no_split(q))
+    assert torch.equal(c1.view(torch.int16), c2.view(torch.int16))
+    _status_ok(q)
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp8"])
+def test_float_kinds_with_last_wave_split_of_narrow_pair_tiles(qlib, oracle, dev, kind):
+    q = qlib
+    M, N, K = 512, 5120, 5120 if kind == "bf16" else 8192
+    dt = q.BF16 if kind == "bf16" else q.FP8_E4M3
+    # the planner's own choice for this shape: 80 tiles of 256 x 128, the last six in K slices
+    plan = q.plan_query(dt, q.BF16, q.B_K_MAJOR, M, N, K)
+    assert (plan["tile_m"], plan["tile_n"], plan["ctas_per_tile"], plan["tail_tiles"]) == (256, 128, 2, 6), plan
+    a32, b32 = datagen.normal((M, K), 5, 0), datagen.normal((N, K), 5, 1)
+    tdt = torch.bfloat16 if kind == "bf16" else torch.float8_e4m3fn
+    a, b = torch.from_numpy(a32).to(tdt), torch.from_numpy(b32).to(tdt)
+    ref = oracle.gemm_f32(a.float().numpy(), b.float().numpy(), True)
+    a, b = a.to(dev), b.to(dev)
+    for out in (torch.float32, torch.bfloat16):
+        c = torch.full((M, N), float("nan"), dtype=out, device=dev)
+        q.gemm(a, b, c, b_kmajor=True)
+        got = c.float().cpu().numpy()
+        assert np.isfinite(got).all()
+        if kind == "fp8":
+            assert oracle.max_rel(got, ref) <= 1e-2  # fp8 tier
+        else:
+            assert oracle.rel_l2(got, ref) <= (1e-3 if out == torch.float32 else 4e-3)  # 16-bit tier
+        c0 = torch.empty_like(c)
+        q.gemm(a, b, c0, b_kmajor=True, tuning=_narrow_no_split(q))
+        view = torch.int32 if out == torch.float32 else torch.int16
+        changed = int((c.view(view) != c0.view(view)).any(dim=1).sum().item())
+        assert changed <= 6 * 256, "only rows of the six last-wave tiles may differ"
     _status_ok(q)
