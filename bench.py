@@ -75,6 +75,13 @@ WORKLOADS = {
     "d1_fp8_deep": ("fp8", "bf16", 128, 2048, 16384, True,
                     "FP8 e4m3 M=128 N=2048 K=16384 (few tiles, long K: split-K inside one launch), bf16 out"),
     "d2_bf16_deep": ("bf16", "bf16", 32, 2048, 8192, True, "BF16 M=32 N=2048 K=8192 (few tiles, long K), bf16 out"),
+    "s1_fp8_skinny_wide": ("fp8", "bf16", 16, 11008, 4096, True,
+                           "FP8 e4m3 M=16 N=11008 K=4096 (too wide for one wave of 64-wide tiles: 128-wide tiles on 16 "
+                           "rows of A per stage), bf16 out"),
+    "s2_bf16_skinny_wide": ("bf16", "bf16", 8, 28672, 4096, True,
+                            "BF16 M=8 N=28672 K=4096 (256-wide tiles on 16 rows of A per stage), bf16 out"),
+    "t1_bf16_tail": ("bf16", "bf16", 768, 3328, 8192, True,
+                     "BF16 M=768 N=3328 K=8192 (78 tiles of 256 x 128 on 74 CTA pairs: last-wave split), bf16 out"),
     "m1_bf16_mid": ("bf16", "bf16", 1024, 2048, 8192, True,
                     "BF16 M=1024 N=2048 K=8192 (one wave of mid-size tiles: 256 x 128 tiles on CTA pairs), bf16 out"),
     "m2_bf16_mid_deep": ("bf16", "bf16", 1024, 1024, 8192, True,
@@ -84,7 +91,8 @@ WORKLOADS = {
                         "int8 mixed GEMM 32768x32768x8192, B/C column-sharded over the ranks (strong scaling)"),
 }
 CONFIG_BLOCK = ["c1_fp16_1024", "c3_int8_8192", "c3_fp8_8192", "c4_fp8_16", "c4_fp8_64", "c4_fp8_256", "c4_fp8_1024",
-                "c4_fp8_6144", "d1_fp8_deep", "d2_bf16_deep", "m1_bf16_mid", "m2_bf16_mid_deep", "f1_fp8_blockscale"]
+                "c4_fp8_6144", "d1_fp8_deep", "d2_bf16_deep", "s1_fp8_skinny_wide", "s2_bf16_skinny_wide", "t1_bf16_tail", "m1_bf16_mid",
+                "m2_bf16_mid_deep", "f1_fp8_blockscale"]
 
 
 _REAL_STDOUT = None
@@ -961,7 +969,7 @@ def run_config(ctx, args, name):
     out = {"description": WORKLOADS[name][6], "shape": [ops["M"], ops["N"], ops["K"]], "us": best * 1e3,
            "tflops": roof.get("tflops", roof["achieved"]), "roofline": roof, "sm_mhz": mhz, "steps": steps,
            "timed_loop": ("CUDA graph replay over %d rotating operand sets" % nsets) if use_graph else "direct launches"}
-    if name.startswith(("c4_", "d1_", "d2_", "m1_", "m2_")) or name == "c3_fp8_8192":
+    if name.startswith(("c4_", "d1_", "d2_", "m1_", "m2_", "s1_", "s2_", "t1_")) or name == "c3_fp8_8192":
         try:
             lcnt = [0]
 
