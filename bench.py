@@ -969,9 +969,13 @@ def run_config(ctx, args, name):
     out = {"description": WORKLOADS[name][6], "shape": [ops["M"], ops["N"], ops["K"]], "us": best * 1e3,
            "tflops": roof.get("tflops", roof["achieved"]), "roofline": roof, "sm_mhz": mhz, "steps": steps,
            "timed_loop": ("CUDA graph replay over %d rotating operand sets" % nsets) if use_graph else "direct launches"}
-    if name.startswith(("c4_", "d1_", "d2_", "m1_", "m2_", "s1_", "s2_", "t1_")) or name == "c3_fp8_8192":
+    if name.startswith(("c1_", "c4_", "d1_", "d2_", "m1_", "m2_", "s1_", "s2_", "t1_")) or name == "c3_fp8_8192":
         try:
             lcnt = [0]
+            # torch.matmul writes the inputs' type: a 16-bit result buffer of its own where ours is fp32
+            lib_out = None
+            if ops["in_name"] != "fp8" and ops["c"].dtype != ops["a"].dtype:
+                lib_out = torch.empty(ops["c"].shape, dtype=ops["a"].dtype, device=ops["c"].device)
 
             def lib_call():
                 a_, b_, c_ = sets[lcnt[0] % nsets]
@@ -979,13 +983,14 @@ def run_config(ctx, args, name):
                 if ops["in_name"] == "fp8":
                     torch._scaled_mm(a_, b_.t(), scale_a=ops["sa"], scale_b=ops["sb"], out_dtype=torch.bfloat16)
                 else:
-                    torch.matmul(a_, b_.t(), out=c_)
+                    torch.matmul(a_, b_.t(), out=c_ if lib_out is None else lib_out)
 
             for _ in range(3):
                 lib_call()
             lbest = min(ctx.timed(lib_call, steps, use_graph, sync_ranks=False)[0] / steps for _ in range(2))
             out["library_scaled_mm_us"] = lbest * 1e3
-            out["library"] = "torch._scaled_mm (cuBLASLt)" if ops["in_name"] == "fp8" else "torch.matmul (cuBLAS)"
+            out["library"] = ("torch._scaled_mm (cuBLASLt)" if ops["in_name"] == "fp8" else
+                              "torch.matmul (cuBLAS)" + ("" if lib_out is None else ", 16-bit out where ours is fp32"))
             out["vs_library"] = lbest / best
         except Exception as exc:
             out["library_scaled_mm_us"] = None
