@@ -344,7 +344,7 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
         // last one whose tiles are cut into K slices (tail_split) counts as one wave: such a problem has about 40 tiles of
         // 256 x 256, which leave half the SMs idle. Measured (BF16, planner before / with this form, us): 768 x 3328 x 8192
         // 45.7 / 37.6, 512 x 4864 x 8192 45.1 / 37.8, 1280 x 2048 x 8192 45.8 / 39.3, 1024 x 2560 x 4096 28.0 / 23.9,
-        // 512 x 5120 x 5120 30.5 / 28.1, but 256 x 10240 x 4096 26.4 / 28.5; FP8 768 x 3328 x 8192 25.7 / 23.4, 512 x 4864 x
+        // 512 x 5120 x 5120 30.5 / 28.1; FP8 768 x 3328 x 8192 25.7 / 23.4, 512 x 4864 x
         // 8192 25.4 / 22.9, 1280 x 2048 x 8192 25.6 / 24.6 (with 148 CTAs on 24 KB per K block the L2-to-SM traffic, not the
         // tensor pipe, sets the pace, so the gain is far from the factor the idle SMs suggest).
         if (c.pair && c.bn == 128) {
@@ -352,7 +352,13 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
             const long long tiles128 = static_cast<long long>((M + kPairTileM - 1) / kPairTileM) *
                                        static_cast<long long>((N + 127) / 128);
             int tt = 0, ts = 0, tk = 0;
+            // With a single row of tiles (M <= 256) whose 256 x 256 tiles fit one wave, those keep the choice: every
+            // 256 x 128 tile re-reads the same 256 rows of A (BF16 256 x 10240 x 4096 26.4 us against 28.5, 256 x 11008 x
+            // 4096 25.8 against 28.7).
+            const long long m_tiles = static_cast<long long>((M + kPairTileM - 1) / kPairTileM);
+            const long long tiles256 = m_tiles * static_cast<long long>((N + kPairTileN - 1) / kPairTileN);
             const bool tail_fits = allow_tail && !want_split && tiles128 > sms / 2 && tiles128 < sms &&
+                                   (m_tiles >= 2 || tiles256 > sms / 2) &&
                                    tail_split(tiles128, sms / 2, kb_total, &tt, &ts, &tk, kPair128TimePerKb);
             if (!(want_pair > 0 && want_bn == 128) && tiles128 > sms / 2 && !tail_fits) continue;
         }
