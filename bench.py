@@ -48,6 +48,7 @@ NCU_TRAFFIC_BYTES = {
     "c3_int8_8192": 237.3e6 + 115.2e6,
     "c4_fp8_16": 14.74e6,
     "d1_fp8_deep": 35.67e6,
+    "s1_fp8_skinny_wide": 45.2e6,
     "f1_fp8_blockscale": 131.1e6 + 40.1e6,
 }
 
