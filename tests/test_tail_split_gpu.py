@@ -137,14 +137,16 @@ def _narrow_no_split(q):
     return q.Tuning(128, 1, 0, 0, 1, 0)
 
 
-@pytest.mark.parametrize("M,N,K", [(1280, 2048, 8192), (1250, 2000, 8208), (512, 5120, 12288)])
-def test_int8_exact_with_last_wave_split_of_narrow_pair_tiles(qlib, oracle, dev, M, N, K):
+# 80 tiles (one wave and six tiles), ragged, a single-row-of-tiles-free shape, and 160 tiles (two waves and twelve)
+@pytest.mark.parametrize("M,N,K,tail", [(1280, 2048, 8192, 6), (1250, 2000, 8208, 6), (512, 5120, 12288, 6),
+                                        (2560, 2048, 8192, 12)])
+def test_int8_exact_with_last_wave_split_of_narrow_pair_tiles(qlib, oracle, dev, M, N, K, tail):
     q = qlib
     plan = q.plan_query(q.INT8, q.INT32, q.B_K_MAJOR, M, N, K, _narrow(q))
-    assert (plan["tile_m"], plan["tile_n"], plan["ctas_per_tile"], plan["tail_tiles"]) == (256, 128, 2, 6), plan
+    assert (plan["tile_m"], plan["tile_n"], plan["ctas_per_tile"], plan["tail_tiles"]) == (256, 128, 2, tail), plan
     assert plan["tail_slices"] >= 2
     need = q.workspace_query(q.INT8, q.B_K_MAJOR, M, N, K, _narrow(q))
-    assert need == plan["tail_slices"] * 6 * 256 * 128 * 4
+    assert need == plan["tail_slices"] * tail * 256 * 128 * 4
     assert q.workspace_query(q.INT8, q.B_K_MAJOR, M, N, K, _narrow_no_split(q)) == 0
     ai = datagen.int8_uniform((M, K), seed=K, stream=0)
     bi = datagen.int8_uniform((N, K), seed=K, stream=1)
