@@ -14,8 +14,9 @@ from qgemm_b200 import datagen
 pytestmark = pytest.mark.gpu
 
 # (M, N, K): M = 1, 16 | 17, 32 | 33, 64 (the three row classes and their edges)
+# (16, 512, 640): five K blocks of int8, an odd count for the two-blocks-per-load form of the 128-wide tile on 16 rows
 SHAPES = [(1, 384, 512), (16, 1000, 1040), (17, 640, 272), (32, 2304, 384), (33, 520, 2048), (64, 203, 768),
-          (8, 40000, 256)]
+          (8, 40000, 256), (16, 512, 640)]
 
 
 def _rows(M, bn):
@@ -67,7 +68,7 @@ def test_int8_exact_and_scaled(qlib, oracle, dev, M, N, K, bn, split):
 
 @pytest.mark.parametrize("kind", ["bf16", "fp16", "fp8"])
 @pytest.mark.parametrize("bn", [128, 256])
-@pytest.mark.parametrize("M,N,K", SHAPES[:6])
+@pytest.mark.parametrize("M,N,K", SHAPES[:6] + SHAPES[7:])
 def test_float_kinds(qlib, oracle, dev, M, N, K, bn, kind):
     q = qlib
     a32, b32 = datagen.normal((M, K), M + K, 0), datagen.normal((N, K), M + K, 1)
@@ -156,6 +157,10 @@ def test_row_major_b_int8(qlib, oracle, dev, bn):
 
 def test_planner_rows_per_stage(qlib):
     q = qlib
+    # two K blocks per TMA instruction with the 128-wide tile only on 16 rows of A, and not with slices inside a cluster
+    assert q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 16, 11008, 4096)["k_blocks_per_load"] == 2
+    assert q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 32, 11008, 4096)["k_blocks_per_load"] == 1
+    assert q.plan_query(q.INT8, q.INT32, q.B_K_MAJOR, 16, 1000, 2048, q.Tuning(128, 4, 0, 0, -1, 0))["k_blocks_per_load"] == 1
     # a skinny problem whose 64-wide tiles would need two waves: one wave of 128-wide tiles on 16 rows of A
     p = q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 16, 11008, 4096)
     assert (p["tile_n"], p["split_k"], p["a_rows_per_stage"], p["ctas"]) == (128, 1, 16, 86), p
