@@ -529,15 +529,15 @@ struct Plan {
 // 2048 10.13 / 8.73 / 8.94 / 9.67, FP8 1024 x 1024 x 4096 10.25 / 8.87 / 10.43 / 13.09, BF16 1024^3 6.78 / 6.14 / 6.75 /
 // 7.74: two halve the instruction count, more make the barriers too coarse for the pipeline. With the 128-wide tile
 // (16 KB boxes, six stages) it does not pay: FP8 256 x 7168 x 2048 8.08 / 8.41 -- except where its A box is a 2 KB one
-// (16 rows, ten stages; not the in-cluster kernel, whose ring has an odd number of slots there): FP8 16 x 11008 x 4096
+// (16 rows, ten stages, lone-CTA and in-cluster kernel alike): FP8 16 x 11008 x 4096
 // 11.15 / 10.74, 16 x 9728 x 4096 11.08 / 10.39, 16 x 12288 x 2048 8.01 / 7.52, BF16 16 x 9728 x 4096 18.8 / 17.4; with 32
 // rows nothing (FP8 32 x 10240 x 8192 19.17 / 19.12), with the 256-wide tile nothing (14.17 / 14.17).
 int choose_kgroup(const Config& cfg, bool b_direct, size_t K, int elem_bytes) {
     if (cfg.pair || b_direct || cfg.bal_tiles != 0 || (K * elem_bytes) % 128 != 0) return 1;
     const int stages = std::min(16, (192 * 1024) / ((cfg.am + cfg.bn) * 128));
-    const bool by_default = cfg.bn == 64 || (cfg.bn == 128 && cfg.am <= 16 && cfg.kcluster == 0);
+    const bool by_default = cfg.bn == 64 || (cfg.bn == 128 && cfg.am <= 16);
     int g = g_env.kgroup > 0 ? g_env.kgroup : (by_default ? 2 : 1);
-    if (cfg.bn == 128 && cfg.kcluster != 0) g = 1;  // that kernel's ring has stages + 1 slots, which `stages` below does not describe
+    if (cfg.bn == 128 && cfg.kcluster != 0 && cfg.am != 16) g = 1;  // there the in-cluster kernel's ring has stages + 1 slots
     if (g != 2 && g != 4 && g != 8) g = 1;
     while (g > 1 && stages % g != 0) g /= 2;
     return g;

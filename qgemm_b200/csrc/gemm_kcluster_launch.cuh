@@ -11,7 +11,9 @@ cudaError_t launch_kcluster_one(const CUtensorMap& ta, const CUtensorMap& tb, co
                                 cudaStream_t stream) {
     // the kernel has no staging buffers, which leaves room for a seventh stage of the 128-wide tile (the 64-wide
     // tile keeps its even stage count for the two-blocks-per-load grouping)
-    constexpr int STAGES = StagesFor<BN, AM>::value + (BN == 128 ? 1 : 0);
+    // No staging buffers in this kernel, so one more stage fits beside the 128-wide tile's; not with 16 rows of A, where
+    // the ring keeps its ten slots for the loads of two K blocks per instruction (an even count).
+    constexpr int STAGES = StagesFor<BN, AM>::value + ((BN == 128 && AM != 16) ? 1 : 0);
     auto kernel = gemm_tcgen05_kcluster_kernel<KIND, BN, STAGES, OUT, AM, S>;
     constexpr int smem = GemmSmem<BN, STAGES, AM, true>::kDynamicBytes;
     static_assert(smem <= 227 * 1024, "dynamic shared memory of one CTA");

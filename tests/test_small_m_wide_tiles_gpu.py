@@ -89,7 +89,8 @@ def test_float_kinds(qlib, oracle, dev, M, N, K, bn, kind):
 
 
 # K a multiple of 8 x 128 bytes, so that 2, 4 and 8 slices are all non-empty and equal
-CLUSTER_SHAPES = [(1, 384, 2048), (16, 1000, 2048), (17, 640, 4096), (33, 520, 2048), (64, 203, 3072)]
+# (16, 256, 3072): three K blocks per slice with eight slices, an odd count for the two-blocks-per-load form
+CLUSTER_SHAPES = [(1, 384, 2048), (16, 1000, 2048), (17, 640, 4096), (33, 520, 2048), (64, 203, 3072), (16, 256, 3072)]
 
 
 @pytest.mark.parametrize("slices", [2, 4, 8])
@@ -157,10 +158,11 @@ def test_row_major_b_int8(qlib, oracle, dev, bn):
 
 def test_planner_rows_per_stage(qlib):
     q = qlib
-    # two K blocks per TMA instruction with the 128-wide tile only on 16 rows of A, and not with slices inside a cluster
+    # two K blocks per TMA instruction with the 128-wide tile only on 16 rows of A (slices inside a cluster included)
     assert q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 16, 11008, 4096)["k_blocks_per_load"] == 2
     assert q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 32, 11008, 4096)["k_blocks_per_load"] == 1
-    assert q.plan_query(q.INT8, q.INT32, q.B_K_MAJOR, 16, 1000, 2048, q.Tuning(128, 4, 0, 0, -1, 0))["k_blocks_per_load"] == 1
+    assert q.plan_query(q.INT8, q.INT32, q.B_K_MAJOR, 16, 1000, 2048, q.Tuning(128, 4, 0, 0, -1, 0))["k_blocks_per_load"] == 2
+    assert q.plan_query(q.INT8, q.INT32, q.B_K_MAJOR, 17, 640, 4096, q.Tuning(128, 4, 0, 0, -1, 0))["k_blocks_per_load"] == 1
     # a skinny problem whose 64-wide tiles would need two waves: one wave of 128-wide tiles on 16 rows of A
     p = q.plan_query(q.FP8_E4M3, q.BF16, q.B_K_MAJOR, 16, 11008, 4096)
     assert (p["tile_n"], p["split_k"], p["a_rows_per_stage"], p["ctas"]) == (128, 1, 16, 86), p
