@@ -345,8 +345,9 @@ Config choose_config(size_t M, size_t N, int kb_total, int sms, const qgemm_tuni
         // 256 x 256, which leave half the SMs idle. Measured (BF16, planner before / with this form, us): 768 x 3328 x 8192
         // 45.7 / 37.6, 512 x 4864 x 8192 45.1 / 37.8, 1280 x 2048 x 8192 45.8 / 39.3, 1024 x 2560 x 4096 28.0 / 23.9,
         // 512 x 5120 x 5120 30.5 / 28.1; FP8 768 x 3328 x 8192 25.7 / 23.4, 512 x 4864 x
-        // 8192 25.4 / 22.9, 1280 x 2048 x 8192 25.6 / 24.6 (with 148 CTAs on 24 KB per K block the L2-to-SM traffic, not the
-        // tensor pipe, sets the pace, so the gain is far from the factor the idle SMs suggest).
+        // 8192 25.4 / 22.9, 1280 x 2048 x 8192 25.6 / 24.6. The gain is far from the factor the idle SMs suggest: per K
+        // block a CTA of a 256 x 128 pair moves 56 KB through its shared memory (24 KB in by TMA, 32 KB read by the tensor
+        // cores) for 256 cycles of tensor work, a ceiling of 58 % of the tensor pipe (ncu: 54-55 %).
         if (c.pair && c.bn == 128) {
             if (!allow_pair128 || want_pair == 2) continue;
             const long long tiles128 = static_cast<long long>((M + kPairTileM - 1) / kPairTileM) *
