@@ -195,7 +195,7 @@ int qgemm_device_status(int* out4);
 /*
  * The QGEMM_* environment variables (tuning overrides for experiments: QGEMM_TILE_N, QGEMM_SPLIT_K,
  * QGEMM_GROUP_M, QGEMM_CTA_PAIR, QGEMM_RELAYOUT_B, QGEMM_MAX_CTAS, QGEMM_DIRECT_STORE, QGEMM_FULL_A_TILE,
- * QGEMM_TAIL_SPLIT, QGEMM_BALANCE, QGEMM_PREFETCH, QGEMM_KCLUSTER, QGEMM_KGROUP, QGEMM_EARLY_GROUPS, QGEMM_ONE_TILE, QGEMM_HOST_BANDS, QGEMM_HOST_BANDS_N) are
+ * QGEMM_TAIL_SPLIT, QGEMM_BALANCE, QGEMM_PREFETCH, QGEMM_KCLUSTER, QGEMM_KGROUP, QGEMM_EARLY_GROUPS, QGEMM_ONE_TILE, QGEMM_EVEN_RUNS, QGEMM_HOST_BANDS, QGEMM_HOST_BANDS_N) are
  * read once, when the library is
  * loaded; this reads them again. Not meant to run concurrently with GEMM calls of other threads.
  */

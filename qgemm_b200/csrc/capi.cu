@@ -221,6 +221,7 @@ EnvSettings read_env() {
     e.full_a_tile = env_int("QGEMM_FULL_A_TILE");
     const char* tail = std::getenv("QGEMM_TAIL_SPLIT");
     e.tail_split_off = (tail != nullptr && tail[0] == '0') ? 1 : 0;
+    e.even_runs = env_int("QGEMM_EVEN_RUNS") > 0 ? 1 : 0;  // 1: the K range of all 256 x 256 pair tiles dealt out evenly
     e.balance = env_int("QGEMM_BALANCE") > 0 ? 1 : 0;
     const char* pf = std::getenv("QGEMM_PREFETCH");
     e.prefetch_off = (pf != nullptr && pf[0] == '0') ? 1 : 0;
@@ -271,6 +272,24 @@ bool tail_split(long long tiles, int clusters, int kb_total, int* tail_tiles, in
     return *slices >= 2;
 }
 
+// The K range dealt out evenly over the clusters (GemmParams::sk_parts): T tiles of 256 x 256 on S clusters that are not a
+// whole number of waves then take T / S tile times of main loop instead of ceil(T / S). Built, exact (tests/
+// test_even_runs_gpu.py) and measured on B200, it does not pay and is therefore taken only with QGEMM_EVEN_RUNS=1: every
+// cluster has two partial tiles of 256 KB of 32-bit sums to store and the pass that adds them up reads 39 MB, together
+// 15-20 us, more than the idle SMs cost (us, whole tiles / even runs: FP8 768 x 3328 x 8192 25.8 / 32.2, 2048^3 10.9 / 29.7,
+// 4096^3 51.6 / 74.1; BF16 768 x 3328 x 8192 45.7 / 47.3, 1024 x 2048 x 8192 31.2 / 38.1); on many waves the runs also
+// break the tile order that keeps neighbouring tiles in L2 together (FP8 8192^3 345 / 545).
+// `pieces_out` = the most pieces a tile can have.
+bool even_runs_time(long long tiles, int clusters, int kb_total, double* t_out, int* pieces_out) {
+    if (g_env.even_runs <= 0 || clusters <= 0 || tiles <= 0 || tiles % clusters == 0) return false;
+    const long long total = tiles * kb_total;
+    const long long per_run = total / clusters;
+    if (per_run < 8) return false;  // runs of fewer than eight K blocks: set-up and drain outweigh them
+    *t_out = 0.0;  // asked for: before all else
+    *pieces_out = static_cast<int>((kb_total + per_run - 1) / per_run) + 1;
+    return true;
+}
+
 // Estimated duration in units of "one 128-byte K block of a 128x256 tile" (about 0.27 us at peak).
 // `pair` = CTA pairs on 256x256 tiles (half as many schedulable units, a third fewer bytes per flop).
 // `in_cluster` = the K slices of a tile run on the CTAs of one cluster and are added up through distributed shared
@@ -298,6 +317,11 @@ double estimate(int bn, bool pair, int splits, size_t M, size_t N, int kb_total,
     int tt = 0, ts = 0, tk = 0;
     if (pair && real_splits == 1 && allow_tail && tail_split(units, slots, kb_total, &tt, &ts, &tk, t_kb))
         t = static_cast<double>(waves - 1) * (kbps * t_kb + fill) + (tk * t_kb + fill) + kTailOverhead;
+    else if (pair && bn == kPairTileN && real_splits == 1 && allow_tail) {
+        double te = 0.0;
+        int pieces = 0;
+        if (even_runs_time(units, slots, kb_total, &te, &pieces)) t = te;
+    }
     if (real_splits > 1 && in_cluster) {
         // full 128-row tiles have four times the partial sums of a 32-row problem to put through shared memory
         // (measured: FP8 1024 x 512 x 2048 in two slices 6.9 us against 6.0 unsplit, so the split must not be taken there)
@@ -522,6 +546,8 @@ struct Plan {
     int tail_slices;
     int tail_kb_per_slice;
     int kgroup;             // K blocks per TMA instruction (GemmParams::kgroup), 1 = one block per load
+    int even_runs;          // clusters the K range of all tiles is dealt out over (GemmParams::sk_parts), 0 = off
+    int even_pieces;        // the most pieces a tile has then (depth of the scratch array)
 };
 
 // K-grouped loads (GemmParams::kgroup): the lone-CTA kernels on K-major operands whose K is a whole number of 128-byte
@@ -578,6 +604,19 @@ int make_plan(int in_dtype, int out_dtype, int b_layout, size_t M, size_t N, siz
             p->partial_bytes = static_cast<size_t>(p->tail_slices) * p->tail_tiles * kPairTileM * p->cfg.bn * 4;
         else
             p->tail_tiles = 0;
+    }
+    p->even_runs = p->even_pieces = 0;
+    if (allow_tail && p->tail_tiles == 0 && p->cfg.pair && p->cfg.bn == kPairTileN && !p->cfg.wide && p->cfg.splits == 1 &&
+        p->cfg.kcluster == 0) {
+        const long long tiles = static_cast<long long>((M + kPairTileM - 1) / kPairTileM) *
+                                static_cast<long long>((N + kPairTileN - 1) / kPairTileN);
+        double t = 0.0;
+        int pieces = 0;
+        if (tiles < (1 << 20) && even_runs_time(tiles, sms / 2, p->kb_total, &t, &pieces)) {
+            p->even_runs = sms / 2;
+            p->even_pieces = pieces;
+            p->partial_bytes = static_cast<size_t>(2) * p->even_runs * kPairTileM * kPairTileN * 4;  // two slots per run
+        }
     }
     return QGEMM_OK;
 }
@@ -765,6 +804,7 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
                           kgroup == 1 && work == static_cast<long long>(grid);
     cudaError_t e;
     const bool tail = cfg.pair && !cfg.wide && plan.tail_tiles > 0 && p.c_tma_ok && n_extra == 0;
+    const bool even_runs = cfg.pair && !cfg.wide && !tail && plan.even_runs > 0 && p.c_tma_ok && n_extra == 0 && cfg.bn == kPairTileN;
     p.total_work = static_cast<int>(work);
     if (cfg.kcluster > 0 && cfg.pair) {
         switch (plan.ti.kind) {
@@ -792,6 +832,16 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
             p.total_work = p.tail_begin + plan.tail_tiles * plan.tail_slices;
             rc = make_output_map(partials, static_cast<uint64_t>(plan.tail_tiles) * kPairTileM, static_cast<uint64_t>(cfg.bn),
                                  static_cast<uint64_t>(cfg.bn), static_cast<uint64_t>(plan.tail_slices), OUT_RAW32, &tws);
+            if (rc != QGEMM_OK) return rc;
+        }
+        if (even_runs) {
+            // every cluster one run of K blocks across tile boundaries; a run's partial first and last tile go to its two scratch slots
+            p.sk_parts = plan.even_runs;
+            p.sk_tiles = static_cast<int>(work);
+            const long long per_run = (work * p.kb_total + plan.even_runs - 1) / plan.even_runs;
+            p.total_work = plan.even_runs * (static_cast<int>((per_run + p.kb_total - 1) / p.kb_total) + 1);
+            rc = make_output_map(partials, static_cast<uint64_t>(2 * plan.even_runs) * kPairTileM, kPairTileN, kPairTileN, 1,
+                                 OUT_RAW32, &tws);
             if (rc != QGEMM_OK) return rc;
         }
         int clusters = static_cast<int>(std::min<long long>(p.total_work, st->sm_count / 2));
@@ -823,6 +873,14 @@ int gemm_dispatch_locked(int in_dtype, int out_dtype, int b_layout, const void* 
         rc = splitk_reduce_tiles_launch(partials, plan.tail_tiles, plan.tail_slices, plan.ti.acc_int, C,
                                         static_cast<long long>(ldc), p.M, p.N, plan.out_kind, scale_a, scale_b, tiles,
                                         cfg.bn, stream);
+        if (rc != QGEMM_OK) return rc;
+    }
+
+    if (even_runs) {
+        GemmParams tiles = p;
+        tiles.tile_offset = 0;
+        rc = splitk_reduce_runs_launch(partials, plan.ti.acc_int, C, static_cast<long long>(ldc), p.M, p.N, plan.out_kind,
+                                       scale_a, scale_b, tiles, stream);
         if (rc != QGEMM_OK) return rc;
     }
 
@@ -1104,7 +1162,8 @@ int qgemm_plan_query_ex(int in_dtype, int out_dtype, int b_layout, size_t M, siz
     const Config& c = plan.cfg;
     const int tile_m = c.wide ? kWideTileM : (c.pair ? kPairTileM : kBM);
     const long long tiles_n = c.bal_tiles > 0 ? c.bal_tiles : static_cast<long long>((N + c.bn - 1) / c.bn);
-    const long long ctas = static_cast<long long>((M + tile_m - 1) / tile_m) * tiles_n * c.splits * (c.pair ? 2 : 1);
+    long long ctas = static_cast<long long>((M + tile_m - 1) / tile_m) * tiles_n * c.splits * (c.pair ? 2 : 1);
+    if (plan.even_runs > 0) ctas = 2LL * plan.even_runs;  // one run of K blocks per cluster, whatever the number of tiles
     const int vals[QGEMM_PLAN_FIELDS] = {
         tile_m, c.bn, c.pair ? 2 : 1, c.splits, plan.tail_tiles, plan.tail_slices, c.bal_tiles,
         c.bal_tiles > 0 ? c.bal_units * 16 : c.bn, c.am, static_cast<int>(std::min<long long>(ctas, sms)), c.kcluster,

@@ -282,6 +282,11 @@ int splitk_reduce_tiles_launch(const void* partials, int slots, int splits, bool
                                int M, int N, int out_kind, const float* scale_a, const float* scale_b,
                                const GemmParams& tiles, int tile_n, cudaStream_t stream);
 
+// Adds up the pieces of runs (GemmParams::sk_parts; splitk_reduce.cu): 2 * sk_parts slots of 256 x 256 partial sums;
+// `tiles` carries sk_parts, sk_tiles, kb_total and the tile order (m_tiles, n_tiles, group_m; splits = 1).
+int splitk_reduce_runs_launch(const void* partials, bool acc_is_int, void* C, long long ldc, int M, int N, int out_kind,
+                              const float* scale_a, const float* scale_b, const GemmParams& tiles, cudaStream_t stream);
+
 // In-cluster split-K (gemm_sm100_kcluster.cuh; gemm_kc_*.cu): `tiles` clusters of `slices` CTAs, 64- or 128-wide tiles.
 cudaError_t launch_gemm_kcluster_f16(int bn, int out, int am, int slices, const CUtensorMap& ta, const CUtensorMap& tb,
                                      const GemmParams& p, int tiles, cudaStream_t stream);

@@ -58,6 +58,15 @@ struct GemmParams {
     int tail_begin;
     int tail_slices;
     int tail_kb_per_slice;
+    // K range dealt out evenly (CTA-pair kernel, splits == 1, no last-wave split): the sk_tiles * kb_total K blocks of
+    // all tiles, laid end to end in tile order, are cut into sk_parts equal runs; run r is the blocks [r * U / parts,
+    // (r + 1) * U / parts). A run covers the end of one tile, whole tiles and the start of another; work item w is
+    // piece (w / sk_parts) of run (w % sk_parts), so a launch of sk_parts clusters gives every cluster one run. A piece
+    // that is a whole tile is stored to C as usual; the others (at most the first and the last of a run) store 32-bit
+    // partial sums to scratch slot [run] if they begin the run, else [sk_parts + run], and splitk_reduce_runs_kernel
+    // adds up each tile's pieces in run order. 0 = off.
+    int sk_parts;
+    int sk_tiles;
     int total_work;
     int tile_offset;  // added to the tile number by decode_tile (the pass that sums the slices locates slot i with it)
     // Balanced column tiling (lone-CTA kernel, K-major B, one wave): instead of n_tiles equal tiles of BN columns,
@@ -181,15 +190,51 @@ __device__ __forceinline__ void tile_columns(const GemmParams& p, int n_blk, int
     }
 }
 
-// One work item of the CTA-pair kernel: a whole tile, or one K slice of a last-wave tile.
+// One work item of the CTA-pair kernel: a whole tile, one K slice of a last-wave tile, or one piece of a run
+// (GemmParams::sk_parts; kb0 == kb1 marks an empty item).
 struct WorkItem {
     TileCoord t;
     int kb0, kb1;  // K blocks [kb0, kb1)
     int slot;      // >= 0: partial sums of slice t.split go to this scratch slot; -1: an ordinary tile
 };
 
+// The run (see GemmParams::sk_parts) that holds K block x of the end-to-end order: the largest r with r * U / parts <= x.
+__host__ __device__ __forceinline__ int run_of_block(long long x, int parts, long long total) {
+    return static_cast<int>(((x + 1) * parts - 1) / total);
+}
+
 __device__ __forceinline__ WorkItem decode_work(int w, const GemmParams& p) {
     WorkItem it;
+    if (p.sk_parts > 0) {
+        const int run = w % p.sk_parts, piece = w / p.sk_parts;
+        const long long total = static_cast<long long>(p.sk_tiles) * p.kb_total;
+        const int start = static_cast<int>((run * total) / p.sk_parts);
+        int pos = start;
+        const int end = static_cast<int>(((run + 1) * total) / p.sk_parts);
+        int tile = pos / p.kb_total;
+        int pe = min(end, (tile + 1) * p.kb_total);
+        for (int i = 0; i < piece && pos < end; ++i) {
+            pos = pe;
+            tile = pos / p.kb_total;
+            pe = min(end, (tile + 1) * p.kb_total);
+        }
+        if (pos >= end) {  // this run has fewer pieces: an empty item, which every role passes over
+            it.t = decode_tile(0, p);
+            it.slot = -1;
+            it.kb0 = it.kb1 = 0;
+            return it;
+        }
+        it.t = decode_tile(tile, p);  // splits == 1: work item number == tile number
+        it.kb0 = pos - tile * p.kb_total;
+        it.kb1 = pe - tile * p.kb_total;
+        if (it.kb0 == 0 && it.kb1 == p.kb_total) {
+            it.slot = -1;
+        } else {
+            it.slot = pos == start ? run : p.sk_parts + run;
+            it.t.split = 0;
+        }
+        return it;
+    }
     if (p.tail_begin > 0 && w >= p.tail_begin) {
         const int u = w - p.tail_begin;
         it.slot = u / p.tail_slices;

@@ -106,7 +106,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         ptx::prefetch_tensormap(&tmap_a);
         ptx::prefetch_tensormap(&tmap_b);
         if (p.c_tma_ok) ptx::prefetch_tensormap(&tmap_c);
-        if (p.tail_begin > 0) ptx::prefetch_tensormap(&tmap_ws);
+        if (p.tail_begin > 0 || p.sk_parts > 0) ptx::prefetch_tensormap(&tmap_ws);
         if constexpr (GATHER)
             for (int d = 0; d < p.n_extra_dst; ++d) ptx::prefetch_tensormap(&extra.map[d]);
     }
@@ -176,6 +176,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             for (int w = cluster_id; ok && w < total_work; w += n_clusters, ++it) {
                 const WorkItem item = decode_work(w, p);
                 const int kb0 = item.kb0, kb1 = item.kb1;
+                if (kb0 >= kb1) {  // an empty item (GemmParams::sk_parts): no accumulator is taken for it
+                    --it;
+                    continue;
+                }
                 const uint32_t acc = it & 1u;
                 const uint32_t acc_phase = (it >> 1) & 1u;
                 if (!wait_bounded(bar_tempty + acc * 8, acc_phase ^ 1u, abort_flag, p.status, ROLE_MMA, -1, peer_abort)) break;
@@ -218,6 +222,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         uint32_t out_buf = 0;
         for (int w = cluster_id; w < total_work; w += n_clusters, ++it) {
             const WorkItem item = decode_work(w, p);
+            if (item.kb0 >= item.kb1) {  // an empty item: the MMA issuer passed over it as well
+                --it;
+                continue;
+            }
             const TileCoord t = item.t;
             const uint32_t acc = it & 1u;
             const uint32_t acc_phase = (it >> 1) & 1u;

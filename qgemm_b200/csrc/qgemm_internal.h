@@ -39,7 +39,7 @@ int take_test_skip_kb();
 // QGEMM_* environment variables, read when the library is loaded and again by qgemm_reload_env().
 struct EnvSettings {
     int tile_n = 0, split_k = 0, group_m = 0, cta_pair = 0, relayout_b = 0, max_ctas = 0, direct_store = 0;
-    int full_a_tile = 0, tail_split_off = 0, balance = 0, prefetch_off = 0, prefetch_force = 0, kcluster_off = 0, kcluster_pair_off = 0, kgroup = 0, early_groups = -1, one_tile_off = 0;
+    int full_a_tile = 0, tail_split_off = 0, balance = 0, prefetch_off = 0, prefetch_force = 0, kcluster_off = 0, kcluster_pair_off = 0, kgroup = 0, early_groups = -1, one_tile_off = 0, even_runs = 0;
     int host_bands = 0, host_bands_n = 0;  // 0 = default
 };
 const EnvSettings& env_settings();

@@ -20,13 +20,15 @@ template <bool ACC_INT>
 __device__ __forceinline__ void reduce_quad(const uint32_t* __restrict__ src, long long split_stride, int splits,
                                             void* __restrict__ C, long long ldc, long long row, int col, int N,
                                             int out_kind, const float* __restrict__ scale_a,
-                                            const float* __restrict__ scale_b, int c_vec_ok) {
+                                            const float* __restrict__ scale_b, int c_vec_ok,
+                                            const uint32_t* __restrict__ first_src = nullptr) {
+    // first_src != nullptr: term 0 is read there instead of at src (the other terms stay at src + k * split_stride)
     uint32_t raw[4];
     float f[4];
     if constexpr (ACC_INT) {
         int s[4] = {0, 0, 0, 0};
         for (int k = 0; k < splits; ++k) {
-            const uint4 v = __ldg(reinterpret_cast<const uint4*>(src + k * split_stride));
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>((k == 0 && first_src != nullptr) ? first_src : src + k * split_stride));
             s[0] += static_cast<int>(v.x);
             s[1] += static_cast<int>(v.y);
             s[2] += static_cast<int>(v.z);
@@ -40,7 +42,7 @@ __device__ __forceinline__ void reduce_quad(const uint32_t* __restrict__ src, lo
     } else {
         float s[4] = {0.f, 0.f, 0.f, 0.f};
         for (int k = 0; k < splits; ++k) {
-            const uint4 v = __ldg(reinterpret_cast<const uint4*>(src + k * split_stride));
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>((k == 0 && first_src != nullptr) ? first_src : src + k * split_stride));
             s[0] += __uint_as_float(v.x);
             s[1] += __uint_as_float(v.y);
             s[2] += __uint_as_float(v.z);
@@ -136,7 +138,57 @@ splitk_reduce_tiles_kernel(const uint32_t* __restrict__ partials, long long spli
     reduce_quad<ACC_INT>(src, split_stride, splits, C, ldc, row, col, N, out_kind, scale_a, scale_b, c_vec_ok);
 }
 
+// The same sum for the pieces of runs (GemmParams::sk_parts): blockIdx.y = tile; the tile's K blocks [t * kb, (t + 1) * kb)
+// of the end-to-end order lie in runs first ... last, one piece each, in run order. A piece that begins its run lies in
+// scratch slot [run], one that does not (it began at the tile's first block) in slot [parts + run]; slots are 256 x 256
+// partial sums. A tile that lies in one run was stored to C by the GEMM itself.
+template <bool ACC_INT>
+__global__ void __launch_bounds__(256)
+splitk_reduce_runs_kernel(const uint32_t* __restrict__ partials, void* __restrict__ C, long long ldc, int M, int N,
+                          int out_kind, const float* __restrict__ scale_a, const float* __restrict__ scale_b,
+                          int c_vec_ok, const GemmParams tiles) {
+    ptx::pdl_launch_dependents();
+    ptx::pdl_wait();
+    const int tile = static_cast<int>(blockIdx.y);
+    const long long total = static_cast<long long>(tiles.sk_tiles) * tiles.kb_total;
+    const long long begin = static_cast<long long>(tile) * tiles.kb_total;
+    const int first = run_of_block(begin, tiles.sk_parts, total);
+    const int last = run_of_block(begin + tiles.kb_total - 1, tiles.sk_parts, total);
+    if (first == last) return;
+    const TileCoord t = decode_tile(tile, tiles);
+    const int idx = static_cast<int>(blockIdx.x) * 256 + static_cast<int>(threadIdx.x);  // 256 rows x 64 quads
+    const int r = idx >> 6;
+    const int c = (idx & 63) * 4;
+    const long long row = static_cast<long long>(t.m_blk) * kPairTileM + r;
+    const int col = t.n_blk * kPairTileN + c;
+    if (r >= kPairTileM || row >= M || col >= N) return;
+    const long long slot_elems = static_cast<long long>(kPairTileM) * kPairTileN;
+    const long long in_slot = static_cast<long long>(r) * kPairTileN + c;
+    const bool first_begins_here = (first * total) / tiles.sk_parts == begin;
+    const uint32_t* first_src = partials + (first_begins_here ? first : tiles.sk_parts + first) * slot_elems + in_slot;
+    const uint32_t* src = partials + first * slot_elems + in_slot;  // src + k * slot_elems: the piece that begins run first + k
+    reduce_quad<ACC_INT>(src, slot_elems, last - first + 1, C, ldc, row, col, N, out_kind, scale_a, scale_b, c_vec_ok,
+                         first_src);
+}
+
 }  // namespace
+
+int splitk_reduce_runs_launch(const void* partials, bool acc_is_int, void* C, long long ldc, int M, int N, int out_kind,
+                              const float* scale_a, const float* scale_b, const GemmParams& tiles, cudaStream_t stream) {
+    if (tiles.sk_tiles <= 0 || tiles.sk_parts <= 0) return QGEMM_OK;
+    const int out_bytes = (out_kind == OUT_BF16 || out_kind == OUT_F16) ? 2 : 4;
+    const int c_vec_ok = (reinterpret_cast<uintptr_t>(C) % 16 == 0) && ((ldc * out_bytes) % 16 == 0);
+    const uint32_t* p = reinterpret_cast<const uint32_t*>(partials);
+    const dim3 grid(kPairTileM * (kPairTileN / 4) / 256, static_cast<unsigned>(tiles.sk_tiles));
+    cudaError_t e;
+    if (acc_is_int)
+        e = launch_pdl(splitk_reduce_runs_kernel<true>, grid, dim3(256), 0, stream, p, C, ldc, M, N, out_kind, scale_a,
+                       scale_b, c_vec_ok, tiles);
+    else
+        e = launch_pdl(splitk_reduce_runs_kernel<false>, grid, dim3(256), 0, stream, p, C, ldc, M, N, out_kind, scale_a,
+                       scale_b, c_vec_ok, tiles);
+    return e == cudaSuccess ? QGEMM_OK : QGEMM_ERR_CUDA;
+}
 
 int splitk_reduce_tiles_launch(const void* partials, int slots, int splits, bool acc_is_int, void* C, long long ldc,
                                int M, int N, int out_kind, const float* scale_a, const float* scale_b,
